@@ -1,0 +1,217 @@
+/*
+ * mdc.h -- C ABI of libmdc.so: sm_100a CUDA kernels for the context-parallel
+ * DeepSeek-sparse-attention decode path (indexer logits, top-k selection and
+ * merge, sparse MLA attention, LSE merge, KV compressor, event / comm /
+ * scheduler device layer, persistent decode megakernel).
+ *
+ * Conventions
+ *   - Every pointer is a device pointer unless stated otherwise; the caller
+ *     owns all memory, the library allocates nothing (borrowed for the
+ *     duration of the stream-ordered launch).
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous.
+ *   - Return value: MDC_OK or a negative MDC_ERR_* code; nothing aborts.
+ *   - Device-side failures (a wait that ran out of its budget, an id out of
+ *     range) are written to the caller's 8-word `status` block (may be NULL):
+ *     [0]=MDC_DEV_* code, [1]=block, [2..3]=detail, [4..5]=seen, [6..7]=wanted.
+ *
+ * Each entry point cites the interface of the reference project
+ * (ultism/mega-dsa-cp, paths relative to its root) that it replaces.
+ */
+#ifndef MDC_H_
+#define MDC_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MDC_ABI_VERSION 1
+
+/* host-side return codes */
+#define MDC_OK 0
+#define MDC_ERR_BAD_SHAPE (-1)   /* unsupported size / count            */
+#define MDC_ERR_BAD_ALIGN (-2)   /* pointer or stride not 16 B aligned  */
+#define MDC_ERR_BAD_FORMAT (-3)  /* unknown format / dtype enum         */
+#define MDC_ERR_NULL (-4)        /* required pointer missing            */
+#define MDC_ERR_CUDA (-5)        /* CUDA runtime error, see mdc_last_cuda_error */
+#define MDC_ERR_TOO_LARGE (-6)   /* exceeds a stated capacity           */
+
+/* device-side status codes (status[0]) */
+#define MDC_DEV_OK 0
+#define MDC_DEV_WAIT_TIMEOUT 1   /* event wait gave up: [2]=event id            */
+#define MDC_DEV_COPY_TIMEOUT 2   /* staged copy never completed: [2]=stage      */
+#define MDC_DEV_BAD_INDEX 3      /* page / entry id out of range: [2]=id        */
+#define MDC_DEV_BAD_OP 4         /* unknown task op code: [2]=op                */
+#define MDC_DEV_ABORTED 5        /* left early because another block failed     */
+
+/* index-K cache formats (E2M1 values, two per byte, even element low nibble) */
+#define MDC_FMT_MXFP4 0 /* UE8M0 scale per 32 elements; page = [P x 64 B][atom-ordered scales] */
+#define MDC_FMT_NVFP4 1 /* UE4M3 scale per 16 elements; page = [P x 64 B][P x 8 B scales]      */
+
+/* query formats of the indexer */
+#define MDC_Q_FP4 0  /* (B, N, 64) packed E2M1 + (B, N*4) atom-ordered UE8M0 scales */
+#define MDC_Q_BF16 1 /* (B, N, 128) bf16                                             */
+
+/* element types of attention operands / partial outputs */
+#define MDC_DT_F32 0
+#define MDC_DT_BF16 1
+#define MDC_DT_E4M3 2
+
+int mdc_abi_version(void);
+const char* mdc_status_string(int code);
+int mdc_last_cuda_error(void);
+/* registers / static smem / max dynamic smem of a kernel, for co-residency
+ * checks (the probe planned in docs/phase1.4-comm-tasks.md:14-16).
+ * kernel ids: MDC_K_* below.  Needs a CUDA device. */
+int mdc_kernel_attrs(int kernel_id, int* regs, int* static_smem, int* max_dynamic_smem);
+#define MDC_K_LOGITS 0
+#define MDC_K_MERGE_TOPK 1
+#define MDC_K_LSE_MERGE 2
+#define MDC_K_SPARSE_MLA 3
+#define MDC_K_MEGAKERNEL 4
+#define MDC_K_COUNT 5
+
+/* ------------------------------------------------------------------------
+ * FP4 paged MQA indexer logits (+ optional fused exact local top-k).
+ * Replaces run_fp4_paged_mqa_logits, mega_dsa_cp/tiles/logits.py:1054-1145
+ * (kernel Fp4PagedMQALogits.kernel, logits.py:421-870; candidate heap
+ * logits.py:886-1042).
+ *
+ *   logits[(b*q_len+t), pos] = sum_h w[b, t*heads+h] * relu(q[b, t*heads+h] . k[pos])
+ *   k[pos] = dequantised row (pos % page_tokens) of page block_table[b, pos / page_tokens]
+ *
+ * One thread block per (chunk, b); a chunk is `blocks_per_chunk` consecutive
+ * page-table entries.  With cand_v == NULL the fp32 logits row is written.
+ * With cand_v != NULL the block keeps its scores on chip and emits the exact
+ * top_k of the chunk positions pos < seq_lens[b] - window_exclude under the
+ * total order (logit descending, position ascending), in position order:
+ *   cand_v/cand_i (B, q_len, n_chunks, top_k), cand_c (B, q_len, n_chunks),
+ *   cand_i = pos * id_mul + id_add   (global token id under token-interleaved
+ *   context parallelism: id_mul = cp, id_add = rank).
+ * Page ids outside [0, num_pages) produce -inf scores and MDC_DEV_BAD_INDEX.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const uint8_t* kv_pages;   /* (num_pages, page_bytes) fused pages, 16 B aligned */
+  int32_t num_pages;
+  int32_t page_tokens;       /* 64 or 128 (MXFP4: 128 only)                       */
+  int32_t fmt;               /* MDC_FMT_*                                          */
+  int32_t q_fmt;             /* MDC_Q_*                                            */
+  const void* q;             /* see MDC_Q_*; N = q_len*heads rows per request      */
+  const uint8_t* q_sf;       /* MDC_Q_FP4 only: (B, N*4) atom-ordered scales        */
+  const float* weights;      /* (B, N) head-gate weights                           */
+  const int32_t* block_table;/* (B, max_pages)                                     */
+  int32_t max_pages;
+  const int32_t* seq_lens;   /* (B,) rank-local token counts; NULL = max_pages*page_tokens */
+  float* logits;             /* (B*q_len, logits_stride) or NULL when fused        */
+  int64_t logits_stride;
+  float* cand_v;             /* fused top-k outputs, or NULL                        */
+  int32_t* cand_i;
+  int32_t* cand_c;
+  int32_t top_k;             /* multiple of 32, <= 2048 (fused only)                */
+  int32_t B;
+  int32_t q_len;             /* 1 or 2                                              */
+  int32_t heads;             /* 64                                                  */
+  int32_t blocks_per_chunk;
+  int32_t n_chunks;
+  int32_t window_exclude;    /* reference: 128 (sliding-window tokens skipped)      */
+  int32_t id_mul, id_add;
+  int32_t* status;           /* 8 words or NULL                                     */
+} mdc_logits_params;
+int mdc_logits_fp4_launch(const mdc_logits_params* p, void* stream);
+/* dynamic shared memory the launch above will request (bytes), or <0 */
+int mdc_logits_fp4_smem_bytes(const mdc_logits_params* p);
+
+/* ------------------------------------------------------------------------
+ * Exact top-k over L candidate lists per (b, t); deterministic input-order
+ * emit.  Replaces run_merge_topk, mega_dsa_cp/tiles/merge.py:347-379 (kernel
+ * MergeTopK.kernel, merge.py:147-323).  Total order: logit descending (bit
+ * level, so -0.0 < +0.0), then id ascending (as signed int32 ids >= 0).
+ * dbg (>= 1 word, may be NULL): [0] += 1 per (b,t) whose emitted count
+ * differs from min(total, top_k).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const float* cand_v;    /* (B, q_len, L, maxK) */
+  const int32_t* cand_i;  /* (B, q_len, L, maxK) */
+  const int32_t* cand_c;  /* (B, q_len, L)       */
+  float* out_v;           /* (B, q_len, top_k)   */
+  int32_t* out_i;         /* (B, q_len, top_k)   */
+  int32_t* out_c;         /* (B, q_len)          */
+  int32_t* dbg;
+  int32_t B, q_len, L, maxK, top_k;
+} mdc_merge_topk_params;
+int mdc_merge_topk_launch(const mdc_merge_topk_params* p, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Merge of per-rank (or per-split) normalised attention partials by their
+ * log2-domain LSE.  Replaces run_lse_merge, mega_dsa_cp/tiles/lse_merge.py:175-197
+ * (kernel LseMerge.kernel, lse_merge.py:77-142):
+ *   g = max_i l_i; glse = g + log2(sum_i 2^(l_i-g)); O = sum_i O_i * 2^(l_i-glse);
+ *   all-empty heads give O = 0, glse = -inf.
+ * Partials: acc_o (rows, n_slices_max, H, D) in acc_dtype, acc_lse (rows,
+ * n_slices_max, H) fp32, rows = B*q_len; the first n_slices slices are merged.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* acc_o;
+  const float* acc_lse;
+  void* o;               /* (rows, H, D) in out_dtype */
+  float* lse;            /* (rows, H) or NULL         */
+  int32_t rows, H, D;
+  int32_t n_slices, n_slices_max;
+  int32_t acc_dtype;     /* MDC_DT_F32 | MDC_DT_BF16  */
+  int32_t out_dtype;     /* MDC_DT_F32 | MDC_DT_BF16  */
+} mdc_lse_merge_params;
+int mdc_lse_merge_launch(const mdc_lse_merge_params* p, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Sparse MLA decode attention over a window pool plus a gathered pool.
+ * Replaces run_hca_fp8, mega_dsa_cp/tiles/hca.py:3160-3270 (kernel
+ * HcaFp8Forward.attention_kernel, hca.py:694-1206).
+ *
+ * Row r = b*q_len + t attends to slots [0,128) = kv_win[pt_win[r]] (valid
+ * below win_valid[r]) and slots [128, k_valid[r]) = gathered rows
+ * kv_cmp[id] for id = pt_cmp[r, slot-128] (page_cmp == 1) or entry
+ * (slot-128) % page_cmp of page pt_cmp[r, (slot-128)/page_cmp].  V is the
+ * first d_v columns of K.  attn_sink[h] (-inf = off) adds a zero-valued
+ * logit.  Output is normalised; lse = log2(sum) + scale*log2(e)*max, or
+ * -inf with O = 0 when nothing is valid.
+ *
+ * n_splits > 1 splits the slot range; partials go to `ws_o` (rows, n_splits,
+ * H, d_v) fp32 and `ws_lse` (rows, n_splits, H) and are merged into o / lse
+ * by a second kernel launched by the same call.  Workspace is caller-owned.
+ * fp8_p != 0 rounds the probabilities through e4m3 before P.V, as the
+ * reference kernel does.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;            /* (B, q_len, H, d_qk) kv_dtype                  */
+  const void* kv_win;       /* (pages_win, 128, d_qk) or NULL                */
+  const void* kv_cmp;       /* (pages_cmp, page_cmp, d_qk)                   */
+  const int32_t* pt_win;    /* (rows,) window page per row, or NULL          */
+  const int32_t* pt_cmp;    /* (rows, pt_cols)                               */
+  const int32_t* k_valid;   /* (rows,) includes the 128 window slots         */
+  const int32_t* win_valid; /* (rows,) or NULL (= 0)                         */
+  const float* attn_sink;   /* (H,) or NULL                                  */
+  void* o;                  /* (rows, H, d_v) out_dtype, row stride o_stride */
+  float* lse;               /* (rows, H), row stride lse_stride, or NULL     */
+  int64_t o_stride;         /* elements between consecutive rows of o        */
+  int64_t lse_stride;
+  float* ws_o;              /* split workspace (n_splits > 1)                */
+  float* ws_lse;
+  int32_t B, q_len, H;      /* H multiple of 64                              */
+  int32_t d_qk, d_v;        /* (576,512) or (512,512)                        */
+  int32_t pages_win, pages_cmp, page_cmp, pt_cols;
+  int32_t kv_dtype;         /* MDC_DT_BF16 | MDC_DT_E4M3                     */
+  int32_t out_dtype;        /* MDC_DT_F32 | MDC_DT_BF16                      */
+  int32_t n_splits;
+  int32_t fp8_p;
+  float softmax_scale;
+  float output_scale;
+  int32_t* status;
+} mdc_sparse_mla_params;
+int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* stream);
+int mdc_sparse_mla_smem_bytes(const mdc_sparse_mla_params* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MDC_H_ */

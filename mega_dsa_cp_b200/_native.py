@@ -1,0 +1,127 @@
+"""ctypes binding of libmdc.so (declared in include/mdc.h).
+
+The CUDA library is the product: importing a launcher from here fails loudly
+when libmdc.so is missing; there is no Python or CPU fallback for any kernel.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmdc.so")
+
+ABI_VERSION = 1
+FMT_MXFP4, FMT_NVFP4 = 0, 1
+Q_FP4, Q_BF16 = 0, 1
+DT_F32, DT_BF16, DT_E4M3 = 0, 1, 2
+
+p_void, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+
+
+class MdcError(RuntimeError):
+    pass
+
+
+class LogitsParams(C.Structure):
+    _fields_ = [
+        ("kv_pages", p_void), ("num_pages", i32), ("page_tokens", i32), ("fmt", i32), ("q_fmt", i32),
+        ("q", p_void), ("q_sf", p_void), ("weights", p_void), ("block_table", p_void), ("max_pages", i32),
+        ("seq_lens", p_void), ("logits", p_void), ("logits_stride", i64),
+        ("cand_v", p_void), ("cand_i", p_void), ("cand_c", p_void), ("top_k", i32),
+        ("B", i32), ("q_len", i32), ("heads", i32), ("blocks_per_chunk", i32), ("n_chunks", i32),
+        ("window_exclude", i32), ("id_mul", i32), ("id_add", i32), ("status", p_void),
+    ]
+
+
+class MergeTopkParams(C.Structure):
+    _fields_ = [
+        ("cand_v", p_void), ("cand_i", p_void), ("cand_c", p_void), ("out_v", p_void), ("out_i", p_void),
+        ("out_c", p_void), ("dbg", p_void),
+        ("B", i32), ("q_len", i32), ("L", i32), ("maxK", i32), ("top_k", i32),
+    ]
+
+
+class LseMergeParams(C.Structure):
+    _fields_ = [
+        ("acc_o", p_void), ("acc_lse", p_void), ("o", p_void), ("lse", p_void),
+        ("rows", i32), ("H", i32), ("D", i32), ("n_slices", i32), ("n_slices_max", i32),
+        ("acc_dtype", i32), ("out_dtype", i32),
+    ]
+
+
+class SparseMlaParams(C.Structure):
+    _fields_ = [
+        ("q", p_void), ("kv_win", p_void), ("kv_cmp", p_void), ("pt_win", p_void), ("pt_cmp", p_void),
+        ("k_valid", p_void), ("win_valid", p_void), ("attn_sink", p_void), ("o", p_void), ("lse", p_void),
+        ("o_stride", i64), ("lse_stride", i64), ("ws_o", p_void), ("ws_lse", p_void),
+        ("B", i32), ("q_len", i32), ("H", i32), ("d_qk", i32), ("d_v", i32),
+        ("pages_win", i32), ("pages_cmp", i32), ("page_cmp", i32), ("pt_cols", i32),
+        ("kv_dtype", i32), ("out_dtype", i32), ("n_splits", i32), ("fp8_p", i32),
+        ("softmax_scale", f32), ("output_scale", f32), ("status", p_void),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises MdcError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MdcError(
+                f"{LIB_PATH} is missing: build it with `python -m mega_dsa_cp_b200.build` "
+                "(nvcc, sm_100a); this package has no fallback path")
+        l = C.CDLL(LIB_PATH)
+        l.mdc_abi_version.restype = C.c_int
+        if l.mdc_abi_version() != ABI_VERSION:
+            raise MdcError("libmdc.so ABI version mismatch; rebuild the library")
+        l.mdc_status_string.restype = C.c_char_p
+        l.mdc_status_string.argtypes = [C.c_int]
+        l.mdc_last_cuda_error.restype = C.c_int
+        for name in EXPORTS:
+            fn = getattr(l, name)
+            fn.restype = C.c_int
+        _lib = l
+    return _lib
+
+
+# every symbol include/mdc.h declares (checked by the CPU test-suite)
+EXPORTS = [
+    "mdc_abi_version", "mdc_status_string", "mdc_last_cuda_error", "mdc_kernel_attrs",
+    "mdc_logits_fp4_launch", "mdc_logits_fp4_smem_bytes", "mdc_merge_topk_launch",
+    "mdc_lse_merge_launch", "mdc_sparse_mla_launch", "mdc_sparse_mla_smem_bytes",
+]
+
+
+def check(rc: int, what: str) -> None:
+    if rc < 0:
+        l = lib()
+        msg = l.mdc_status_string(rc).decode()
+        extra = f" (cudaError {l.mdc_last_cuda_error()})" if rc == -5 else ""
+        raise MdcError(f"{what}: {msg}{extra}")
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a torch tensor (None passes NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(stream=None) -> int:
+    """cudaStream_t of `stream` (a torch stream, a raw handle, or None = current)."""
+    if stream is None:
+        import torch
+
+        return torch.cuda.current_stream().cuda_stream
+    if hasattr(stream, "cuda_stream"):
+        return stream.cuda_stream
+    if hasattr(stream, "getPtr"):  # cuda.bindings.driver.CUstream
+        return int(stream)
+    return int(stream)
+
+
+def call(name: str, params: C.Structure, stream=None) -> None:
+    fn = getattr(lib(), name)
+    check(fn(C.byref(params), C.c_void_p(stream_ptr(stream))), name)

@@ -1,0 +1,181 @@
+// Block-wide exact top-k by radix select, shared by the fused local top-k of
+// the indexer tile and by the candidate merge tile.
+//
+// Keys are unsigned integers whose order is the selection order (larger is
+// better): u32 = sortable(logit) when positions break ties, u64 =
+// (sortable(logit) << 32) | ~id for explicit ids.  The select walks the key
+// bytes from the top, one 256-bin histogram per byte over the elements that
+// still match the prefix found so far; lanes of a warp that hit the same bin are
+// combined with match.any before touching shared memory, so a histogram costs
+// one shared atomic per distinct bin per warp instead of one per element.  The
+// emit is deterministic: output slot = number of selected elements at lower
+// positions, computed from warp ballots, never from atomics.
+#pragma once
+
+#include "common.cuh"
+
+namespace mdc {
+
+struct SelectScratch {
+  uint32_t hist[256 + 32];  // 256 bins + one dummy bin per lane for non-matching elements
+  int32_t bnd, c_gt, hist_bnd, total;
+  int32_t wgt[kWarps], weq[kWarps];
+};
+
+template <typename KeyT>
+struct Threshold {
+  KeyT tau;         // selected: key > tau, or key == tau and rank among equals < need_eq
+  int32_t need_eq;
+  int32_t n_sel;    // number of selected elements = min(total valid, k)
+};
+
+// src(pos, valid) -> key.  All threads of the block call this with the same
+// arguments; n_pos is the padded position space, k >= 1.
+template <typename KeyT, typename Src>
+__device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, SelectScratch& sc) {
+  constexpr int NPASS = static_cast<int>(sizeof(KeyT));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int iters = ceil_div(n_pos, kBlockThreads);
+  Threshold<KeyT> th;
+
+  // total number of valid elements
+  int mine = 0;
+  for (int it = 0; it < iters; ++it) {
+    int pos = it * kBlockThreads + tid;
+    bool valid = false;
+    if (pos < n_pos) (void)src(pos, valid);
+    mine += valid ? 1 : 0;
+  }
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  __syncthreads();  // scratch may still be in use by a previous call
+  if (lane == 0) sc.wgt[warp] = mine;
+  __syncthreads();
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) total += sc.wgt[w];
+  if (total <= k) {
+    th.tau = 0;
+    th.need_eq = 0x7fffffff;
+    th.n_sel = total;
+    __syncthreads();
+    return th;
+  }
+
+  KeyT prefix = 0;
+  int remaining = k;
+  bool done = false;
+#pragma unroll 1
+  for (int p = 0; p < NPASS && !done; ++p) {
+    const int shift = 8 * (NPASS - 1 - p);
+    for (int i = tid; i < 256 + 32; i += kBlockThreads) sc.hist[i] = 0;
+    __syncthreads();
+    for (int it = 0; it < iters; ++it) {
+      int pos = it * kBlockThreads + tid;
+      bool valid = false;
+      KeyT key = 0;
+      if (pos < n_pos) key = src(pos, valid);
+      bool hit = valid;
+      if (p > 0) hit = hit && ((key >> (shift + 8)) == (prefix >> (shift + 8)));
+      uint32_t bin = hit ? static_cast<uint32_t>((key >> shift) & 0xff) : 256u + lane;
+      uint32_t peers = __match_any_sync(0xffffffffu, bin);
+      if (hit && lane == __ffs(peers) - 1) atomicAdd(&sc.hist[bin], __popc(peers));
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 255-8l .. 248-8l, scanned from the top
+      uint32_t c[8];
+      int local = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        c[j] = sc.hist[255 - 8 * lane - j];
+        local += c[j];
+      }
+      int tot;
+      int cum = warp_excl_scan(local, lane, &tot);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (cum < remaining && cum + static_cast<int>(c[j]) >= remaining) {
+          sc.bnd = 255 - 8 * lane - j;
+          sc.c_gt = cum;
+          sc.hist_bnd = c[j];
+        }
+        cum += c[j];
+      }
+    }
+    __syncthreads();
+    prefix |= static_cast<KeyT>(sc.bnd) << shift;
+    remaining -= sc.c_gt;
+    if (sc.hist_bnd == remaining) done = true;  // the boundary bin is taken whole
+    __syncthreads();
+  }
+  if (done) {
+    if (prefix == 0) {
+      th.tau = 0;
+      th.need_eq = 0x7fffffff;
+    } else {
+      th.tau = prefix - 1;
+      th.need_eq = 0;
+    }
+  } else {
+    th.tau = prefix;
+    th.need_eq = remaining;
+  }
+  th.n_sel = k;
+  return th;
+}
+
+// Deterministic emit of the selected elements in position order.
+// emit(pos, slot) is called once per selected element; returns the count.
+template <typename KeyT, typename Src, typename Emit>
+__device__ int block_emit_selected(Src src, int n_pos, Threshold<KeyT> th, SelectScratch& sc, Emit emit) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seg = ceil_div(ceil_div(n_pos, kWarps), 32) * 32;
+  const int lo = warp * seg;
+  const int hi = min(n_pos, lo + seg);
+  int gt = 0, eq = 0;
+  for (int base = lo; base < hi; base += 32) {
+    int pos = base + lane;
+    bool valid = false;
+    KeyT key = 0;
+    if (pos < hi) key = src(pos, valid);
+    gt += __popc(__ballot_sync(0xffffffffu, valid && key > th.tau));
+    eq += __popc(__ballot_sync(0xffffffffu, valid && key == th.tau));
+  }
+  __syncthreads();
+  if (lane == 0) {
+    sc.wgt[warp] = gt;
+    sc.weq[warp] = eq;
+  }
+  __syncthreads();
+  int gt_before = 0, eq_before = 0, gt_all = 0, eq_all = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    if (w < warp) {
+      gt_before += sc.wgt[w];
+      eq_before += sc.weq[w];
+    }
+    gt_all += sc.wgt[w];
+    eq_all += sc.weq[w];
+  }
+  int out_run = gt_before + min(eq_before, th.need_eq);
+  int eq_run = eq_before;
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int base = lo; base < hi; base += 32) {
+    int pos = base + lane;
+    bool valid = false;
+    KeyT key = 0;
+    if (pos < hi) key = src(pos, valid);
+    bool g = valid && key > th.tau;
+    bool e = valid && key == th.tau;
+    uint32_t eb = __ballot_sync(0xffffffffu, e);
+    bool take = g || (e && (eq_run + __popc(eb & lt)) < th.need_eq);
+    uint32_t tb = __ballot_sync(0xffffffffu, take);
+    if (take) emit(pos, out_run + __popc(tb & lt));
+    out_run += __popc(tb);
+    eq_run += __popc(eb);
+  }
+  __syncthreads();
+  return gt_all + min(eq_all, th.need_eq);
+}
+
+}  // namespace mdc

@@ -1,0 +1,103 @@
+"""Sparse MLA decode attention: host runners.
+
+`run_hca_fp8` is the drop-in for mega_dsa_cp/tiles/hca.py:3160-3270 of the
+reference (fp8 operands, latent 512, dual pool, sink).  `run_sparse_mla` is
+the same kernel family on bf16 operands with 576 QK / 512 V dims.  Both call
+mdc_sparse_mla_launch (csrc/tile_mla.cuh).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _native as N
+
+H = 128
+D = 512
+_SM_COUNT = 148
+_ws_cache: dict = {}
+
+
+def _workspace(device, rows: int, splits: int, heads: int):
+    key = (device, rows, splits, heads)
+    if key not in _ws_cache:
+        _ws_cache[key] = (
+            torch.empty(rows, splits, heads, D, dtype=torch.float32, device=device),
+            torch.empty(rows, splits, heads, dtype=torch.float32, device=device),
+        )
+    return _ws_cache[key]
+
+
+def pick_splits(rows: int, heads: int, slots: int) -> int:
+    """KV splits so that rows * heads/64 * splits blocks roughly fill the SMs."""
+    blocks = rows * (heads // 64)
+    tiles = max(1, (slots + 63) // 64)
+    return int(max(1, min(16, tiles, _SM_COUNT // max(1, blocks))))
+
+
+def run_sparse_mla(
+    q: torch.Tensor,            # (B, T, H, d_qk) bf16 | float8_e4m3fn
+    kv_win: torch.Tensor | None,   # (pages_win, 128, d_qk)
+    kv_cmp: torch.Tensor,       # (pages_cmp, page_cmp, d_qk)
+    pt_win: torch.Tensor | None,   # (B*T, 1) int32
+    pt_cmp: torch.Tensor,       # (B*T, cols) int32
+    o: torch.Tensor,            # (B, T, H, 512) fp32 | bf16 (row stride free)
+    lse: torch.Tensor | None,   # (B, T, H) fp32
+    k_valid: torch.Tensor,      # (B*T,) int32, counts the 128 window slots
+    win_valid: torch.Tensor | None,
+    attn_sink: torch.Tensor | None,
+    softmax_scale: float,
+    output_scale: float = 1.0,
+    n_splits: int | None = None,
+    fp8_p: bool = False,
+    status: torch.Tensor | None = None,
+    stream=None,
+) -> None:
+    B, T, heads, d_qk = q.shape
+    rows = B * T
+    kv_dt = N.DT_E4M3 if q.dtype == torch.float8_e4m3fn else N.DT_BF16
+    assert kv_cmp.dtype == q.dtype and kv_cmp.is_contiguous() and q.is_contiguous()
+    o2 = o.view(rows, heads, o.shape[-1]) if o.dim() == 4 else o
+    assert o2.stride(2) == 1 and o2.stride(1) == o2.shape[2]
+    if n_splits is None:
+        n_splits = pick_splits(rows, heads, pt_cmp.shape[1] * kv_cmp.shape[1] + 128)
+    contiguous_out = o2.stride(0) == heads * o2.shape[2] and (lse is None or lse.is_contiguous())
+    if not contiguous_out:
+        n_splits = 1
+    ws_o = ws_l = None
+    if n_splits > 1:
+        ws_o, ws_l = _workspace(q.device, rows, n_splits, heads)
+    p = N.SparseMlaParams(
+        q=N.ptr(q), kv_win=N.ptr(kv_win), kv_cmp=N.ptr(kv_cmp), pt_win=N.ptr(pt_win), pt_cmp=N.ptr(pt_cmp),
+        k_valid=N.ptr(k_valid), win_valid=N.ptr(win_valid), attn_sink=N.ptr(attn_sink),
+        o=N.ptr(o), lse=N.ptr(lse), o_stride=o2.stride(0), lse_stride=heads if lse is None else lse.reshape(rows, heads).stride(0),
+        ws_o=N.ptr(ws_o), ws_lse=N.ptr(ws_l),
+        B=B, q_len=T, H=heads, d_qk=d_qk, d_v=D,
+        pages_win=0 if kv_win is None else kv_win.shape[0], pages_cmp=kv_cmp.shape[0],
+        page_cmp=kv_cmp.shape[1], pt_cols=pt_cmp.shape[1],
+        kv_dtype=kv_dt, out_dtype=N.DT_F32 if o.dtype == torch.float32 else N.DT_BF16,
+        n_splits=n_splits, fp8_p=int(fp8_p), softmax_scale=softmax_scale, output_scale=output_scale,
+        status=N.ptr(status),
+    )
+    N.call("mdc_sparse_mla_launch", p, stream)
+
+
+def run_hca_fp8(
+    q, kv_win, kv_cmp, pt_win, pt_cmp, o, lse, k_valid, win_valid, attn_sink,
+    softmax_scale: float, output_scale: float = 1.0,
+    acc_o: torch.Tensor | None = None,    # (B, T, H, 1, D) fp32 partial output
+    acc_lse: torch.Tensor | None = None,  # (B, T, H, 1) fp32
+    dbg: torch.Tensor | None = None,
+    stream=None,
+) -> None:
+    """fp8 dual-pool attention with the reference's argument list; with
+    acc_o/acc_lse the normalised partial and its log2-LSE go there instead of
+    o/lse (the layout a cross-rank LSE merge consumes)."""
+    B, T, heads, _ = q.shape
+    if acc_o is not None:
+        out_o = acc_o.view(B, T, heads, D)
+        out_l = acc_lse.view(B, T, heads)
+    else:
+        out_o, out_l = o, lse
+    run_sparse_mla(q, kv_win, kv_cmp, pt_win, pt_cmp, out_o, out_l, k_valid, win_valid, attn_sink,
+                   softmax_scale, output_scale, fp8_p=True, stream=stream)
