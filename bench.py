@@ -1,0 +1,339 @@
+"""Benchmark of the DSA decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1 runs BASELINE config 2 (indexer logits + exact top-k 2048, B = 32 decode
+queries, context 32768, NVFP4 index cache in 64-token pages, random page
+tables).  One step = one pass of that path over the batch; the metric is decode
+tokens per second (B * q_len / step time).  Prints ONE JSON line (rank 0).
+
+Timing: CUDA events on the launching stream around exactly K steps, after W
+warm-up steps, max over ranks.  The 75.5 MB index cache would fit the 126 MB
+L2, so the steps rotate over several independent copies of the cache (more
+than L2 in total): every step streams its bytes from HBM.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+METRIC = "dsa_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+                for n, v in zip(names, s[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------------
+# config 2 workload
+# ----------------------------------------------------------------------------
+CFG2 = dict(B=32, S=32768, page=64, top_k=2048, q_len=1, copies=4, blocks_per_chunk=128)
+
+
+def cfg2_algorithmic_bytes(c) -> int:
+    """Bytes one logits launch must move: 72 B per (sequence, token) of NVFP4
+    index-K, 4 B per page-table entry, 16640 B of bf16 query + weights per
+    sequence, 8 B per emitted candidate."""
+    B, S, P, K = c["B"], c["S"], c["page"], c["top_k"]
+    n_chunks = (S // P) // c["blocks_per_chunk"]
+    return B * S * 72 + B * (S // P) * 4 + B * 16640 + B * n_chunks * K * 8
+
+
+def build_cfg2_device(c, device, seed=0):
+    """Index caches (one per rotation copy), queries, weights, page tables on the GPU.
+    Values: K ~ N(0,1) quantised to NVFP4, q ~ N(0,1) in bf16, w ~ N(0, 1/64)."""
+    import torch
+    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, S, P = c["B"], c["S"], c["page"]
+    pages_per_seq = S // P
+    pool = B * pages_per_seq
+    caches, tables = [], []
+    for _ in range(c["copies"]):
+        parts = []
+        for _ in range(8):  # quantise in slices to bound temporary memory
+            raw = torch.randn(pool // 8 * P, 128, generator=g, device=device)
+            parts.append(fuse_pages(raw, "nvfp4", P)[0])
+        caches.append(torch.cat(parts))
+        perm = torch.randperm(pool, generator=g, device=device).to(torch.int32)
+        tables.append(perm.reshape(B, pages_per_seq).contiguous())
+    q = torch.randn(B, 64 * c["q_len"], 128, generator=g, device=device).to(torch.bfloat16)
+    w = (torch.randn(B, 64 * c["q_len"], generator=g, device=device) / 64.0).contiguous()
+    return caches, tables, q, w
+
+
+def run_gpu_cfg2(args):
+    import torch
+    from mega_dsa_cp_b200.tiles.logits import run_fp4_paged_mqa_logits
+    from mega_dsa_cp_b200.tiles.merge import run_merge_topk
+
+    c = CFG2
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    caches, tables, q, w = build_cfg2_device(c, dev)
+    B, K, T = c["B"], c["top_k"], c["q_len"]
+    bpc = c["blocks_per_chunk"]
+    n_chunks = (c["S"] // c["page"]) // bpc
+    cv = torch.empty(B, T, n_chunks, K, device=dev)
+    ci = torch.empty(B, T, n_chunks, K, dtype=torch.int32, device=dev)
+    cc = torch.empty(B, T, n_chunks, dtype=torch.int32, device=dev)
+    ov = torch.empty(B, T, K, device=dev)
+    oi = torch.empty(B, T, K, dtype=torch.int32, device=dev)
+    oc = torch.empty(B, T, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+
+    def logits_only(i, qq=q, ww=w):
+        r = i % c["copies"]
+        run_fp4_paged_mqa_logits(caches[r], qq, None, ww, tables[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
+                                 top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
+
+    def step(i, qq=q, ww=w):
+        logits_only(i, qq, ww)
+        run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clk:
+        time.sleep(0.1)
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms_total = ev0.elapsed_time(ev1)
+        # dominant kernel alone (same rotation), for the roofline
+        reps = max(args.steps, 20)
+        for i in range(3):
+            logits_only(i)
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for i in range(reps):
+            logits_only(i)
+        k1.record()
+        torch.cuda.synchronize()
+        ms_logits = k0.elapsed_time(k1) / reps
+        time.sleep(0.1)
+    assert status[0].item() == 0, f"device failure {status.tolist()}"
+    ms_step = ms_total / args.steps
+
+    # end to end: per-step tensors start in pinned host memory (query, gate
+    # weights, page table), the selected ids come back; the index cache is
+    # resident state, like model weights, and is not re-sent.
+    hq = q.cpu().pin_memory()
+    hw = w.cpu().pin_memory()
+    hbt = [t.cpu().pin_memory() for t in tables]
+    dq, dw = torch.empty_like(q), torch.empty_like(w)
+    dbt = [torch.empty_like(t) for t in tables]
+    h_ids = torch.empty(B, T, K, dtype=torch.int32).pin_memory()
+    h_cnt = torch.empty(B, T, dtype=torch.int32).pin_memory()
+
+    def e2e_step(i):
+        r = i % c["copies"]
+        dq.copy_(hq, non_blocking=True)
+        dw.copy_(hw, non_blocking=True)
+        dbt[r].copy_(hbt[r], non_blocking=True)
+        run_fp4_paged_mqa_logits(caches[r], dq, None, dw, dbt[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
+                                 top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
+        run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
+        h_ids.copy_(oi, non_blocking=True)
+        h_cnt.copy_(oc, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    h2d = hq.numel() * 2 + hw.numel() * 4 + hbt[0].numel() * 4
+    d2h = h_ids.numel() * 4 + h_cnt.numel() * 4
+
+    peak, peak_kind = measured_peaks()
+    algo = cfg2_algorithmic_bytes(c)
+    achieved = algo / (ms_logits * 1e-3) / 1e9
+    cpu = None if args.skip_cpu else cpu_baseline_cfg2(sample_seqs=1, reps=3)
+    tokens = B * T
+    line = {
+        "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1 x ue4m3) x bf16 -> f32", "data": "synthetic",
+        "config": {"workload": "cfg2: indexer logits + exact top-k 2048, B=32, ctx 32768, NVFP4 64-token pages, "
+                               "random page tables, bf16 q (64 heads x 128)",
+                   "l2": f"rotating {c['copies']} cache copies ({c['copies'] * 75.5:.0f} MB > 126 MB L2)",
+                   "parallelism": "cp1", "kernels_per_step": 2},
+        "step_us": ms_step * 1e3,
+        "indexer_us": ms_logits * 1e3,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel": "logits_kernel<NVFP4,64,1>", "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES},
+        "cpu_baseline": cpu,
+        "clocks": clk.summary(),
+    }
+    print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one logits launch, from the
+# ncu capture summarised under profiles/ (None until captured)
+NCU_TRAFFIC_BYTES = None
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle port of the same path on the host cores
+# ----------------------------------------------------------------------------
+def cpu_cfg2_once(case, K):
+    import torch
+    from oracle import dsa_oracle as orc
+
+    logits = orc.ref_logits(case["q_deq"], case["w"], case["fused"], case["bt"], 1, fmt="nvfp4", page_tokens=64)
+    return torch.topk(logits, K, dim=-1)
+
+
+def cpu_baseline_cfg2(sample_seqs=1, reps=3):
+    import torch
+    from dsa_inputs import indexer_case
+
+    c = CFG2
+    case = indexer_case(sample_seqs, c["S"], c["page"], "nvfp4", seed=0)
+    cpu_cfg2_once(case, c["top_k"])
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_cfg2_once(case, c["top_k"])
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": sample_seqs / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sample_seqs} of the 32 sequences of cfg2 (ctx 32768, dequant + 64-head logits + top-k 2048) "
+                      f"per step, {reps} timed steps, torch CPU, {os.cpu_count()} host cpus"}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path, as restated in oracle/
+    (the reference is pure Python and is not installed on the bench box)."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from dsa_inputs import indexer_case
+
+    c = CFG2
+    seqs = 2
+    case = indexer_case(seqs, c["S"], c["page"], "nvfp4", seed=0)
+    for _ in range(min(args.warmup, 2)):
+        cpu_cfg2_once(case, c["top_k"])
+    steps = min(args.steps, 20)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_cfg2_once(case, c["top_k"])
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    val = seqs / (ms * 1e-3)
+    cpu = {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+           "sample": f"{seqs} of the 32 sequences of cfg2 per step, {steps} steps"}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2 sample on host cores: indexer logits + top-k 2048, ctx 32768"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--copies", type=int, default=None, help="rotation copies of the index cache (profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    args = ap.parse_args()
+    if args.copies:
+        CFG2["copies"] = args.copies
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_gpu_cfg2(args)
+    else:
+        raise SystemExit("multi-GPU decode step: not wired yet")
+
+
+if __name__ == "__main__":
+    main()

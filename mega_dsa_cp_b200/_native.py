@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmdc.so")
+LIB_PATH = os.environ.get("MDC_LIB_PATH") or os.path.join(_PKG, "libmdc.so")
 
 ABI_VERSION = 1
 FMT_MXFP4, FMT_NVFP4 = 0, 1

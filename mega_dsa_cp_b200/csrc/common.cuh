@@ -13,8 +13,13 @@
 
 namespace mdc {
 
-constexpr int kBlockThreads = 256;   // every tile is written for 8 warps
+constexpr int kBlockThreads = 256;   // every tile's worker part is written for 8 warps (warps 0..7)
 constexpr int kWarps = kBlockThreads / 32;
+constexpr int kLaunchThreads = 320;  // blocks that drive tcgen05 add an issue warp and a copy warp
+
+// Barrier among the 256 worker threads only (warps 0..7); blocks may carry
+// extra service warps that never join it.
+__device__ inline void sync_workers() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
@@ -66,14 +71,19 @@ __device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait on an mbarrier phase.  Returns false once `budget` clock cycles
-// (about a second by default) have passed without the phase completing.
+// Bounded wait on an mbarrier phase.  try_wait itself suspends the thread for a
+// hardware-defined slice, so the loop is not a hot spin; the clock is read only
+// every 64 polls.  Returns false once `budget` clock cycles (about a second by
+// default) have passed without the phase completing.
 __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, long long budget = (1ll << 31)) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < budget) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+  } while (clock64() - t0 < budget);
   return false;
 }
 

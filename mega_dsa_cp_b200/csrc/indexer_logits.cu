@@ -4,8 +4,10 @@
 namespace mdc {
 
 template <int FMT, int PAGE, int T>
-__global__ void __launch_bounds__(kBlockThreads, 1) logits_kernel(const __grid_constant__ mdc_logits_params p) {
-  extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(kLogitsThreads, 1) logits_kernel(const __grid_constant__ mdc_logits_params p) {
+  extern __shared__ unsigned char smem_raw[];
+  // the UMMA operand block wants a 1024-byte aligned base
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   logits_tile<FMT, PAGE, T>(p, blockIdx.y, blockIdx.x, smem);
 }
 
@@ -14,7 +16,7 @@ static int launch_logits(const mdc_logits_params& p, cudaStream_t st, int smem) 
   auto kern = logits_kernel<FMT, PAGE, T>;
   MDC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(p.n_chunks, p.B);
-  kern<<<grid, kBlockThreads, smem, st>>>(p);
+  kern<<<grid, kLogitsThreads, smem, st>>>(p);
   MDC_CUDA_OK(cudaGetLastError());
   return MDC_OK;
 }
@@ -50,7 +52,10 @@ static int logits_smem(const mdc_logits_params* p) {
   if (p->fmt == MDC_FMT_MXFP4) total = logits_smem_layout<MDC_FMT_MXFP4, 128>(p->q_len, ct, fused).total;
   else if (p->page_tokens == 64) total = logits_smem_layout<MDC_FMT_NVFP4, 64>(p->q_len, ct, fused).total;
   else total = logits_smem_layout<MDC_FMT_NVFP4, 128>(p->q_len, ct, fused).total;
-  return total;
+  // slack for the 1024-byte alignment of the base; at least 116 KB so that one
+  // block owns an SM (each block allocates all of the SM's tensor memory)
+  total += 1024;
+  return total < 116 * 1024 ? 116 * 1024 : total;
 }
 
 }  // namespace mdc
@@ -82,3 +87,9 @@ extern "C" int mdc_logits_fp4_launch(const mdc_logits_params* p, void* stream) {
 int mdc_attrs_logits(cudaFuncAttributes* a) {
   return static_cast<int>(cudaFuncGetAttributes(a, mdc::logits_kernel<MDC_FMT_NVFP4, 64, 1>));
 }
+
+#ifdef MDC_TRACE
+extern "C" int mdc_debug_logits_trace(unsigned long long* host_out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mdc::g_logits_trace, sizeof(mdc::g_logits_trace)));
+}
+#endif

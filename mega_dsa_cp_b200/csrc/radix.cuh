@@ -47,9 +47,9 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
     mine += valid ? 1 : 0;
   }
   mine = __reduce_add_sync(0xffffffffu, mine);
-  __syncthreads();  // scratch may still be in use by a previous call
+  sync_workers();  // scratch may still be in use by a previous call
   if (lane == 0) sc.wgt[warp] = mine;
-  __syncthreads();
+  sync_workers();
   int total = 0;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) total += sc.wgt[w];
@@ -57,7 +57,7 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
     th.tau = 0;
     th.need_eq = 0x7fffffff;
     th.n_sel = total;
-    __syncthreads();
+    sync_workers();
     return th;
   }
 
@@ -68,7 +68,7 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
   for (int p = 0; p < NPASS && !done; ++p) {
     const int shift = 8 * (NPASS - 1 - p);
     for (int i = tid; i < 256 + 32; i += kBlockThreads) sc.hist[i] = 0;
-    __syncthreads();
+    sync_workers();
     for (int it = 0; it < iters; ++it) {
       int pos = it * kBlockThreads + tid;
       bool valid = false;
@@ -80,7 +80,7 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
       uint32_t peers = __match_any_sync(0xffffffffu, bin);
       if (hit && lane == __ffs(peers) - 1) atomicAdd(&sc.hist[bin], __popc(peers));
     }
-    __syncthreads();
+    sync_workers();
     if (warp == 0) {
       // lane l owns bins 255-8l .. 248-8l, scanned from the top
       uint32_t c[8];
@@ -102,11 +102,11 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
         cum += c[j];
       }
     }
-    __syncthreads();
+    sync_workers();
     prefix |= static_cast<KeyT>(sc.bnd) << shift;
     remaining -= sc.c_gt;
     if (sc.hist_bnd == remaining) done = true;  // the boundary bin is taken whole
-    __syncthreads();
+    sync_workers();
   }
   if (done) {
     if (prefix == 0) {
@@ -141,12 +141,12 @@ __device__ int block_emit_selected(Src src, int n_pos, Threshold<KeyT> th, Selec
     gt += __popc(__ballot_sync(0xffffffffu, valid && key > th.tau));
     eq += __popc(__ballot_sync(0xffffffffu, valid && key == th.tau));
   }
-  __syncthreads();
+  sync_workers();
   if (lane == 0) {
     sc.wgt[warp] = gt;
     sc.weq[warp] = eq;
   }
-  __syncthreads();
+  sync_workers();
   int gt_before = 0, eq_before = 0, gt_all = 0, eq_all = 0;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
@@ -174,7 +174,7 @@ __device__ int block_emit_selected(Src src, int n_pos, Threshold<KeyT> th, Selec
     out_run += __popc(tb);
     eq_run += __popc(eb);
   }
-  __syncthreads();
+  sync_workers();
   return gt_all + min(eq_all, th.need_eq);
 }
 

@@ -26,12 +26,12 @@ __device__ inline void merge_topk_tile(const mdc_merge_topk_params& p, int row, 
   const int64_t base = static_cast<int64_t>(row) * L * maxK;
   const float* cv = p.cand_v + base;
   const int32_t* ci = p.cand_i + base;
-  __syncthreads();
+  sync_workers();
   for (int l = tid; l < L; l += kBlockThreads) {
     int c = p.cand_c[static_cast<int64_t>(row) * L + l];
     sm.cnt[l] = max(0, min(c, maxK));
   }
-  __syncthreads();
+  sync_workers();
   auto src = [&](int pos, bool& valid) -> unsigned long long {
     const int l = pos / maxK, j = pos - l * maxK;
     valid = j < sm.cnt[l];
