@@ -211,6 +211,94 @@ typedef struct {
 int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* stream);
 int mdc_sparse_mla_smem_bytes(const mdc_sparse_mla_params* p);
 
+
+/* ------------------------------------------------------------------------
+ * Event / comm / scheduler device layer and the persistent decode megakernel.
+ *
+ * mdc_event_set replaces the device view EventSet (mega_dsa_cp/events/core.py:40-62):
+ * 128-byte cells of u64 counters, `offsets[r]` = byte offset of rank r's cells
+ * from `base`.  mdc_peer_buffer replaces PeerBuffer (comm/device.py:11-44).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  void* base;
+  const int64_t* offsets; /* device, [world] */
+  int32_t my_rank;
+  int32_t world;
+} mdc_event_set;
+
+typedef struct {
+  void* base;
+  const int64_t* offsets; /* device, [world] */
+  int32_t my_rank;
+  int32_t world;
+  int64_t mc_base;        /* NVLS multicast address or 0 */
+} mdc_peer_buffer;
+
+/* task op codes understood by mdc_megakernel_launch */
+#define MDC_OP_NOP 0
+#define MDC_OP_LOGITS 1     /* c0 = b, c1 = chunk                                  */
+#define MDC_OP_MERGE_L1 2   /* c0 = b: chunk lists -> local top-k -> every rank    */
+#define MDC_OP_MERGE_L2 3   /* c0 = b: cp lists -> global top-k + local gather list */
+#define MDC_OP_ATTN 4       /* c0 = b, c1 = 2*head block + output-column half: partial -> owner inbox */
+#define MDC_OP_LSE_MERGE 5  /* c0 = b (owned): inbox slices -> output              */
+#define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
+#define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
+#define MDC_OP_PUSH 18      /* c1 = dst rank, c2 = slot: bulk push a pattern (test op) */
+#define MDC_OP_VERIFY 19    /* c1 = src rank, c2 = slot: check a pushed pattern (test op) */
+
+/* One decode layer-step of context-parallel sparse attention, one query token
+ * per sequence (the composition planned in docs/phase1.4-comm-tasks.md:37-117
+ * of the reference).  Rank r holds tokens t with t % cp == r at local index
+ * t / cp.  All buffers are per rank; the arena regions are per phase.
+ *   cand region : (B, cp, cand_slice) with cand_slice = top_k*8 + 16 bytes:
+ *                 [top_k f32 logits][top_k i32 global ids][i32 count, pad]
+ *   inbox region: (B_owned, cp, H*512*2 + H*4) bytes, owner(b) = b % cp,
+ *                 owned index b / cp: [H x 512 bf16 partial O][H f32 log2-LSE]  */
+typedef struct {
+  int32_t cp, rank, B, top_k, H;
+  int32_t n_chunks;             /* chunks per sequence in `logits`             */
+  int32_t kv_seq_stride;        /* KV pool row of local token l of sequence b = b*kv_seq_stride + l */
+  int32_t reserved0;
+  mdc_logits_params logits;     /* fused mode; cand_* = chunk candidate scratch */
+  mdc_sparse_mla_params mla;    /* local KV pool; pt_cmp/k_valid = local gather list written by MERGE_L2 */
+  int64_t cand_off, inbox_off;  /* byte offsets of the regions inside one phase */
+  int64_t phase_bytes;          /* arena bytes per phase                         */
+  int32_t phases;
+  float* sel_v;                 /* (B, top_k) merged logits                      */
+  int32_t* sel_i;               /* (B, top_k) global ids, identical on every rank */
+  int32_t* sel_c;               /* (B,)                                          */
+  void* out;                    /* (B, H, 512) merged attention output (owned rows only) */
+  float* out_lse;               /* (B, H)                                        */
+  int32_t out_dtype;            /* MDC_DT_F32 | MDC_DT_BF16                      */
+} mdc_layer_params;
+
+/* Persistent kernel: block i walks queue row i (format of
+ * mega_dsa_cp/schedule/codegen.py:3-11), executes each task's inline waits,
+ * dispatches on the op code, executes its notifies.  Replaces the scheduler
+ * device loop of schedule/device.py:35-129 and the skeleton kernel of
+ * tests/test_skeleton_cp2.py:144-240.  n_ctas must not exceed the number of
+ * blocks that can be co-resident (one per SM): tasks wait on each other. */
+typedef struct {
+  const int32_t* queue;        /* (n_ctas, row_words) */
+  int32_t row_words, n_ctas;
+  const uint64_t* scalars;     /* [0] = phase, [1..] dynamic extents */
+  const int32_t* arity;        /* per event: notifies per phase into this rank's cell */
+  const int32_t* scopes;       /* per event: 0 local, 1 sys */
+  int32_t n_events;
+  mdc_event_set events;
+  mdc_peer_buffer arena;
+  int64_t wait_budget_ns;      /* every event wait gives up after this long */
+  int32_t* status;             /* 8 words, see top of file */
+  int32_t* log;                /* [0] = entries used, then entries; or NULL */
+  int32_t log_cap;
+  int64_t test_off;            /* arena offset of the test region (PUSH / VERIFY) */
+  int32_t test_slot_bytes;
+  mdc_layer_params layer;
+} mdc_mega_params;
+int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
+int mdc_megakernel_smem_bytes(void);
+int mdc_megakernel_threads(void);
+
 #ifdef __cplusplus
 }
 #endif

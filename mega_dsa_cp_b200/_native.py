@@ -63,6 +63,38 @@ class SparseMlaParams(C.Structure):
     ]
 
 
+class EventSetC(C.Structure):
+    _fields_ = [("base", p_void), ("offsets", p_void), ("my_rank", i32), ("world", i32)]
+
+
+class PeerBufferC(C.Structure):
+    _fields_ = [("base", p_void), ("offsets", p_void), ("my_rank", i32), ("world", i32), ("mc_base", i64)]
+
+
+class LayerParams(C.Structure):
+    _fields_ = [
+        ("cp", i32), ("rank", i32), ("B", i32), ("top_k", i32), ("H", i32), ("n_chunks", i32),
+        ("kv_seq_stride", i32), ("reserved0", i32),
+        ("logits", LogitsParams), ("mla", SparseMlaParams),
+        ("cand_off", i64), ("inbox_off", i64), ("phase_bytes", i64), ("phases", i32),
+        ("sel_v", p_void), ("sel_i", p_void), ("sel_c", p_void), ("out", p_void), ("out_lse", p_void),
+        ("out_dtype", i32),
+    ]
+
+
+class MegaParams(C.Structure):
+    _fields_ = [
+        ("queue", p_void), ("row_words", i32), ("n_ctas", i32), ("scalars", p_void), ("arity", p_void),
+        ("scopes", p_void), ("n_events", i32), ("events", EventSetC), ("arena", PeerBufferC),
+        ("wait_budget_ns", i64), ("status", p_void), ("log", p_void), ("log_cap", i32),
+        ("test_off", i64), ("test_slot_bytes", i32), ("layer", LayerParams),
+    ]
+
+
+OP_NOP, OP_LOGITS, OP_MERGE_L1, OP_MERGE_L2, OP_ATTN, OP_LSE_MERGE = 0, 1, 2, 3, 4, 5
+OP_SLEEP, OP_LOG, OP_PUSH, OP_VERIFY = 16, 17, 18, 19
+DEV_WAIT_TIMEOUT, DEV_COPY_TIMEOUT, DEV_BAD_INDEX, DEV_BAD_OP = 1, 2, 3, 4
+
 _lib = None
 
 
@@ -93,6 +125,7 @@ EXPORTS = [
     "mdc_abi_version", "mdc_status_string", "mdc_last_cuda_error", "mdc_kernel_attrs",
     "mdc_logits_fp4_launch", "mdc_logits_fp4_smem_bytes", "mdc_merge_topk_launch",
     "mdc_lse_merge_launch", "mdc_sparse_mla_launch", "mdc_sparse_mla_smem_bytes",
+    "mdc_megakernel_launch", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
 ]
 
 

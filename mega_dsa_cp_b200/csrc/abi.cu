@@ -24,6 +24,7 @@ int mdc_attrs_logits(cudaFuncAttributes* a);
 int mdc_attrs_merge_topk(cudaFuncAttributes* a);
 int mdc_attrs_lse_merge(cudaFuncAttributes* a);
 int mdc_attrs_sparse_mla(cudaFuncAttributes* a);
+int mdc_attrs_megakernel(cudaFuncAttributes* a);
 
 extern "C" int mdc_kernel_attrs(int kernel_id, int* regs, int* static_smem, int* max_dynamic_smem) {
   cudaFuncAttributes a;
@@ -33,6 +34,7 @@ extern "C" int mdc_kernel_attrs(int kernel_id, int* regs, int* static_smem, int*
     case MDC_K_MERGE_TOPK: e = mdc_attrs_merge_topk(&a); break;
     case MDC_K_LSE_MERGE: e = mdc_attrs_lse_merge(&a); break;
     case MDC_K_SPARSE_MLA: e = mdc_attrs_sparse_mla(&a); break;
+    case MDC_K_MEGAKERNEL: e = mdc_attrs_megakernel(&a); break;
     default: return MDC_ERR_BAD_FORMAT;
   }
   if (e != 0) {

@@ -1,0 +1,334 @@
+// Persistent decode megakernel: one block per SM walks its static task queue;
+// every task waits on its events, runs one tile (indexer logits, candidate
+// merges, sparse attention, LSE merge, or a test op) and posts its notifies.
+// Cross-rank payload travels by direct stores / bulk copies into the peers'
+// symmetric arena, followed by a system-scope release notify.
+//
+// Block shape: 15 warps.  Warps 0..7 are the workers every tile is written
+// for; the indexer tile additionally uses warps 8..14 (gate, issue, copy).
+// Blocks wait on each other, so the grid must be co-resident (<= one block per
+// SM; the launcher checks it).  Every wait has a time budget; a block that
+// runs out records the event in the status block, which all blocks check at
+// each task boundary, and the grid drains.
+#include "comm.cuh"
+#include "events.cuh"
+#include "sched.cuh"
+#include "tile_logits.cuh"
+#include "tile_lse_merge.cuh"
+#include "tile_merge.cuh"
+#include "tile_mla.cuh"
+
+namespace mdc {
+
+constexpr int kMegaThreads = kLogitsThreads;
+constexpr int kStagedWords = 128;  // queue rows up to this length are staged in shared memory
+constexpr int kMegaTileSmem = MlaSmem<576>::kTotal;  // the largest tile
+
+struct MegaShared {
+  int32_t row[kStagedWords];
+  int32_t fail;
+};
+
+__device__ inline int64_t phase_offset(const mdc_mega_params& p, unsigned long long phase) {
+  return static_cast<int64_t>(phase % static_cast<unsigned long long>(max(p.layer.phases, 1))) * p.layer.phase_bytes;
+}
+__device__ inline int cand_slice_bytes(const mdc_layer_params& L) { return L.top_k * 8 + 16; }
+__device__ inline int inbox_slice_bytes(const mdc_layer_params& L) { return L.H * kMlaDv * 2 + L.H * 4; }
+
+// Ordered compaction by the 256 workers: keeps ids[i] (i < n) with
+// ids[i] % cp == rank and writes row_base + ids[i] / cp to out in input order.  Returns the count.
+__device__ inline int compact_local_ids(const int32_t* ids, int n, int cp, int rank, int row_base, int32_t* out,
+                                        int out_cap, SelectScratch& sc) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seg = ceil_div(ceil_div(n, kWarps), 32) * 32;
+  const int lo = warp * seg, hi = min(n, lo + seg);
+  int cnt = 0;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool keep = i < hi && (ids[i] % cp) == rank;
+    cnt += __popc(__ballot_sync(0xffffffffu, keep));
+  }
+  sync_workers();
+  if (lane == 0) sc.wgt[warp] = cnt;
+  sync_workers();
+  int before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    if (w < warp) before += sc.wgt[w];
+    total += sc.wgt[w];
+  }
+  const uint32_t lt = (1u << lane) - 1u;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const int id = i < hi ? ids[i] : 0;
+    const bool keep = i < hi && (id % cp) == rank;
+    const uint32_t m = __ballot_sync(0xffffffffu, keep);
+    const int slot = before + __popc(m & lt);
+    if (keep && slot < out_cap) out[slot] = row_base + id / cp;
+    before += __popc(m);
+  }
+  sync_workers();
+  return min(total, out_cap);
+}
+
+// ------------------------------------------------------------------ layer ops
+template <int FMT, int PAGE>
+__device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned char* smem) {
+  logits_tile<FMT, PAGE, 1>(p.layer.logits, b, chunk, smem);
+}
+
+// chunk candidate lists of sequence b -> this rank's top-k, written into the
+// own slice of the candidate region and copied to every peer's arena
+__device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+  const mdc_layer_params& L = p.layer;
+  MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
+  const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
+                         p.arena.mc_base};
+  const int K = L.top_k, C = L.n_chunks;
+  MergeLists ls;
+  ls.v = L.logits.cand_v + static_cast<int64_t>(b) * C * K;
+  ls.i = L.logits.cand_i + static_cast<int64_t>(b) * C * K;
+  ls.c = L.logits.cand_c + static_cast<int64_t>(b) * C;
+  ls.stride = K;
+  ls.c_stride = 1;
+  const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
+  unsigned char* slice = arena.local_ptr(off);
+  merge_lists_tile<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
+                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm);
+  if (L.cp > 1) {
+    __threadfence();
+    sync_workers();
+    for (int dst = 0; dst < L.cp; ++dst) {
+      if (dst != L.rank) copy_to_peer(arena.peer_ptr(off, dst), slice, cand_slice_bytes(L));
+    }
+  }
+}
+
+// cp candidate lists of sequence b (one per rank, in the own arena) -> global
+// top-k (identical on every rank) and this rank's gather list for attention
+template <bool SYS>
+__device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+  const mdc_layer_params& L = p.layer;
+  MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
+  const int K = L.top_k;
+  const int64_t off = phase_offset(p, phase) + L.cand_off + static_cast<int64_t>(b) * L.cp * cand_slice_bytes(L);
+  const unsigned char* first = static_cast<const unsigned char*>(p.arena.base) + off;
+  MergeLists ls;
+  ls.v = reinterpret_cast<const float*>(first);
+  ls.i = reinterpret_cast<const int32_t*>(first + K * 4);
+  ls.c = reinterpret_cast<const int32_t*>(first + K * 8);
+  ls.stride = cand_slice_bytes(L) / 4;
+  ls.c_stride = cand_slice_bytes(L) / 4;
+  int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
+  const int n = merge_lists_tile<SYS>(ls, L.cp, K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm);
+  __threadfence();
+  sync_workers();
+  int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
+  const int mine = compact_local_ids(sel_i, n, L.cp, L.rank, b * L.kv_seq_stride, pt, L.mla.pt_cols, sm.sel);
+  if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
+}
+
+// attention of 64 heads of sequence b over this rank's share of the selection;
+// the normalised partial (bf16) and its log2-LSE go straight into the owner's inbox
+__device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, unsigned long long phase, unsigned char* smem) {
+  const int hb = hbv >> 1, dv0 = (hbv & 1) * 256;  // task = 64 heads x 256 output columns
+  const mdc_layer_params& L = p.layer;
+  const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
+                         p.arena.mc_base};
+  const int owner = b % L.cp;
+  const int64_t off = phase_offset(p, phase) + L.inbox_off +
+                      (static_cast<int64_t>(b / L.cp) * L.cp + L.rank) * inbox_slice_bytes(L);
+  unsigned char* slot = arena.peer_ptr(off, owner);
+  float* lse_row = reinterpret_cast<float*>(slot + static_cast<int64_t>(L.H) * kMlaDv * 2);
+  if (L.mla.d_qk == 576 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
+  else if (L.mla.d_qk == 512 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
+  else if (L.mla.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
+  else mla_tile<512, MDC_DT_E4M3, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
+}
+
+// owner of sequence b: cp inbox slices -> merged output
+template <bool SYS>
+__device__ inline void op_lse_merge(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+  const mdc_layer_params& L = p.layer;
+  const int64_t off = phase_offset(p, phase) + L.inbox_off + static_cast<int64_t>(b / L.cp) * L.cp * inbox_slice_bytes(L);
+  LseSrc src;
+  src.o = static_cast<const unsigned char*>(p.arena.base) + off;
+  src.lse = reinterpret_cast<const float*>(src.o + static_cast<int64_t>(L.H) * kMlaDv * 2);
+  src.o_stride = inbox_slice_bytes(L);
+  src.lse_stride = inbox_slice_bytes(L) / 4;
+  const int osz = (L.out_dtype == MDC_DT_F32) ? 4 : 2;
+  lse_merge_rows<SYS>(src, L.cp, L.H, kMlaDv, MDC_DT_BF16, L.out_dtype,
+                      static_cast<unsigned char*>(L.out) + static_cast<int64_t>(b) * L.H * kMlaDv * osz,
+                      L.out_lse ? L.out_lse + static_cast<int64_t>(b) * L.H : nullptr, 0, L.H,
+                      reinterpret_cast<float*>(smem));
+}
+
+// ------------------------------------------------------------------ test ops
+__device__ inline uint32_t test_pattern(int src_rank, int slot, unsigned long long phase, int i) {
+  return 0x9e3779b9u * static_cast<uint32_t>(i + 1) + static_cast<uint32_t>(src_rank) * 0x01000193u +
+         static_cast<uint32_t>(slot) * 7919u + static_cast<uint32_t>(phase) * 104729u;
+}
+// stage a pattern in shared memory and bulk-push it into slot (my rank, slot) of rank dst
+__device__ inline void op_push(const mdc_mega_params& p, int dst, int slot, unsigned long long phase, unsigned char* smem) {
+  const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
+                         p.arena.mc_base};
+  uint32_t* stage = reinterpret_cast<uint32_t*>(smem);
+  const int words = p.test_slot_bytes / 4;
+  for (int i = threadIdx.x; i < words; i += kBlockThreads) stage[i] = test_pattern(arena.my_rank, slot, phase, i);
+  fence_proxy_async_smem();
+  sync_workers();
+  if (threadIdx.x == 0) {
+    const int64_t off = p.test_off + (static_cast<int64_t>(slot) * arena.world + arena.my_rank) * p.test_slot_bytes;
+    push_start(arena.peer_ptr(off, dst), stage, p.test_slot_bytes);
+    push_finish();
+  }
+}
+__device__ inline void op_verify(const mdc_mega_params& p, int src_rank, int slot, unsigned long long phase) {
+  const int words = p.test_slot_bytes / 4;
+  const int64_t off = p.test_off + (static_cast<int64_t>(slot) * p.arena.world + src_rank) * p.test_slot_bytes;
+  const float* data = reinterpret_cast<const float*>(static_cast<const unsigned char*>(p.arena.base) + off);
+  for (int i = threadIdx.x; i < words; i += kBlockThreads) {
+    const uint32_t got = __float_as_uint(ld_sys_f32(data + i));
+    if (got != test_pattern(src_rank, slot, phase, i)) report_failure(p.status, MDC_DEV_BAD_INDEX, slot, i, got, 0);
+  }
+}
+
+}  // namespace mdc
+
+namespace mdc {
+
+__global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_constant__ mdc_mega_params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ MegaShared sh;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool worker = warp < kWarps;
+
+  const int32_t* row_g = p.queue + static_cast<int64_t>(blockIdx.x) * p.row_words;
+  const bool staged = p.row_words <= kStagedWords;
+  if (staged) {
+    for (int i = tid; i < p.row_words; i += kMegaThreads) sh.row[i] = row_g[i];
+  }
+  if (tid == 0) sh.fail = 0;
+  __syncthreads();
+
+  Cursor cur;
+  cur.row = staged ? sh.row : row_g;
+  cur.scalars = reinterpret_cast<const unsigned long long*>(p.scalars);
+  cur.arity = p.arity;
+  cur.scopes = p.scopes;
+  cur.phase = cur.scalars[0];
+  const EventSet ev{static_cast<unsigned char*>(p.events.base), p.events.offsets, p.events.my_rank, p.events.world};
+  const mdc_layer_params& L = p.layer;
+
+  for (TaskInfo t = cur.read(0); t.valid(); t = cur.advance(t)) {
+    // ---- waits: thread 0 polls, the barrier publishes
+    if (tid == 0) {
+      if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) sh.fail = 1;
+      for (int i = 0; i < t.n_waits && !sh.fail; ++i) {
+        const int e = cur.wait_event(t, i);
+        unsigned long long seen = 0;
+        const bool bad_id = e < 0 || e >= p.n_events;
+        if (bad_id || !ev.poll_1t(e, cur.target(e), cur.scopes[e] != 0, p.wait_budget_ns, &seen)) {
+          report_failure(p.status, bad_id ? MDC_DEV_BAD_OP : MDC_DEV_WAIT_TIMEOUT, e, t.op, seen, bad_id ? 0 : cur.target(e));
+          sh.fail = 1;
+        }
+      }
+    }
+    __syncthreads();
+    if (sh.fail) break;
+
+    // ---- the task body
+    switch (t.op) {
+      case MDC_OP_NOP:
+        break;
+      case MDC_OP_LOGITS:
+        if (L.logits.fmt == MDC_FMT_MXFP4) op_logits<MDC_FMT_MXFP4, 128>(p, t.c0, t.c1, smem);
+        else if (L.logits.page_tokens == 64) op_logits<MDC_FMT_NVFP4, 64>(p, t.c0, t.c1, smem);
+        else op_logits<MDC_FMT_NVFP4, 128>(p, t.c0, t.c1, smem);
+        break;
+      case MDC_OP_MERGE_L1:
+        if (worker) op_merge_l1(p, t.c0, cur.phase, smem);
+        break;
+      case MDC_OP_MERGE_L2:
+        if (worker) {
+          if (L.cp > 1) op_merge_l2<true>(p, t.c0, cur.phase, smem);
+          else op_merge_l2<false>(p, t.c0, cur.phase, smem);
+        }
+        break;
+      case MDC_OP_ATTN:
+        if (worker) op_attn(p, t.c0, t.c1, cur.phase, smem);
+        break;
+      case MDC_OP_LSE_MERGE:
+        if (worker) {
+          if (L.cp > 1) op_lse_merge<true>(p, t.c0, cur.phase, smem);
+          else op_lse_merge<false>(p, t.c0, cur.phase, smem);
+        }
+        break;
+      case MDC_OP_SLEEP:
+        if (tid == 0) {
+          const unsigned long long t0 = global_timer_ns();
+          const unsigned long long want = static_cast<unsigned long long>(min(max(t.c1, 0), 100000000));
+          while (global_timer_ns() - t0 < want) nanosleep(256);
+        }
+        break;
+      case MDC_OP_LOG:
+        if (tid == 0 && p.log) {
+          const int slot = atomicAdd(p.log, 1);
+          if (slot + 1 < p.log_cap) p.log[slot + 1] = t.c0;
+          __threadfence();
+        }
+        break;
+      case MDC_OP_PUSH:
+        if (worker) op_push(p, t.c1, t.c2, cur.phase, smem);
+        break;
+      case MDC_OP_VERIFY:
+        if (worker) op_verify(p, t.c1, t.c2, cur.phase);
+        break;
+      default:
+        if (tid == 0) report_failure(p.status, MDC_DEV_BAD_OP, t.op, t.pos, 0, 0);
+        break;
+    }
+
+    // ---- notifies: everything this block wrote is released first
+    if (t.n_notifies > 0) {
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0) {
+        for (int i = 0; i < t.n_notifies; ++i) {
+          const int w = cur.notify_word(t, i);
+          const int e = w >> 8, dst = w & 0xFF;
+          if (e >= 0 && e < p.n_events && dst < ev.world) ev.notify_1t(e, dst);
+          else report_failure(p.status, MDC_DEV_BAD_OP, e, dst, 0, 0);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace mdc
+
+extern "C" int mdc_megakernel_smem_bytes(void) { return mdc::kMegaTileSmem + 1024; }
+extern "C" int mdc_megakernel_threads(void) { return mdc::kMegaThreads; }
+
+int mdc_attrs_megakernel(cudaFuncAttributes* a) { return static_cast<int>(cudaFuncGetAttributes(a, mdc::mega_kernel)); }
+
+extern "C" int mdc_megakernel_launch(const mdc_mega_params* p, void* stream) {
+  using namespace mdc;
+  if (!p || !p->queue || !p->scalars || !p->arity || !p->scopes || !p->events.base || !p->events.offsets)
+    return MDC_ERR_NULL;
+  if (p->n_ctas < 1 || p->row_words < 1 || p->n_events < 0) return MDC_ERR_BAD_SHAPE;
+  if (p->wait_budget_ns <= 0) return MDC_ERR_BAD_SHAPE;
+  const int smem = mdc_megakernel_smem_bytes();
+  MDC_CUDA_OK(cudaFuncSetAttribute(mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  // the blocks wait on each other: all of them must be resident at once
+  int dev = 0, sms = 0, per_sm = 0;
+  MDC_CUDA_OK(cudaGetDevice(&dev));
+  MDC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  MDC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mega_kernel, kMegaThreads, smem));
+  if (per_sm < 1 || p->n_ctas > sms * per_sm) return MDC_ERR_TOO_LARGE;
+  mega_kernel<<<p->n_ctas, kMegaThreads, smem, static_cast<cudaStream_t>(stream)>>>(*p);
+  MDC_CUDA_OK(cudaGetLastError());
+  return MDC_OK;
+}

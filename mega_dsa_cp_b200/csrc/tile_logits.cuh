@@ -71,8 +71,8 @@ constexpr int kTileTok = 128;    // tokens per pipeline stage (= UMMA M)
 constexpr int kRawStages = 8;    // raw page ring
 constexpr int kAStages = 4;      // decoded-A ring in tensor memory
 constexpr int kTmemCols = 512;
-constexpr int kLogitsThreads = 448;  // 8 decode + 4 gate + issue + copy warps
-constexpr int kGateWarp0 = 8, kIssueWarp = 12, kCopyWarp = 13;
+constexpr int kLogitsThreads = 480;  // 8 decode + 4 gate + 2 issue + 1 copy warps
+constexpr int kGateWarp0 = 8, kIssueWarp = 12, kIssueWarps = 2, kCopyWarp = 14;
 
 template <int FMT, int PAGE>
 struct IdxPage {
@@ -189,7 +189,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   // accumulator ring and MMA interleave: dependent MMAs on one accumulator are
   // latency bound at N = 64, so two stages are issued interleaved when q_len = 1
   constexpr int kAccStages = (T == 1) ? 4 : 2;
-  constexpr int kGroup = 1;
   constexpr uint32_t kAccBase = 0, kABase = kAccStages * N;  // tensor-memory columns
   static_assert(kABase + kAStages * 64 <= kTmemCols, "tensor memory over-subscribed");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -233,7 +232,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       mbar_init(&a_full[s], 8);
       mbar_init(&a_empty[s], 1);
     }
-    for (int s = 0; s < kAccStages; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 4);
     }
@@ -294,41 +293,31 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         MDC_TRACE_AT(0, tile, 1);
       }
     }
-  } else if (warp == kIssueWarp) {
-    // ---------------- issue warp
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma::idesc_f16(kTileTok, N, 0);
-      const uint32_t qb_u = smem_u32(qb);
-      uint64_t bdesc[8];
+  } else if (warp >= kIssueWarp && warp < kIssueWarp + kIssueWarps) {
+    // ---------------- issue warps (tiles are dealt round-robin to them): all lanes walk the loop together, one elected
+    // lane issues (the tensor-core instructions take warp-uniform operands)
+    constexpr uint32_t idesc = umma::idesc_f16(kTileTok, N, 0);
+    const uint32_t qb_u = smem_u32(qb);
+    uint64_t bdesc[8];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) bdesc[kk] = umma::smem_desc_sw128(qb_u + (kk >> 2) * (N * 128) + (kk & 3) * 32);
-      bool dead = false;
-      for (int t0 = 0; t0 < n_tiles && !*abort_flag && !dead; t0 += kGroup) {
-        const int g_n = min(kGroup, n_tiles - t0);
-        for (int u = 0; u < g_n; ++u) {
-          const int tile = t0 + u;
-          if (!mbar_wait(&a_full[tile % kAStages], (tile / kAStages) & 1)) {
-            give_up(1, tile);
-            dead = true;
-            break;
-          }
-          if (tile >= kAccStages && !mbar_wait(&acc_empty[tile % kAccStages], ((tile / kAccStages) - 1) & 1)) {
-            give_up(2, tile);
-            dead = true;
-            break;
-          }
-        }
-        if (dead) break;
-        umma::fence_after_sync();
-        MDC_TRACE_AT(2, t0, 0);
-        umma::mma_f16_ts_x8(tmem + kAccBase + (t0 % kAccStages) * N, tmem + kABase + (t0 % kAStages) * 64, bdesc, idesc);
-        for (int u = 0; u < g_n; ++u) {
-          const int tile = t0 + u;
-          umma::commit(&a_empty[tile % kAStages]);
-          umma::commit(&acc_full[tile % kAccStages]);
-        }
-        MDC_TRACE_AT(2, t0, 1);
+    for (int kk = 0; kk < 8; ++kk) bdesc[kk] = umma::smem_desc_sw128(qb_u + (kk >> 2) * (N * 128) + (kk & 3) * 32);
+    for (int tile = warp - kIssueWarp; tile < n_tiles && !*abort_flag; tile += kIssueWarps) {
+      const int a = tile % kAStages, c = tile % kAccStages;
+      bool ok = mbar_wait(&a_full[a], (tile / kAStages) & 1);
+      if (ok && tile >= kAccStages) ok = mbar_wait(&acc_empty[c], ((tile / kAccStages) - 1) & 1);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) give_up(1, tile);
+        break;
       }
+      umma::fence_after_sync();
+      if (umma::elect_one()) {
+        MDC_TRACE_AT(2, tile, 0);
+        umma::mma_f16_ts_x8(tmem + kAccBase + c * N, tmem + kABase + a * 64, bdesc, idesc);
+        umma::commit(&a_empty[a]);
+        umma::commit(&acc_full[c]);
+        MDC_TRACE_AT(2, tile, 1);
+      }
+      __syncwarp();
     }
   } else if (warp < kWarps) {
     // ---------------- decode warps: thread = half a token row of the stage
@@ -463,6 +452,9 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   umma::fence_after_sync();
   const bool failed = *abort_flag != 0;
   if (warp == kIssueWarp) umma::tmem_dealloc(tmem, kTmemCols);
+  if (tid == 0) {  // the shared memory is reused by the next task of a persistent block
+    for (int i = 0; i < 2 * kRawStages + 2 * kAStages + 2 * 4; ++i) mbar_inval(raw_full + i);
+  }
   if (warp >= kWarps || failed) return;
 
   if (fused) {

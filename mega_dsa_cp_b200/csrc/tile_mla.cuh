@@ -31,7 +31,7 @@ struct MlaSmem {
   static constexpr int kK1 = kK0 + kMlaTile * kRowB;
   static constexpr int kP = kK1 + kMlaTile * kRowB;
   static constexpr int kStat = kP + kMlaHeads * kMlaTile * 2;       // 2 x 64 floats max, 2 x 64 sum
-  static constexpr int kValid = kStat + 4 * 64 * 4;                 // 2 x 64 ints
+  static constexpr int kValid = kStat + 2 * 64 * 4;                 // 2 x 64 ints (the sums reuse the max slots)
   static constexpr int kTotal = kValid + 2 * 64 * 4;
 };
 
@@ -141,9 +141,16 @@ __device__ inline void mla_load_tile(const mdc_sparse_mla_params& p, int r, int 
 }
 
 // r = b*q_len + t, hb = head block, split / n_splits = slice of the slot range.
-template <int DQK, int KVDT>
+// o_row / lse_row, when given, replace p.o / p.lse for this row: they point at
+// the (H, d_v) block and the (H,) vector that receive the row's direct output
+// (possibly in a peer GPU's memory).  Called by the 256 worker threads.
+// NDV = output columns this call produces (512, or 256 starting at column dv0:
+// half the accumulator registers, for blocks whose register budget is 128).
+template <int DQK, int KVDT, int NDV = kMlaDv>
 __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int split, int n_splits,
-                         unsigned char* smem) {
+                         unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr, int dv0 = 0) {
+  constexpr int NT = NDV / 16;            // 8-column accumulator tiles per warp
+  const int col0 = dv0 + (NDV / 2) * (static_cast<int>(threadIdx.x) >> 7);  // first output column of this warp
   using SM = MlaSmem<DQK>;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -152,7 +159,7 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
   unsigned char* sKb[2] = {smem + SM::kK0, smem + SM::kK1};
   unsigned char* sP = smem + SM::kP;
   float* sMax = reinterpret_cast<float*>(smem + SM::kStat);   // [2][64]
-  float* sSum = sMax + 128;                                    // [2][64]
+  float* sSum = sMax;                                          // [2][64], after the last tile
   int32_t* sValid = reinterpret_cast<int32_t*>(smem + SM::kValid);  // [2][64]
   const float neg_inf = __int_as_float(0xff800000);
   const float scale_log2 = p.softmax_scale * kLog2e;
@@ -165,7 +172,7 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
   const int t_begin = first + split * per;
   const int t_end = min(n_tiles_all, t_begin + per);
 
-  __syncthreads();  // shared memory may be in use by the previous task of this block
+  sync_workers();  // shared memory may be in use by the previous task of this block
   // ---- stage Q (64 heads x DQK) as bf16, swizzled
   {
     const int h0 = hb * kMlaHeads;
@@ -196,9 +203,9 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
   if (t_begin < t_end) mla_load_tile<DQK, KVDT>(p, r, t_begin * kMlaTile, k_valid, win_valid, sKb[0], sValid);
   else cp_async_commit();
 
-  float acc_o[32][4];
+  float acc_o[NT][4];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) acc_o[i][0] = acc_o[i][1] = acc_o[i][2] = acc_o[i][3] = 0.f;
+  for (int i = 0; i < NT; ++i) acc_o[i][0] = acc_o[i][1] = acc_o[i][2] = acc_o[i][3] = 0.f;
   // running statistics of rows (16mt+g) and (16mt+g+8); the sink seeds split 0
   float run_max[2] = {neg_inf, neg_inf};
   float run_sum[2] = {0.f, 0.f};  // this warp's half of the slots only
@@ -218,7 +225,7 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
   for (int tile = t_begin; tile < t_end; ++tile) {
     const int buf = (tile - t_begin) & 1;
     cp_async_wait<0>();
-    __syncthreads();
+    sync_workers();
     if (tile + 1 < t_end)
       mla_load_tile<DQK, KVDT>(p, r, (tile + 1) * kMlaTile, k_valid, win_valid, sKb[buf ^ 1], sValid + 64 * (buf ^ 1));
     else
@@ -267,7 +274,7 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
       sMax[half * 64 + 16 * mt + g] = pm[0];
       sMax[half * 64 + 16 * mt + g + 8] = pm[1];
     }
-    __syncthreads();
+    sync_workers();
     float corr[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -303,14 +310,14 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
     }
     if (corr[0] != 1.f || corr[1] != 1.f) {
 #pragma unroll
-      for (int nt = 0; nt < 32; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         acc_o[nt][0] *= corr[0];
         acc_o[nt][1] *= corr[0];
         acc_o[nt][2] *= corr[1];
         acc_o[nt][3] *= corr[1];
       }
     }
-    __syncthreads();
+    sync_workers();
     // ---- O += P V for 16 heads x 256 columns
     {
       const int a_row = 16 * mt + (lane & 15), a_cadd = lane >> 4;
@@ -324,9 +331,9 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
         }
         const int v_row = 16 * kk + (mi & 1) * 8 + r8;
 #pragma unroll
-        for (int np = 0; np < 16; ++np) {
+        for (int np = 0; np < NT / 2; ++np) {
           uint32_t bv[4];
-          ldsm_x4_t(bv, sK_u + swz<DQK>(v_row, 32 * half + 2 * np + (mi >> 1)));
+          ldsm_x4_t(bv, sK_u + swz<DQK>(v_row, col0 / 8 + 2 * np + (mi >> 1)));
           mma_bf16_16816(acc_o[2 * np], a, bv[0], bv[1]);
           mma_bf16_16816(acc_o[2 * np + 1], a, bv[2], bv[3]);
         }
@@ -334,13 +341,13 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
     }
   }
   cp_async_wait<0>();
-  __syncthreads();
+  sync_workers();
   // ---- combine the two slot halves' sums and write out
   if (c == 0) {
     sSum[half * 64 + 16 * mt + g] = run_sum[0];
     sSum[half * 64 + 16 * mt + g + 8] = run_sum[1];
   }
-  __syncthreads();
+  sync_workers();
   const bool direct = n_splits == 1;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -350,25 +357,28 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
     const bool live = sum > 0.f;
     const float inv = live ? p.output_scale / sum : 0.f;
     const float lse = live ? log2f(sum) + scale_log2 * run_max[i] : neg_inf;
-    if (half == 0 && c == 0) {
+    if (half == 0 && c == 0 && dv0 == 0) {
       if (direct) {
-        if (p.lse) p.lse[static_cast<int64_t>(r) * p.lse_stride + h] = lse;
+        if (lse_row) lse_row[h] = lse;
+        else if (p.lse) p.lse[static_cast<int64_t>(r) * p.lse_stride + h] = lse;
       } else {
         p.ws_lse[(static_cast<int64_t>(r) * n_splits + split) * p.H + h] = lse;
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < 32; ++nt) {
-      const int col = 256 * half + 8 * nt + 2 * c;
+    for (int nt = 0; nt < NT; ++nt) {
+      const int col = col0 + 8 * nt + 2 * c;
       const float v0 = acc_o[nt][2 * i] * inv, v1 = acc_o[nt][2 * i + 1] * inv;
       if (!direct) {
         float* dst = p.ws_o + ((static_cast<int64_t>(r) * n_splits + split) * p.H + h) * kMlaDv + col;
         *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
       } else if (p.out_dtype == MDC_DT_F32) {
-        float* dst = static_cast<float*>(p.o) + static_cast<int64_t>(r) * p.o_stride + static_cast<int64_t>(h) * kMlaDv + col;
+        float* dst = (o_row ? static_cast<float*>(o_row) : static_cast<float*>(p.o) + static_cast<int64_t>(r) * p.o_stride) +
+                     static_cast<int64_t>(h) * kMlaDv + col;
         *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
       } else {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.o) + static_cast<int64_t>(r) * p.o_stride +
+        __nv_bfloat16* dst = (o_row ? static_cast<__nv_bfloat16*>(o_row)
+                                    : static_cast<__nv_bfloat16*>(p.o) + static_cast<int64_t>(r) * p.o_stride) +
                              static_cast<int64_t>(h) * kMlaDv + col;
         *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(v0, v1);
       }

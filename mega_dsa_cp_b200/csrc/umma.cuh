@@ -48,6 +48,19 @@ __device__ inline void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 
+// true in exactly one lane of the (converged) warp
+__device__ inline bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " elect.sync _|p, 0xffffffff;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- descriptors -------------------------------------------------------------
 // Shared-memory operand, K-major, 128-byte swizzle: rows of 128 bytes, 8-row
 // groups 1024 bytes apart, 16-byte chunk j of row r stored at chunk j ^ (r % 8).

@@ -1,0 +1,173 @@
+"""One decode layer-step of context-parallel DeepSeek sparse attention as a
+single persistent-kernel launch per rank.
+
+Per rank r of cp ranks (token t lives on rank t % cp at local index t // cp):
+
+    LOGITS(b, c)   indexer logits + exact local top-k of chunk c     (x B x C)
+    MERGE_L1(b)    C chunk lists -> rank-local top-k, stored into every rank's arena
+    MERGE_L2(b)    cp lists -> global top-k (bit-identical on all ranks) and
+                   this rank's gather list (ids with id % cp == r)
+    ATTN(b, j)     sparse MLA over the local share, 64 heads x 256 columns per
+                   task; bf16 partial + log2-LSE stored into the owner's inbox
+    LSE_MERGE(b)   on owner b % cp: cp partials -> output row
+
+wired by events l1[b], cand[b], topk[b], part[b] (docs/phase1.4-comm-tasks.md
+section 3 of the reference; its design never got assembled there).  The task
+graph is validated and turned into per-block queues by schedule.codegen; the
+device side is csrc/megakernel.cu.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _native as N
+from .comm.buffers import alloc_arena
+from .events import SCOPE_LOCAL, SCOPE_SYS, EventSpec, NotifyEdge, TaskSpec, WaitEdge
+from .events.symm import alloc_event_buffer
+from .schedule.codegen import codegen_schedule
+from .schedule.device import launch_megakernel, upload_schedule
+
+D_V = 512
+
+
+def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128):
+    """Tasks / events of one layer-step for ALL ranks, plus op codes by task name."""
+    cross = SCOPE_SYS if cp > 1 else SCOPE_LOCAL
+    events, tasks, ops = [], [], {}
+    for b in range(B):
+        events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL), EventSpec(f"cand[{b}]", cross),
+                   EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
+    n_attn = 2 * (heads // 64)
+    for r in range(cp):
+        for b in range(B):
+            for c in range(n_chunks):
+                name = f"logits[{r},{b},{c}]"
+                tasks.append(TaskSpec(name, r, (), (NotifyEdge(f"l1[{b}]", r),), (b, c, 0)))
+                ops[name] = N.OP_LOGITS
+        for b in range(B):
+            name = f"merge_l1[{r},{b}]"
+            tasks.append(TaskSpec(name, r, (WaitEdge(f"l1[{b}]"),),
+                                  tuple(NotifyEdge(f"cand[{b}]", d) for d in range(cp)), (b, 0, 0)))
+            ops[name] = N.OP_MERGE_L1
+        for b in range(B):
+            name = f"merge_l2[{r},{b}]"
+            tasks.append(TaskSpec(name, r, (WaitEdge(f"cand[{b}]"),), (NotifyEdge(f"topk[{b}]", r),), (b, 0, 0)))
+            ops[name] = N.OP_MERGE_L2
+        for b in range(B):
+            for j in range(n_attn):
+                name = f"attn[{r},{b},{j}]"
+                tasks.append(TaskSpec(name, r, (WaitEdge(f"topk[{b}]"),), (NotifyEdge(f"part[{b}]", b % cp),), (b, j, 0)))
+                ops[name] = N.OP_ATTN
+        for b in range(B):
+            if b % cp == r:
+                name = f"lse_merge[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (WaitEdge(f"part[{b}]"),), (), (b, 0, 0)))
+                ops[name] = N.OP_LSE_MERGE
+    return tasks, events, ops
+
+
+def arena_regions(B: int, cp: int, top_k: int, heads: int = 128):
+    cand = B * cp * (top_k * 8 + 16)
+    inbox = -(-B // cp) * cp * (heads * D_V * 2 + heads * 4)
+    return {"cand": cand, "inbox": inbox}
+
+
+@dataclass
+class LayerInputs:
+    kv_pages: torch.Tensor      # (num_pages, page_bytes) uint8 index-K cache of this rank
+    block_table: torch.Tensor   # (B, max_pages) int32
+    seq_lens: torch.Tensor      # (B,) int32 rank-local token counts
+    q_idx: torch.Tensor         # (B, 64, 128) bf16 indexer query (replicated on all ranks)
+    w_idx: torch.Tensor         # (B, 64) fp32 head-gate weights
+    q_mla: torch.Tensor         # (B, 1, H, d_qk) bf16 attention query (replicated)
+    kv_mla: torch.Tensor        # (B * kv_seq_stride, 1, d_qk) bf16 local KV rows
+
+
+class DsaDecodeLayer:
+    """Owns the schedule, the symmetric buffers and the scratch of one layer."""
+
+    def __init__(self, B: int, cp: int = 1, rank: int = 0, top_k: int = 2048, heads: int = 128, d_qk: int = 576,
+                 fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
+                 kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
+                 device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None):
+        self.B, self.cp, self.rank, self.K, self.H, self.d_qk = B, cp, rank, top_k, heads, d_qk
+        self.fmt, self.P, self.max_pages, self.bpc = fmt, page_tokens, max_pages, blocks_per_chunk
+        self.n_chunks = -(-max_pages // blocks_per_chunk)
+        self.kv_seq_stride = kv_seq_stride or max_pages * page_tokens
+        self.device = torch.device(device)
+        self.phases = phases
+        self.scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d_qk)
+        if n_ctas is None:
+            n_ctas = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.n_ctas = n_ctas
+        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads)
+        self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
+        self.dsched = upload_schedule(self.schedule, self.device)
+        self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
+        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads), phases, rank, cp, group_name, self.device)
+        dev = self.device
+        C, K = self.n_chunks, top_k
+        self.cand_v = torch.empty(B, 1, C, K, device=dev)
+        self.cand_i = torch.empty(B, 1, C, K, dtype=torch.int32, device=dev)
+        self.cand_c = torch.zeros(B, 1, C, dtype=torch.int32, device=dev)
+        self.sel_v = torch.zeros(B, K, device=dev)
+        self.sel_i = torch.zeros(B, K, dtype=torch.int32, device=dev)
+        self.sel_c = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.pt_local = torch.zeros(B, K, dtype=torch.int32, device=dev)
+        self.k_valid = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(B, heads, D_V, dtype=out_dtype, device=dev)
+        self.out_lse = torch.zeros(B, heads, device=dev)
+        self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.phase = 0
+        self._params = None
+        self._inputs = None
+
+    def bind(self, x: LayerInputs) -> None:
+        """Fixes the input tensors (their addresses are baked into the launch parameters)."""
+        B, K = self.B, self.K
+        assert x.q_idx.dtype == torch.bfloat16 and x.q_mla.dtype == torch.bfloat16
+        lp = N.LogitsParams(
+            kv_pages=N.ptr(x.kv_pages), num_pages=x.kv_pages.shape[0], page_tokens=self.P,
+            fmt=N.FMT_MXFP4 if self.fmt == "mxfp4" else N.FMT_NVFP4, q_fmt=N.Q_BF16,
+            q=N.ptr(x.q_idx), q_sf=None, weights=N.ptr(x.w_idx), block_table=N.ptr(x.block_table),
+            max_pages=self.max_pages, seq_lens=N.ptr(x.seq_lens), logits=None, logits_stride=0,
+            cand_v=N.ptr(self.cand_v), cand_i=N.ptr(self.cand_i), cand_c=N.ptr(self.cand_c), top_k=K,
+            B=B, q_len=1, heads=64, blocks_per_chunk=self.bpc, n_chunks=self.n_chunks, window_exclude=0,
+            id_mul=self.cp, id_add=self.rank, status=N.ptr(self.status))
+        mp = N.SparseMlaParams(
+            q=N.ptr(x.q_mla), kv_win=None, kv_cmp=N.ptr(x.kv_mla), pt_win=None, pt_cmp=N.ptr(self.pt_local),
+            k_valid=N.ptr(self.k_valid), win_valid=None, attn_sink=None, o=N.ptr(self.out), lse=N.ptr(self.out_lse),
+            o_stride=self.H * D_V, lse_stride=self.H, ws_o=None, ws_lse=None,
+            B=B, q_len=1, H=self.H, d_qk=self.d_qk, d_v=D_V, pages_win=0, pages_cmp=x.kv_mla.shape[0], page_cmp=1,
+            pt_cols=K, kv_dtype=N.DT_BF16, out_dtype=N.DT_BF16, n_splits=1, fp8_p=0,
+            softmax_scale=self.scale, output_scale=1.0, status=N.ptr(self.status))
+        L = N.LayerParams()
+        L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = self.cp, self.rank, B, K, self.H, self.n_chunks
+        L.kv_seq_stride = self.kv_seq_stride
+        L.logits, L.mla = lp, mp
+        L.cand_off, L.inbox_off = self.arena.regions["cand"], self.arena.regions["inbox"]
+        L.phase_bytes, L.phases = self.arena.nbytes_per_phase, self.phases
+        L.sel_v, L.sel_i, L.sel_c = N.ptr(self.sel_v), N.ptr(self.sel_i), N.ptr(self.sel_c)
+        L.out, L.out_lse = N.ptr(self.out), N.ptr(self.out_lse)
+        L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
+        self._params, self._inputs = L, x
+
+    def step(self, wait_budget_ns: int = 2_000_000_000, stream=None) -> None:
+        """Launches one layer-step (asynchronous).  Every rank must call it with the same phase."""
+        assert self._params is not None, "bind() inputs first"
+        self.dsched.scalars[0:1].fill_(self.phase)
+        launch_megakernel(self.dsched, self.events, self.arena, self.status, layer=self._params,
+                          wait_budget_ns=wait_budget_ns, stream=stream)
+        self.phase += 1
+
+    def owned_rows(self):
+        return [b for b in range(self.B) if b % self.cp == self.rank]
+
+    def check_status(self) -> None:
+        st = self.status.tolist()
+        if st[0] != 0:
+            raise N.MdcError(f"device failure: code {st[0]} block {st[1]} detail {st[2:4]} seen/wanted {st[4:]}")

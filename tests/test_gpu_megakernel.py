@@ -1,0 +1,151 @@
+"""GPU tests of the event / scheduler / comm device layer and of the decode
+megakernel on one GPU (world size 1), through the C ABI."""
+
+import math
+import random
+
+import pytest
+import torch
+
+from mega_dsa_cp.events import SCOPE_LOCAL, EventSpec, NotifyEdge, TaskSpec, WaitEdge
+from mega_dsa_cp.schedule.codegen import codegen_schedule
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _random_dag(seed, n_tasks, edge_prob):
+    rng = random.Random(seed)
+    order = list(range(n_tasks))
+    rng.shuffle(order)
+    pos = {t: i for i, t in enumerate(order)}
+    preds = {j: [i for i in range(n_tasks) if pos[i] < pos[j] and rng.random() < edge_prob] for j in range(n_tasks)}
+    events, tasks = [], []
+    for t in range(n_tasks):
+        if preds[t]:
+            events.append(EventSpec(f"e{t}", SCOPE_LOCAL))
+        tasks.append(TaskSpec(f"t{t}", 0, (WaitEdge(f"e{t}"),) if preds[t] else (),
+                              tuple(NotifyEdge(f"e{j}", 0) for j in range(n_tasks) if t in preds[j]), (t, 0, 0)))
+    return tasks, events, preds
+
+
+def _setup(tasks, events, ops, n_ctas):
+    from mega_dsa_cp_b200 import _native as N
+    from mega_dsa_cp_b200.events.symm import alloc_event_buffer
+    from mega_dsa_cp_b200.schedule.device import upload_schedule
+
+    sched = codegen_schedule(tasks, events, rank=0, n_ctas=n_ctas, op_of=ops)
+    ds = upload_schedule(sched, DEV)
+    ev = alloc_event_buffer(max(len(events), 1), device=DEV)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    return ds, ev, status
+
+
+def test_random_dag_runs_in_dependency_order_over_two_phases():
+    """512 tasks with random dependencies on 32 blocks; the logged execution
+    order must be a valid linearisation, also when the same launch is replayed
+    with only the phase scalar advanced (the reference's single-GPU event and
+    scheduler tests)."""
+    from mega_dsa_cp_b200 import _native as N
+    from mega_dsa_cp_b200.schedule.device import launch_megakernel
+
+    tasks, events, preds = _random_dag(3, 512, 0.01)
+    ds, ev, status = _setup(tasks, events, {t.name: N.OP_LOG for t in tasks}, 32)
+    for phase in range(2):
+        log = torch.zeros(1024, dtype=torch.int32, device=DEV)
+        ds.scalars[0] = phase
+        launch_megakernel(ds, ev, None, status, log=log)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0, status.tolist()
+        n = log[0].item()
+        order = log[1:1 + n].tolist()
+        assert sorted(order) == list(range(512))
+        at = {t: i for i, t in enumerate(order)}
+        assert all(at[p] < at[t] for t, ps in preds.items() for p in ps)
+    cells = ev.tensor.view(-1, 16)[:, 0]
+    arity = torch.tensor([len(preds[int(e.name[1:])]) for e in events], device=DEV)
+    assert torch.equal(cells[:len(events)], 2 * arity)   # counters only ever grow
+
+
+def test_wait_gives_up_within_its_budget_and_reports():
+    """A wait whose event nobody notifies must end after the budget with a
+    status record (code, event, seen, wanted) and leave the context usable."""
+    from mega_dsa_cp_b200 import _native as N
+    from mega_dsa_cp_b200.schedule.device import launch_megakernel, upload_schedule
+    from mega_dsa_cp_b200.events.symm import alloc_event_buffer
+    from mega_dsa_cp_b200.schedule.codegen import Schedule, pack_header, OP_END
+
+    # hand-made queue: one block waits on event 0 (arity 3) that nothing notifies; another block just logs
+    q0 = [pack_header(N.OP_LOG, 1, 0, 0), 7, 0, 0, 0, pack_header(OP_END, 0, 0, 0)]
+    q1 = [pack_header(N.OP_LOG, 0, 0, 0), 9, 0, 0, pack_header(OP_END, 0, 0, 0)]
+    sched = Schedule(queues=[q0, q1], arity=[3], scopes=[0], topo=[0, 1], op_of=[N.OP_LOG] * 2, n_events=1)
+    ds = upload_schedule(sched, DEV)
+    ev = alloc_event_buffer(1, device=DEV)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    log = torch.zeros(16, dtype=torch.int32, device=DEV)
+    launch_megakernel(ds, ev, None, status, log=log, wait_budget_ns=20_000_000)
+    torch.cuda.synchronize()
+    st = status.tolist()
+    assert st[0] == N.DEV_WAIT_TIMEOUT and st[2] == 0 and st[4] == 0 and st[6] == 3, st
+    assert log[0].item() == 1 and log[1].item() == 9
+    # the context is alive and the library still works
+    assert torch.ones(4, device=DEV).sum().item() == 4
+
+
+def test_bulk_push_and_verify_world1():
+    """smem -> arena bulk push, release notify, system-scope read-back (the
+    world-size-1 degenerate of the reference's comm test)."""
+    from mega_dsa_cp_b200 import _native as N
+    from mega_dsa_cp_b200.comm.buffers import alloc_arena
+    from mega_dsa_cp_b200.schedule.device import launch_megakernel
+
+    slots, nbytes = 6, 4096
+    events = [EventSpec(f"arrived{s}", SCOPE_LOCAL) for s in range(slots)]
+    tasks, ops = [], {}
+    for s in range(slots):
+        tasks.append(TaskSpec(f"push{s}", 0, (), (NotifyEdge(f"arrived{s}", 0),), (s, 0, s)))
+        tasks.append(TaskSpec(f"check{s}", 0, (WaitEdge(f"arrived{s}"),), (), (s, 0, s)))
+        ops[f"push{s}"], ops[f"check{s}"] = N.OP_PUSH, N.OP_VERIFY
+    ds, ev, status = _setup(tasks, events, ops, 4)
+    arena = alloc_arena({"test": slots * nbytes}, phases=1, device=DEV)
+    for phase in range(2):
+        ds.scalars[0] = phase
+        launch_megakernel(ds, ev, arena, status, test_off=arena.region_off("test"), test_slot_bytes=nbytes)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0, status.tolist()
+    assert arena.tensor.view(torch.int32).abs().sum().item() != 0
+
+
+@pytest.mark.parametrize("B,S,K,bpc", [(2, 4096, 512, 16), (3, 8192, 2048, 32)])
+def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
+    from dsa_inputs import indexer_case
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from oracle import dsa_oracle as orc
+
+    P, H, DQK = 64, 128, 576
+    case = indexer_case(B, S, P, "nvfp4", seed=4)
+    g = torch.Generator().manual_seed(8)
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
+    seq = torch.tensor([S - 100 * b for b in range(B)], dtype=torch.int32)
+    layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=64)
+    d = lambda t: t.to(DEV)
+    layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
+    for phase in range(2):   # the second launch replays with the phase bumped
+        layer.step()
+        torch.cuda.synchronize()
+        layer.check_status()
+    data, sf = orc.split_index_pages(case["fused"], "nvfp4", P)
+    kd_all = orc.dequant_fp4(data, sf, "nvfp4").reshape(-1, P, 128)
+    for b in range(B):
+        kd = kd_all[case["bt"][b].long()].reshape(S, 128)
+        sel, o, l = orc.decode_step_ref(case["q_deq"][b], case["w"][b], kd, q_mla[b, 0].float(),
+                                        kv[b * S:(b + 1) * S, 0].float(), int(seq[b]), K, 1 / math.sqrt(DQK))
+        n = int(layer.sel_c[b])
+        got = torch.sort(layer.sel_i[b, :n].cpu()).values
+        overlap = len(set(got.tolist()) & set(sel.tolist())) / max(1, sel.numel())
+        assert n == sel.numel() and overlap >= 0.999, (n, sel.numel(), overlap)
+        if overlap == 1.0:
+            assert (layer.out[b].cpu() - o).abs().max() < 2e-2
+            assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
