@@ -299,6 +299,67 @@ int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
 int mdc_megakernel_smem_bytes(void);
 int mdc_megakernel_threads(void);
 
+/* ------------------------------------------------------------------------
+ * KV compressor: softmax-gated pooling of token records into compressed
+ * entries, context-parallel (per-rank partial statistics -> pushed to the
+ * entry's owner rank -> owner merges, normalises, rotates, quantises and
+ * writes its pools).  Replaces the four kernels and launchers of
+ * mega_dsa_cp/tiles/compress.py:120-250 (csa step), :284-523 (csa finalize),
+ * :564-640 (c128 step), :669-792 (c128 finalize) and the micro kernel :828-889.
+ *
+ * ratio == 4 : overlapping 8-slot window machine, two streams (attention 512
+ *              channels, indexer 128 channels), records (B, 4*hd) =
+ *              [kv_overlap | kv_normal | score_overlap | score_normal].
+ * ratio == 64 / 128 : online machine, one stream of 512 channels, records
+ *              (B, 2*512) = [kv | score], running state (B, 3, 512) = [m | l | kv].
+ * A step covers global positions seq_len[b] .. seq_len[b] + q_len - 1; this
+ * rank owns the position p with p % cp == rank (q_len <= cp).  Entry n is
+ * owned by rank n % cp and stored at its local slot n / cp.
+ * Statistics region: (B, cp, stats_bytes) at arena offset stats_off with
+ * stats_bytes = 7696 (ratio 4) or 6160 (online); event cell ev_base_id + b is
+ * bumped once per rank per step on every rank (arity cp).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, cp, rank, q_len, ratio;
+  int32_t phase;               /* finalize: waits for cell value cp * (phase + 1)        */
+  const int32_t* seq_len;      /* (B,) global length before the step                     */
+  float* ring_attn;            /* ratio 4: (B, 8, 4*512) ring of this rank's records     */
+  float* ring_idx;             /* ratio 4: (B, 8, 4*128)                                 */
+  const float* new_attn;       /* ratio 4: (B, 4*512); online: (B, 2*512)                */
+  const float* new_idx;        /* ratio 4: (B, 4*128)                                    */
+  const float* ape_attn;       /* ratio 4: (8, 512) slot bias; online: (ratio, 512)      */
+  const float* ape_idx;        /* ratio 4: (8, 128)                                      */
+  float* state;                /* online: (B, 3, 512)                                    */
+  mdc_peer_buffer arena;
+  int64_t stats_off;
+  mdc_event_set events;
+  int32_t ev_base_id;
+  int32_t do_push;             /* 0 skips the payload push (bisecting aid)               */
+  int64_t wait_budget_ns;
+  const float* norm_w_attn;    /* (512,)                                                 */
+  const float* norm_w_idx;     /* (128,)                                                 */
+  const float* freqs;          /* (freq_rows, 64) rope table [cos0, sin0, cos1, ...]     */
+  int32_t freq_rows;
+  float norm_eps;
+  float inv_fp8_scale;
+  int32_t attn_pool_dtype;     /* MDC_DT_E4M3 | MDC_DT_BF16                              */
+  void* attn_pool;             /* (B, max_entries, 512)                                  */
+  uint8_t* idx_pool;           /* ratio 4: (B, max_entries / idx_page_tokens, page bytes) */
+  int32_t idx_fmt;             /* MDC_FMT_*                                              */
+  int32_t idx_page_tokens;
+  int32_t max_entries;
+  int32_t reserved0;
+  int32_t* k_valid;            /* (B,) entries held by this rank                         */
+  float* dbg_attn;             /* (B, max_entries, 512) merged fp32 before the norm, or NULL */
+  float* dbg_idx;              /* (B, max_entries, 128) or NULL                          */
+  int32_t* status;
+} mdc_compress_params;
+int mdc_compress_step_launch(const mdc_compress_params* p, void* stream);
+int mdc_compress_finalize_launch(const mdc_compress_params* p, void* stream);
+/* staged 128-point Hadamard + MXFP4 quantisation of n rows: x (n, 128) fp32 ->
+ * out (n, 68) = 64 B packed codes + 4 B UE8M0 (compress.py:828-889) */
+int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

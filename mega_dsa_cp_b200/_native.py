@@ -91,6 +91,20 @@ class MegaParams(C.Structure):
     ]
 
 
+class CompressParams(C.Structure):
+    _fields_ = [
+        ("B", i32), ("cp", i32), ("rank", i32), ("q_len", i32), ("ratio", i32), ("phase", i32),
+        ("seq_len", p_void), ("ring_attn", p_void), ("ring_idx", p_void), ("new_attn", p_void), ("new_idx", p_void),
+        ("ape_attn", p_void), ("ape_idx", p_void), ("state", p_void),
+        ("arena", PeerBufferC), ("stats_off", i64), ("events", EventSetC), ("ev_base_id", i32), ("do_push", i32),
+        ("wait_budget_ns", i64), ("norm_w_attn", p_void), ("norm_w_idx", p_void), ("freqs", p_void),
+        ("freq_rows", i32), ("norm_eps", f32), ("inv_fp8_scale", f32), ("attn_pool_dtype", i32),
+        ("attn_pool", p_void), ("idx_pool", p_void), ("idx_fmt", i32), ("idx_page_tokens", i32),
+        ("max_entries", i32), ("reserved0", i32), ("k_valid", p_void), ("dbg_attn", p_void), ("dbg_idx", p_void),
+        ("status", p_void),
+    ]
+
+
 OP_NOP, OP_LOGITS, OP_MERGE_L1, OP_MERGE_L2, OP_ATTN, OP_LSE_MERGE = 0, 1, 2, 3, 4, 5
 OP_SLEEP, OP_LOG, OP_PUSH, OP_VERIFY = 16, 17, 18, 19
 DEV_WAIT_TIMEOUT, DEV_COPY_TIMEOUT, DEV_BAD_INDEX, DEV_BAD_OP = 1, 2, 3, 4
@@ -126,6 +140,7 @@ EXPORTS = [
     "mdc_logits_fp4_launch", "mdc_logits_fp4_smem_bytes", "mdc_merge_topk_launch",
     "mdc_lse_merge_launch", "mdc_sparse_mla_launch", "mdc_sparse_mla_smem_bytes",
     "mdc_megakernel_launch", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
+    "mdc_compress_step_launch", "mdc_compress_finalize_launch", "mdc_hadamard_quant_launch",
 ]
 
 
