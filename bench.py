@@ -249,6 +249,126 @@ def run_gpu_cfg2(args):
     print(json.dumps(line))
 
 
+# ----------------------------------------------------------------------------
+# N > 1: the full decode layer-step, context parallel over N GPUs
+# ----------------------------------------------------------------------------
+def cp_config(n):
+    """128K-token context sharded over n ranks, 8 sequences per rank (BASELINE
+    config 4 at n = 8: B = 64, 16384 tokens per rank per sequence)."""
+    return dict(B=8 * n, S=131072, page=64, top_k=2048, H=128, d_qk=576, cp=n, copies=2, blocks_per_chunk=128)
+
+
+def run_gpu_cp(args):
+    import torch
+    import torch.distributed as dist
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    c = cp_config(world)
+    B, P, K, H, DQK = c["B"], c["page"], c["top_k"], c["H"], c["d_qk"]
+    S_loc = c["S"] // world
+    pages = S_loc // P
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    gq = torch.Generator(device=dev).manual_seed(7)      # replicated tensors: same seed on every rank
+    q_idx = torch.randn(B, 64, 128, generator=gq, device=dev).to(torch.bfloat16)
+    w_idx = (torch.randn(B, 64, generator=gq, device=dev) / 64.0).contiguous()
+    q_mla = (torch.randn(B, 1, H, DQK, generator=gq, device=dev) * 0.5).to(torch.bfloat16)
+    seq_loc = torch.full((B,), S_loc, dtype=torch.int32, device=dev)
+    layers, inputs = [], []
+    for _ in range(c["copies"]):   # rotate over cache copies so every step streams from HBM
+        parts = [fuse_pages(torch.randn(B * S_loc // 8, 128, generator=g, device=dev), "nvfp4", P)[0] for _ in range(8)]
+        cache = torch.cat(parts)
+        bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages).contiguous()
+        kv = (torch.randn(B * S_loc, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+        layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
+                               blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S_loc,
+                               group_name=dist.group.WORLD.group_name, device=dev)
+        layer.bind(LayerInputs(cache, bt, seq_loc, q_idx, w_idx, q_mla, kv))
+        layers.append(layer)
+        inputs.append((cache, bt, kv))
+    dist.barrier()
+    torch.cuda.synchronize()
+
+    def step(i):
+        layers[i % len(layers)].step()
+
+    for i in range(args.warmup * len(layers)):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        time.sleep(0.1)
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ms = ev0.elapsed_time(ev1)
+        time.sleep(0.1)
+    for l in layers:
+        l.check_status()
+    # end to end: query tensors from pinned host memory each step, merged output rows read back
+    hq, hw, hm = q_idx.cpu().pin_memory(), w_idx.cpu().pin_memory(), q_mla.cpu().pin_memory()
+    owned = layers[0].owned_rows()
+    h_out = torch.empty(len(owned), H, 512, dtype=torch.bfloat16).pin_memory()
+    idx = torch.tensor(owned, device=dev)
+
+    def e2e_step(i):
+        q_idx.copy_(hq, non_blocking=True)
+        w_idx.copy_(hw, non_blocking=True)
+        q_mla.copy_(hm, non_blocking=True)
+        l = layers[i % len(layers)]
+        l.step()
+        h_out.copy_(l.out.index_select(0, idx), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, e2e_step_ms = t[0].item() / args.steps, t[1].item() / args.steps
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        algo = B * S_loc * 72 + B * pages * 4 + B * 16640 + B * (pages // c["blocks_per_chunk"]) * K * 8
+        h2d = hq.numel() * 2 + hw.numel() * 4 + hm.numel() * 2
+        line = {
+            "metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp4(e2m1 x ue4m3) x bf16 -> f32; bf16 MLA", "data": "synthetic",
+            "config": {"workload": f"full DSA decode layer-step, CP={world}: B={B}, ctx 131072 sharded token-interleaved "
+                                   f"({S_loc} tokens/rank/seq), indexer + top-k 2048 + sparse MLA (128 heads, 512+64) + LSE merge, "
+                                   "one persistent kernel per rank, P2P stores into symmetric memory",
+                       "l2": f"rotating {c['copies']} cache copies per rank", "parallelism": f"cp{world}"},
+            "step_us": ms_step * 1e3,
+            "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": algo / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": algo / (ms_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
+                         "kernel": "mega_kernel (whole step; indexer bytes only)", "algorithmic_bytes": algo, "traffic": None},
+            "cpu_baseline": None,
+            "clocks": clk.summary(),
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one logits launch, from the
 # ncu capture summarised under profiles/ (None until captured)
 NCU_TRAFFIC_BYTES = None
@@ -332,7 +452,7 @@ def main():
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         run_gpu_cfg2(args)
     else:
-        raise SystemExit("multi-GPU decode step: not wired yet")
+        run_gpu_cp(args)
 
 
 if __name__ == "__main__":

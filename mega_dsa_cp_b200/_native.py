@@ -128,8 +128,8 @@ def lib() -> C.CDLL:
         l.mdc_status_string.argtypes = [C.c_int]
         l.mdc_last_cuda_error.restype = C.c_int
         for name in EXPORTS:
-            fn = getattr(l, name)
-            fn.restype = C.c_int
+            if name != "mdc_status_string":
+                getattr(l, name).restype = C.c_int
         _lib = l
     return _lib
 

@@ -93,8 +93,8 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
   ls.c_stride = 1;
   const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
   unsigned char* slice = arena.local_ptr(off);
-  merge_lists_tile<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
-                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm);
+  merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
+                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm, smem + 8192, kMegaTileSmem - 8192);
   if (L.cp > 1) {
     __threadfence();
     sync_workers();
@@ -120,7 +120,8 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   ls.stride = cand_slice_bytes(L) / 4;
   ls.c_stride = cand_slice_bytes(L) / 4;
   int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
-  const int n = merge_lists_tile<SYS>(ls, L.cp, K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm);
+  const int n = merge_lists_auto<SYS>(ls, L.cp, K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
+                                     smem + 8192, kMegaTileSmem - 8192);
   __threadfence();
   sync_workers();
   int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;

@@ -2,9 +2,13 @@
 #include "tile_merge.cuh"
 
 namespace mdc {
+constexpr int kMergeStageMax = 200 * 1024;  // rows of up to 25600 positions are staged in shared memory
 __global__ void __launch_bounds__(kBlockThreads) merge_topk_kernel(const __grid_constant__ mdc_merge_topk_params p) {
   __shared__ MergeSmem sm;
-  merge_topk_tile(p, blockIdx.x, sm);
+  extern __shared__ __align__(16) unsigned char stage[];
+  const int n_pos = p.L * p.maxK;
+  const bool staged = n_pos > kBlockThreads * kMergeRegE && n_pos * 8 <= kMergeStageMax;
+  merge_topk_tile(p, blockIdx.x, sm, staged ? stage : nullptr, staged ? n_pos * 8 : 0);
 }
 }  // namespace mdc
 
@@ -14,7 +18,10 @@ extern "C" int mdc_merge_topk_launch(const mdc_merge_topk_params* p, void* strea
   if (p->B < 1 || p->q_len < 1 || p->L < 1 || p->L > kMergeMaxLists || p->maxK < 1 || p->top_k < 1)
     return MDC_ERR_BAD_SHAPE;
   if (static_cast<int64_t>(p->L) * p->maxK > (1ll << 30)) return MDC_ERR_TOO_LARGE;
-  merge_topk_kernel<<<p->B * p->q_len, kBlockThreads, 0, static_cast<cudaStream_t>(stream)>>>(*p);
+  const int64_t n_pos = static_cast<int64_t>(p->L) * p->maxK;
+  const int smem = (n_pos > kBlockThreads * kMergeRegE && n_pos * 8 <= kMergeStageMax) ? static_cast<int>(n_pos * 8) : 0;
+  MDC_CUDA_OK(cudaFuncSetAttribute(merge_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeStageMax));
+  merge_topk_kernel<<<p->B * p->q_len, kBlockThreads, smem, static_cast<cudaStream_t>(stream)>>>(*p);
   MDC_CUDA_OK(cudaGetLastError());
   return MDC_OK;
 }

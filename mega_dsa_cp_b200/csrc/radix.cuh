@@ -124,6 +124,70 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
   return th;
 }
 
+// Same contract as block_select_threshold for u32 keys (0 = no element) that
+// are cheap to re-read (shared memory): a bitwise search for the k-th largest
+// key, one block-wide count per bit, no per-element atomics.  key(pos) -> u32.
+template <typename KeyFn>
+__device__ Threshold<uint32_t> block_select_bits(KeyFn key, int n_pos, int k, SelectScratch& sc) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  Threshold<uint32_t> th;
+  uint32_t kmax = 0u, kmin = 0xffffffffu;
+  int mine = 0;
+  for (int pos = tid; pos < n_pos; pos += kBlockThreads) {
+    const uint32_t kv = key(pos);
+    mine += kv != 0u;
+    kmax = max(kmax, kv);
+    if (kv != 0u) kmin = min(kmin, kv);
+  }
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  kmax = __reduce_max_sync(0xffffffffu, kmax);
+  kmin = __reduce_min_sync(0xffffffffu, kmin);
+  sync_workers();
+  if (lane == 0) {
+    sc.wgt[warp] = mine;
+    sc.hist[warp] = kmax;
+    sc.hist[8 + warp] = kmin;
+  }
+  for (int i = tid; i < 128; i += kBlockThreads) sc.hist[32 + i] = 0;
+  sync_workers();
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    total += sc.wgt[w];
+    kmax = max(kmax, sc.hist[w]);
+    kmin = min(kmin, sc.hist[8 + w]);
+  }
+  if (total <= k) {
+    th.tau = 0;
+    th.need_eq = 0x7fffffff;
+    th.n_sel = total;
+    sync_workers();
+    return th;
+  }
+  const int top_bit = 31 - __clz(static_cast<int>((kmax ^ kmin) | 1u));
+  uint32_t tau = (top_bit == 31) ? 0u : (kmax & ~((2u << top_bit) - 1u));
+#pragma unroll 1
+  for (int bit = top_bit; bit >= 0; --bit) {
+    const uint32_t cand = tau | (1u << bit);
+    int c = 0;
+    for (int pos = tid; pos < n_pos; pos += kBlockThreads) c += key(pos) >= cand;
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (lane == 0) atomicAdd(&sc.hist[32 + bit], static_cast<uint32_t>(c));
+    sync_workers();
+    if (static_cast<int>(sc.hist[32 + bit]) >= k) tau = cand;
+  }
+  int gt = 0;
+  for (int pos = tid; pos < n_pos; pos += kBlockThreads) gt += key(pos) > tau;
+  gt = __reduce_add_sync(0xffffffffu, gt);
+  if (lane == 0) atomicAdd(&sc.hist[96], static_cast<uint32_t>(gt));
+  sync_workers();
+  th.tau = tau;
+  th.need_eq = k - static_cast<int>(sc.hist[96]);
+  th.n_sel = k;
+  sync_workers();
+  return th;
+}
+
 // Deterministic emit of the selected elements in position order.
 // emit(pos, slot) is called once per selected element; returns the count.
 template <typename KeyT, typename Src, typename Emit>

@@ -46,6 +46,7 @@
 #include "common.cuh"
 #include "fp4.cuh"
 #include "radix.cuh"
+#include "radix_regs.cuh"
 #include "umma.cuh"
 
 namespace mdc {
@@ -71,6 +72,7 @@ constexpr int kTileTok = 128;    // tokens per pipeline stage (= UMMA M)
 constexpr int kRawStages = 8;    // raw page ring
 constexpr int kAStages = 4;      // decoded-A ring in tensor memory
 constexpr int kTmemCols = 512;
+constexpr int kFusedRegE = 32;   // fused top-k keeps up to 256 * 32 scores per query token in registers
 constexpr int kLogitsThreads = 480;  // 8 decode + 4 gate + 2 issue + 1 copy warps
 constexpr int kGateWarp0 = 8, kIssueWarp = 12, kIssueWarps = 2, kCopyWarp = 14;
 
@@ -105,7 +107,8 @@ __host__ __device__ inline LogitsSmem logits_smem_layout(int q_len, int chunk_to
   off += q_len * kIdxHeads * 4;
   off = static_cast<int>(align_up(off, 16));
   L.sel = off;
-  off += static_cast<int>(align_up(sizeof(SelectScratch), 16));
+  off += static_cast<int>(align_up(sizeof(SelectScratch) > sizeof(RegSelectScratch<kFusedRegE>) ? sizeof(SelectScratch)
+                                                                                             : sizeof(RegSelectScratch<kFusedRegE>), 16));
   L.page_ok = off;  // one byte per page of the chunk
   off += static_cast<int>(align_up(chunk_tokens / PAGE + 4, 16));
   L.scores = off;
@@ -466,12 +469,38 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         valid = (base_pos + pos) < limit;
         return sortable_u32(sc_row[pos]);
       };
-      Threshold<uint32_t> th = block_select_threshold<uint32_t>(src, n_local, p.top_k, sel);
       const int64_t slot0 = ((static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk) * p.top_k;
-      int n = block_emit_selected<uint32_t>(src, n_local, th, sel, [&](int pos, int slot) {
-        p.cand_v[slot0 + slot] = sc_row[pos];
-        p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
-      });
+      int n;
+      if (n_local <= kBlockThreads * kFusedRegE) {
+        // register-resident select: one pass over shared memory, ties resolved by position
+        RegSelectScratch<kFusedRegE>& rsel = *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel);
+        uint32_t key[kFusedRegE];
+#pragma unroll
+        for (int it = 0; it < kFusedRegE; ++it) {
+          const int pos = it * kBlockThreads + tid;
+          key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+        }
+        const Threshold<uint32_t> th = block_select_regs<kFusedRegE>(key, p.top_k, rsel);
+        const bool all = th.need_eq == 0x7fffffff;
+        int slot[kFusedRegE];
+        n = block_emit_regs<kFusedRegE>(
+            all ? 0 : th.need_eq, rsel, [&](int it) { return all ? key[it] != 0u : key[it] > th.tau; },
+            [&](int it) { return !all && key[it] == th.tau; }, slot);
+#pragma unroll
+        for (int it = 0; it < kFusedRegE; ++it) {
+          if (slot[it] >= 0) {
+            const int pos = it * kBlockThreads + tid;
+            p.cand_v[slot0 + slot[it]] = sc_row[pos];
+            p.cand_i[slot0 + slot[it]] = (base_pos + pos) * p.id_mul + p.id_add;
+          }
+        }
+      } else {
+        Threshold<uint32_t> th = block_select_threshold<uint32_t>(src, n_local, p.top_k, sel);
+        n = block_emit_selected<uint32_t>(src, n_local, th, sel, [&](int pos, int slot) {
+          p.cand_v[slot0 + slot] = sc_row[pos];
+          p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
+        });
+      }
       if (tid == 0) p.cand_c[(static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk] = n;
     }
   }

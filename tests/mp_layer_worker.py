@@ -1,0 +1,79 @@
+"""Multi-GPU worker (launched with torchrun, one process per GPU): runs the
+decode megakernel at cp = world size on a small seeded case and checks the
+selection and the merged attention output against the CPU oracle."""
+
+import math
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from oracle import dsa_oracle as orc
+
+    B, S, K, P, H, DQK = 4, 8192, 512, 64, 128, 576
+    S_loc = S // world
+    g = torch.Generator().manual_seed(123)
+    kraw = torch.randn(B, S, 128, generator=g)
+    q_idx = torch.randn(B, 64, 128, generator=g).bfloat16()
+    w_idx = torch.randn(B, 64, generator=g) / 64.0
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(B, S, DQK, generator=g) * 0.5).bfloat16()
+    seq = torch.tensor([S - 64 * b - 3 for b in range(B)], dtype=torch.int32)
+    # this rank's shard: token t -> local index t // world on rank t % world
+    k_loc = kraw[:, rank::world].reshape(B * S_loc, 128)
+    fused, _ = orc.build_index_pages(k_loc, "nvfp4", P)
+    pages = S_loc // P
+    bt = torch.arange(B * pages, dtype=torch.int32).reshape(B, pages)
+    seq_loc = torch.tensor([(int(s) - rank + world - 1) // world for s in seq], dtype=torch.int32)
+    kv_loc = kv[:, rank::world].reshape(B * S_loc, 1, DQK).contiguous()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    d = lambda t: t.to(dev)
+    layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
+                           kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
+                           group_name=dist.group.WORLD.group_name, device=dev)
+    layer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx), d(w_idx), d(q_mla), d(kv_loc)))
+    dist.barrier()
+    for _ in range(3):
+        layer.step(wait_budget_ns=5_000_000_000)
+        torch.cuda.synchronize()
+        layer.check_status()
+        dist.barrier()
+    # oracle on the dequantised global cache (quantisation is per token row, so sharding commutes with it)
+    pk, sf = orc.quant_nvfp4(kraw.reshape(B * S, 128))
+    kd = orc.dequant_fp4(pk, sf, "nvfp4").reshape(B, S, 128)
+    ok = True
+    for b in range(B):
+        sel, o, l = orc.decode_step_ref(q_idx[b].float(), w_idx[b], kd[b], q_mla[b, 0].float(), kv[b].float(),
+                                        int(seq[b]), K, 1 / math.sqrt(DQK), cp=world)
+        n = int(layer.sel_c[b])
+        got = torch.sort(layer.sel_i[b, :n].cpu()).values
+        overlap = len(set(got.tolist()) & set(sel.tolist())) / max(1, sel.numel())
+        ok &= n == sel.numel() and overlap >= 0.999
+        if b % world == rank and overlap == 1.0:
+            ok &= bool((layer.out[b].cpu() - o).abs().max() < 2e-2)
+            ok &= bool((layer.out_lse[b].cpu() - l).abs().max() < 1e-3)
+    # every rank must hold the same selection bit for bit
+    ref_sel = layer.sel_i.clone()
+    dist.broadcast(ref_sel, 0)
+    ok &= bool(torch.equal(ref_sel, layer.sel_i))
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("MP_LAYER_OK" if flag.item() == 1 else "MP_LAYER_FAIL")
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

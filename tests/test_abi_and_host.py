@@ -1,0 +1,141 @@
+"""CPU checks of the C-ABI library (it loads, exports every symbol the header
+declares, rejects bad arguments without touching a GPU), of the import alias,
+and of the multi-rank host logic (gloo, world size 2)."""
+
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mdc.h")).read()
+    return sorted(set(re.findall(r"^\s*(?:int|const char\*)\s+(mdc_\w+)\s*\(", text, flags=re.M)))
+
+
+def test_library_exports_every_declared_symbol():
+    from mega_dsa_cp_b200 import _native as N
+
+    lib = N.lib()
+    declared = _declared_symbols()
+    assert len(declared) >= 16
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/mdc.h but not exported"
+    assert sorted(N.EXPORTS) == declared
+    assert lib.mdc_abi_version() == N.ABI_VERSION
+    assert lib.mdc_status_string(-1).decode() != lib.mdc_status_string(-4).decode()
+
+
+def test_launchers_reject_bad_arguments_without_a_gpu():
+    from mega_dsa_cp_b200 import _native as N
+
+    lib = N.lib()
+    assert lib.mdc_logits_fp4_launch(None, None) == -4
+    p = N.LogitsParams()
+    assert lib.mdc_logits_fp4_launch(C.byref(p), None) == -4          # null pointers
+    p.kv_pages = p.q = p.weights = p.block_table = p.logits = 4096
+    p.fmt, p.q_fmt, p.page_tokens, p.heads, p.q_len = 7, 1, 64, 64, 1
+    assert lib.mdc_logits_fp4_launch(C.byref(p), None) == -3          # unknown format
+    p.fmt, p.page_tokens = N.FMT_MXFP4, 64
+    assert lib.mdc_logits_fp4_launch(C.byref(p), None) == -1          # mxfp4 needs 128-token pages
+    m = N.MergeTopkParams()
+    assert lib.mdc_merge_topk_launch(C.byref(m), None) == -4
+    l = N.LseMergeParams(acc_o=4096, acc_lse=4096, o=4096, rows=1, H=128, D=512, n_slices=17, n_slices_max=17)
+    assert lib.mdc_lse_merge_launch(C.byref(l), None) == -1           # more slices than supported
+    a = N.SparseMlaParams(q=4096, kv_cmp=4096, pt_cmp=4096, k_valid=4096, o=4096, B=1, q_len=1, H=100)
+    assert lib.mdc_sparse_mla_launch(C.byref(a), None) == -1          # heads not a multiple of 64
+    c = N.CompressParams()
+    assert lib.mdc_compress_step_launch(C.byref(c), None) == -4
+    assert lib.mdc_megakernel_launch(None, None) == -4
+    assert lib.mdc_megakernel_threads() == 480 and lib.mdc_megakernel_smem_bytes() > 200 * 1024
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    code = ("import os, sys; sys.path.insert(0, %r); os.environ['MDC_LIB_PATH'] = %r\n"
+            "from mega_dsa_cp_b200 import _native\n"
+            "try:\n    _native.lib()\nexcept _native.MdcError as e:\n    print('LOUD', 'no fallback' in str(e))\n"
+            % (ROOT, str(tmp_path / "nope.so")))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert "LOUD True" in r.stdout, r.stdout + r.stderr
+
+
+def test_reference_import_paths_resolve():
+    import mega_dsa_cp.tiles.logits as a
+    import mega_dsa_cp_b200.tiles.logits as b
+    from mega_dsa_cp.comm.buffers import alloc_arena  # noqa: F401
+    from mega_dsa_cp.events.symm import alloc_event_buffer  # noqa: F401
+    from mega_dsa_cp.tiles.fp4 import make_index_cache, quant_mxfp4  # noqa: F401
+    from mega_dsa_cp.tiles.hca import run_hca_fp8  # noqa: F401
+    from mega_dsa_cp.tiles.lse_merge import run_lse_merge  # noqa: F401
+    from mega_dsa_cp.tiles.merge import run_merge_topk  # noqa: F401
+
+    assert a.run_fp4_paged_mqa_logits is b.run_fp4_paged_mqa_logits
+
+
+def test_package_fp4_helpers_match_oracle():
+    from mega_dsa_cp_b200.tiles import fp4
+    from oracle import dsa_oracle as orc
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(256, 128, generator=g) * torch.logspace(-2, 1.5, 256).unsqueeze(1)
+    for mine, theirs in ((fp4.quant_mxfp4, orc.quant_mxfp4), (fp4.quant_nvfp4, orc.quant_nvfp4)):
+        a, b = mine(x), theirs(x)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    pk, sf = fp4.quant_mxfp4(x)
+    assert torch.equal(fp4.dequant_mxfp4(pk, sf), orc.dequant_fp4(pk, sf, "mxfp4"))
+    pk, sf = fp4.quant_nvfp4(x)
+    assert torch.equal(fp4.dequant_nvfp4(pk, sf), orc.dequant_fp4(pk, sf, "nvfp4"))
+    assert torch.equal(fp4.sf_to_atom(sf[:, :4].contiguous()), orc.sf_to_atom(sf[:, :4].contiguous()))
+    for fmt, P in (("mxfp4", 128), ("nvfp4", 64), ("nvfp4", 128)):
+        f1, _ = fp4.fuse_pages(x, fmt, P)
+        f2, _ = orc.build_index_pages(x, fmt, P)
+        assert torch.equal(f1, f2) and f1.shape[1] == fp4.page_bytes(fmt, P)
+    kv, sfp = fp4.make_index_cache(2, 2, device="cpu", seed=0)
+    assert kv.shape == (4, 8704) and sfp.shape == (4, 128, 4)
+    qp, qsf, qatom, w = fp4.make_q(2, q_len=1, device="cpu")
+    assert qp.shape == (2, 64, 64) and qatom.shape == (2, 512) and w.shape == (2, 64)
+
+
+WORKER = r'''
+import os, sys, json
+sys.path.insert(0, %(root)r)
+import torch, torch.distributed as dist
+from mega_dsa_cp_b200.layer import build_layer_dag, arena_regions
+from mega_dsa_cp_b200.schedule.codegen import codegen_schedule
+from mega_dsa_cp_b200.comm.buffers import layout_regions
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+tasks, events, ops = build_layer_dag(B=6, n_chunks=3, cp=world, heads=128)
+s = codegen_schedule(tasks, events, rank=rank, n_ctas=5, world_size=world, op_of=ops)
+# every rank derives the same event tables; arities differ only by ownership
+mine = torch.tensor(s.arity + s.scopes + [s.n_events], dtype=torch.int64)
+gathered = [torch.zeros_like(mine) for _ in range(world)]
+dist.all_gather(gathered, mine)
+n = s.n_events
+ok = all(torch.equal(g[n:], mine[n:]) for g in gathered)               # scopes and count identical
+part = [4 * b + 3 for b in range(6)]
+for r, g in enumerate(gathered):                                        # part[b] arity only on the owner
+    ok &= all((int(g[e]) > 0) == (b %% world == r) for b, e in enumerate(part))
+offs, per_phase = layout_regions(arena_regions(6, world, 2048))
+ok &= offs["cand"] == 0 and offs["inbox"] %% 256 == 0 and per_phase %% 256 == 0
+n_tasks = sum(1 for t in tasks if t.rank == rank)
+ok &= len(s.topo) == n_tasks
+flag = torch.tensor([1 if ok else 0]); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0: print("HOST_OK" if flag.item() == 1 else "HOST_FAIL")
+dist.destroy_process_group()
+'''
+
+
+def test_layer_dag_two_ranks_gloo(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(WORKER % {"root": ROOT})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", str(script)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert "HOST_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
