@@ -74,11 +74,23 @@ __device__ inline bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of an mbarrier phase.
+__device__ inline bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait on an mbarrier phase.  try_wait itself suspends the thread for a
 // hardware-defined slice, so the loop is not a hot spin; the clock is read only
 // every 64 polls.  Returns false once `budget` clock cycles (about a second by
-// default) have passed without the phase completing.
-__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, long long budget = (1ll << 31)) {
+// default) have passed without the phase completing, or once the block-wide
+// abort flag (optional) is raised by another role.
+__device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, long long budget = (1ll << 31),
+                                 const volatile uint32_t* abort_flag = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   do {
@@ -86,6 +98,49 @@ __device__ inline bool mbar_wait(uint64_t* bar, uint32_t parity, long long budge
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
+    if (abort_flag && *abort_flag) return false;
+  } while (clock64() - t0 < budget);
+  return false;
+}
+
+// Predicated forms for "one lane signals": a predicated instruction instead of a
+// divergent branch keeps the warp converged, which is much cheaper on a path
+// that runs once per pipeline stage.
+__device__ inline void mbar_arrive_if(uint64_t* bar, bool pred) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.u32 p, %1, 0;\n @p mbarrier.arrive.shared::cta.b64 _, [%0];\n}" ::"r"(
+                   smem_u32(bar)),
+               "r"(static_cast<uint32_t>(pred))
+               : "memory");
+}
+
+// Shared-memory progress counters (cheaper to poll than an mbarrier for a
+// thread that sits on the tensor-core issue path): release increment, acquire load.
+__device__ inline void red_release_cta_shared_inc(uint32_t* p) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(p)) : "memory");
+}
+__device__ inline void red_release_cta_shared_inc_if(uint32_t* p, bool pred) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.u32 p, %1, 0;\n @p red.release.cta.shared::cta.add.u32 [%0], 1;\n}" ::"r"(
+                   smem_u32(p)),
+               "r"(static_cast<uint32_t>(pred))
+               : "memory");
+}
+__device__ inline uint32_t ld_acquire_cta_shared_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+// Bounded wait until a shared counter reaches `target` (same give-up rules as mbar_wait).
+__device__ inline bool counter_wait(const uint32_t* p, uint32_t target, long long budget = (1ll << 31),
+                                    const volatile uint32_t* abort_flag = nullptr) {
+  if (ld_acquire_cta_shared_u32(p) >= target) return true;
+  const long long t0 = clock64();
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(20);  // a hot spin would take issue slots from the warps this one waits for
+      if (ld_acquire_cta_shared_u32(p) >= target) return true;
+    }
+    if (abort_flag && *abort_flag) return false;
   } while (clock64() - t0 < budget);
   return false;
 }

@@ -25,23 +25,6 @@ __device__ inline void e2m1x8_to_f16x2(uint32_t w, uint32_t (&out)[4]) {
       : "r"(w));
 }
 
-// 8 packed E2M1 codes -> 4 x f16x2 holding value * 2^-14, element i in the low
-// half and element i+4 in the high half of out[i].  Integer-only: the 3-bit
-// magnitude code placed at bits 11..9 of an fp16 IS value * 2^-14 (codes 0 and 1
-// land on fp16 subnormals 0 and 2^-15), the sign goes to bit 15; nibbles i and
-// i+4 are 16 bits apart, so one shift serves both halves.  The caller
-// multiplies by (block scale * 2^7), which yields value * scale * 2^-7 exactly
-// in fp16 (at most 6 significant bits, magnitudes between 2^-17 and 21) for any
-// UE4M3 scale; the remaining 2^7 is folded into the head weights.
-constexpr uint32_t kF16x2_2p14 = 0x74007400u;
-constexpr uint32_t kF16x2_2p7 = 0x58005800u;
-__device__ inline void e2m1x8_pairs_f16(uint32_t w, uint32_t (&out)[4]) {
-  out[0] = ((w << 12) & 0x80008000u) | ((w << 9) & 0x0E000E00u);
-  out[1] = ((w << 8) & 0x80008000u) | ((w << 5) & 0x0E000E00u);
-  out[2] = ((w << 4) & 0x80008000u) | ((w << 1) & 0x0E000E00u);
-  out[3] = (w & 0x80008000u) | ((w >> 3) & 0x0E000E00u);
-}
-
 // two UE4M3 scale bytes -> f16x2 (byte 0 in the low half)
 __device__ inline uint32_t e4m3x2_to_f16x2(uint16_t two) {
   uint32_t r;
@@ -52,13 +35,6 @@ __device__ inline uint32_t e4m3x2_to_f16x2(uint16_t two) {
 // UE8M0 byte -> fp16 bits of 2^(e-127), replicated in both halves
 __device__ inline uint32_t ue8m0_to_f16x2(uint32_t e) {
   __half h = __float2half_rn(__uint_as_float(e << 23));
-  uint32_t b = __half_as_ushort(h);
-  return b | (b << 16);
-}
-
-// UE8M0 byte -> fp16 bits of 2^(e-127+7), replicated in both halves
-__device__ inline uint32_t ue8m0_to_f16x2_2p7(uint32_t e) {
-  __half h = __float2half_rn(__uint_as_float(min(e + 7u, 254u) << 23));
   uint32_t b = __half_as_ushort(h);
   return b | (b << 16);
 }

@@ -3,34 +3,43 @@
 // writes the fp32 logits row or keeps the chunk's scores in shared memory and
 // emits the exact local top-k.
 //
-// The tile is a four-role pipeline over 128-token stages (14 warps):
+// The tile is a four-role pipeline over 128-token stages:
 //
-//   copy warp (13)     one thread; a page is contiguous in HBM (P x 64 B of
-//                      packed E2M1, then the page's block scales), so one 1-D
-//                      bulk copy (cp.async.bulk + mbarrier) per page fills a
-//                      ring of 8 raw stages in shared memory.
-//   decode warps (0-7) thread i owns half of a token row of the stage (warp w:
-//                      rows 32*(w%4).., dims 64*(w/4)..): reads its 32 B of
-//                      codes and its scales, converts to fp16 with integer
-//                      and fp16-multiply instructions only (see
-//                      e2m1x8_pairs_f16; the conversion unit is far too slow
-//                      for 16 K elements per stage), times the block scale,
-//                      exact, and stores the row into TENSOR MEMORY
-//                      (tcgen05.st) as the A operand of the next MMA; a ring
-//                      of 4 A stages.
-//   issue warp (12)    one thread issues eight tcgen05.mma (M=128 tokens,
+//   copy warp          a page is contiguous in HBM (P x 64 B of packed E2M1,
+//                      then the page's block scales), so one 1-D bulk copy
+//                      (cp.async.bulk + mbarrier) per page fills a ring of 8
+//                      raw stages in shared memory.  Lane l owns one page slot
+//                      of the ring; the lanes poll the "empty" barriers of
+//                      their stages together and refill whatever is free.
+//   decode warps (0-7) two groups of four warps take the even and the odd
+//                      stages.  Thread i of a group owns token row i: it reads
+//                      the row's 64 B of codes (four 16-byte loads in an order
+//                      rotated per lane pair, which makes them bank-conflict
+//                      free) and its scales, converts with cvt.f16x2.e2m1x2,
+//                      multiplies by the block scale (exact in fp16) and stores
+//                      the row into TENSOR MEMORY (tcgen05.st) as the A operand
+//                      of the stage's MMA; a ring of 4 A stages.
+//   issue warp         one thread issues eight tcgen05.mma (M=128 tokens,
 //                      N=64*q_len heads, K=16, fp16 x fp16 -> fp32) per stage,
 //                      A from tensor memory, B = the query block, staged once
 //                      in shared memory in the K-major 128-byte-swizzle layout;
-//                      two accumulator stages in tensor memory.
-//   gate warps (8-11)  thread i reads accumulator row i (tcgen05.ld), applies
-//                      relu and the head weights, reduces over heads and emits
-//                      the token's score.
+//                      4 (q_len 1) or 2 accumulator stages in tensor memory.
+//   gate warps         GG groups of four warps take stages round-robin; thread
+//                      i reads accumulator row i (tcgen05.ld), applies relu and
+//                      the head weights, reduces over heads and emits the
+//                      token's score.
 //
 // Keeping A in tensor memory instead of shared memory matters: the decode
 // output (32 KB per stage) and its re-read by the tensor core would otherwise
 // triple the shared-memory traffic of a kernel that has to sustain one stage
 // per ~400 cycles to follow HBM.
+//
+// What bounds the loop is not arithmetic but the latency of each hand-off
+// (an mbarrier probe or a shared-memory atomic costs a warp 100-200 cycles
+// even when it succeeds at once), so every role probes the barrier of its
+// NEXT stage early, with a non-blocking test whose answer is read one
+// iteration later, and signals with predicated instructions instead of
+// divergent branches.
 //
 // Exactness.  K values (E2M1 x scale) are exact in fp16.  Query rows are
 // rescaled per head by a power of two so that the largest element lands in
@@ -51,19 +60,16 @@
 
 namespace mdc {
 
-#ifndef MDC_EXP
-#define MDC_EXP 0
-#endif
 #ifdef MDC_TRACE
-// Debug builds only: per-role timestamps of block (0,0), [role][tile][begin/end].
-__device__ unsigned long long g_logits_trace[4 * 256 * 2];
-#define MDC_TRACE_AT(role, tile, which)                                                        \
+// Debug builds only: SM-clock timestamps of block (0,0), [role][tile][point].
+__device__ long long g_logits_trace[4 * 256 * 8];
+#define MDC_TRACE_AT(role, tile, point)                                                        \
   do {                                                                                         \
     if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 256)                                    \
-      g_logits_trace[((role) * 256 + (tile)) * 2 + (which)] = global_timer_ns();               \
+      g_logits_trace[((role) * 256 + (tile)) * 8 + (point)] = clock64();                       \
   } while (0)
 #else
-#define MDC_TRACE_AT(role, tile, which) do { } while (0)
+#define MDC_TRACE_AT(role, tile, point) do { } while (0)
 #endif
 
 constexpr int kIdxDim = 128;
@@ -73,8 +79,12 @@ constexpr int kRawStages = 8;    // raw page ring
 constexpr int kAStages = 4;      // decoded-A ring in tensor memory
 constexpr int kTmemCols = 512;
 constexpr int kFusedRegE = 32;   // fused top-k keeps up to 256 * 32 scores per query token in registers
-constexpr int kLogitsThreads = 480;  // 8 decode + 4 gate + 2 issue + 1 copy warps
-constexpr int kGateWarp0 = 8, kIssueWarp = 12, kIssueWarps = 2, kCopyWarp = 14;
+constexpr int kGateWarp0 = 8;    // warps 0-7 decode
+
+// Warp layout for GG gate groups: 8 decode, 4*GG gate, issue, copy.
+constexpr int logits_threads(int gg) { return (8 + 4 * gg + 2) * 32; }
+constexpr int kLogitsGateGroups = 2;                               // the stand-alone kernel
+constexpr int kLogitsThreads = logits_threads(kLogitsGateGroups);  // 576
 
 template <int FMT, int PAGE>
 struct IdxPage {
@@ -100,17 +110,17 @@ __host__ __device__ inline LogitsSmem logits_smem_layout(int q_len, int chunk_to
   off += kRawStages * IdxPage<FMT, PAGE>::kStageBytes;
   off = static_cast<int>(align_up(off, 128));
   L.bars = off;
-  off += (2 * kRawStages + 2 * kAStages + 2 * 4) * 8;
-  L.misc = off;  // [0] tensor-memory base, [1] abort flag
-  off += 16;
+  off += (2 * kRawStages + kAStages) * 8;
+  L.misc = off;  // [0] tensor-memory base, [1] abort flag, [4..7] and [8..11] progress counters
+  off += 64;
   L.wsc = off;
   off += q_len * kIdxHeads * 4;
   off = static_cast<int>(align_up(off, 16));
   L.sel = off;
   off += static_cast<int>(align_up(sizeof(SelectScratch) > sizeof(RegSelectScratch<kFusedRegE>) ? sizeof(SelectScratch)
                                                                                              : sizeof(RegSelectScratch<kFusedRegE>), 16));
-  L.page_ok = off;  // one byte per page of the chunk
-  off += static_cast<int>(align_up(chunk_tokens / PAGE + 4, 16));
+  L.page_ok = off;  // page id per page of the chunk (-1 = not usable)
+  off += static_cast<int>(align_up((chunk_tokens / PAGE + 4) * 4, 16));
   L.scores = off;
   if (fused) off += q_len * chunk_tokens * 4;
   L.total = static_cast<int>(align_up(off, 128));
@@ -120,9 +130,7 @@ __host__ __device__ inline LogitsSmem logits_smem_layout(int q_len, int chunk_to
 // Prologue: the request's query rows as prescaled fp16 in the UMMA B layout,
 // and the matching head weights (halved: the gate computes (x + |x|) * w/2).
 // Row r of the request = head r % 64 of query token r / 64.  Called by warps
-// 0..7; a half-warp stages one row, lane l of it the dims 8l..8l+7, stored in
-// the order 0,4,1,5,2,6,3,7 -- the order in which the decode warps emit the
-// elements of a packed 32-bit word (element i is paired with element i+4).
+// 0..7; a half-warp stages one row, lane l of it the dims 8l..8l+7.
 template <int T>
 __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, unsigned char* qb, float* wsc) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -166,10 +174,10 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
     const float inv = __uint_as_float(static_cast<uint32_t>(127 - up) << 23);
     uint4 out;
     {
-      __half2 h0 = __floats2half2_rn(v[0] * scale, v[4] * scale);
-      __half2 h1 = __floats2half2_rn(v[1] * scale, v[5] * scale);
-      __half2 h2 = __floats2half2_rn(v[2] * scale, v[6] * scale);
-      __half2 h3 = __floats2half2_rn(v[3] * scale, v[7] * scale);
+      __half2 h0 = __floats2half2_rn(v[0] * scale, v[1] * scale);
+      __half2 h1 = __floats2half2_rn(v[2] * scale, v[3] * scale);
+      __half2 h2 = __floats2half2_rn(v[4] * scale, v[5] * scale);
+      __half2 h3 = __floats2half2_rn(v[6] * scale, v[7] * scale);
       out.x = *reinterpret_cast<uint32_t*>(&h0);
       out.y = *reinterpret_cast<uint32_t*>(&h1);
       out.z = *reinterpret_cast<uint32_t*>(&h2);
@@ -178,22 +186,25 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
     // dims 8*hl .. 8*hl+7: K-half = hl / 8, 16-byte chunk = hl % 8
     unsigned char* dst = qb + (hl >> 3) * (N * 128) + row * 128 + (((hl & 7) ^ (row & 7)) << 4);
     *reinterpret_cast<uint4*>(dst) = out;
-    // 0.5 for the (x + |x|) form of relu, 2^7 for the factor the decode warps leave out
-    if (hl == 0) wsc[row] = 64.f * p.weights[static_cast<int64_t>(b) * N + row] * inv;
+    // 0.5 for the (x + |x|) form of relu
+    if (hl == 0) wsc[row] = 0.5f * p.weights[static_cast<int64_t>(b) * N + row] * inv;
   }
 }
 
 // The tile.  smem: dynamic shared memory base (1024 B aligned), laid out by
-// logits_smem_layout.  All kLogitsThreads threads of the block call it.
-template <int FMT, int PAGE, int T>
+// logits_smem_layout.  All logits_threads(GG) threads of the block call it.
+template <int FMT, int PAGE, int T, int GG>
 __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsigned char* smem) {
   using PG = IdxPage<FMT, PAGE>;
   constexpr int N = T * kIdxHeads;
-  // accumulator ring and MMA interleave: dependent MMAs on one accumulator are
-  // latency bound at N = 64, so two stages are issued interleaved when q_len = 1
-  constexpr int kAccStages = (T == 1) ? 4 : 2;
-  constexpr uint32_t kAccBase = 0, kABase = kAccStages * N;  // tensor-memory columns
+  constexpr int kThreads = logits_threads(GG);
+  constexpr int kIssueWarp = kGateWarp0 + 4 * GG, kCopyWarp = kIssueWarp + 1;
+  // Tensor memory: kAccSt accumulator stages of N columns, then kAStages decoded-A
+  // stages of 64 columns (128 fp16 per row): 512 columns for q_len 1 and 2.
+  constexpr int kAccSt = 4 / T;
+  constexpr uint32_t kAccBase = 0, kABase = kAccSt * N;
   static_assert(kABase + kAStages * 64 <= kTmemCols, "tensor memory over-subscribed");
+  static_assert(kRawStages * PG::kTilePages <= 32, "one copy-warp lane per page of the raw ring");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool fused = p.cand_v != nullptr;
   const int chunk_tokens = p.blocks_per_chunk * PAGE;
@@ -203,13 +214,12 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   unsigned char* ring = smem + L.ring;
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem + L.bars);
   uint64_t* raw_empty = raw_full + kRawStages;
-  uint64_t* a_full = raw_empty + kRawStages;
-  uint64_t* a_empty = a_full + kAStages;
-  uint64_t* acc_full = a_empty + kAStages;
-  uint64_t* acc_empty = acc_full + 4;
+  uint64_t* mma_done = raw_empty + kRawStages;  // [kAStages]: stage t % 4 finished on the tensor core
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L.misc);
   volatile uint32_t* abort_flag = misc + 1;
-  uint8_t* page_ok = smem + L.page_ok;
+  uint32_t* a_cnt = misc + 4;    // [kAStages] decode warps that finished writing the A stage (monotonic)
+  uint32_t* acc_cnt = misc + 8;  // [kAccSt] gate warps that finished reading the accumulator stage (monotonic)
+  int32_t* page_id = reinterpret_cast<int32_t*>(smem + L.page_ok);
   float* wsc = reinterpret_cast<float*>(smem + L.wsc);
   SelectScratch& sel = *reinterpret_cast<SelectScratch*>(smem + L.sel);
   float* scores = reinterpret_cast<float*>(smem + L.scores);
@@ -222,24 +232,18 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   int blk_end = min(blk0 + p.blocks_per_chunk, p.max_pages);
   if (fused) blk_end = min(blk_end, ceil_div(limit, PAGE));
   const int n_pages = max(0, blk_end - blk0);
-  const int n_tiles = ceil_div(n_pages, PG::kTilePages);
+  const int n_tiles = ceil_div(n_pages, PG::kTilePages);  // pipeline stages of this block
   const int32_t* bt = p.block_table + static_cast<int64_t>(b) * p.max_pages;
+  constexpr long long kBudget = 1ll << 31;  // clock cycles a role waits before it gives up
 
   // ---------------- prologue
   if (tid == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 8);
+      mbar_init(&raw_empty[s], 4);
     }
-    for (int s = 0; s < kAStages; ++s) {
-      mbar_init(&a_full[s], 8);
-      mbar_init(&a_empty[s], 1);
-    }
-    for (int s = 0; s < 4; ++s) {
-      mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], 4);
-    }
-    misc[1] = 0;
+    for (int s = 0; s < kAStages; ++s) mbar_init(&mma_done[s], 1);
+    for (int i = 1; i < 16; ++i) misc[i] = 0;
     mbar_fence_init();
   }
   if (warp == kIssueWarp) umma::tmem_alloc(misc, kTmemCols);
@@ -247,11 +251,16 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     logits_stage_query<T>(p, b, qb, wsc);
     fence_proxy_async_smem();  // the tensor core reads the query block through the async proxy
   }
-  for (int i = tid; i < n_pages; i += kLogitsThreads) {
-    const int32_t id = bt[blk0 + i];
-    const bool ok = id >= 0 && id < p.num_pages;
-    if (!ok) report_failure(p.status, MDC_DEV_BAD_INDEX, id, blk0 + i, 0, 0);
-    page_ok[i] = ok;
+  for (int i = tid; i < n_pages + 4; i += kThreads) {  // (+4: the slots behind the last page read as unusable)
+    int32_t id = -1;
+    if (i < n_pages) {
+      id = bt[blk0 + i];
+      if (id < 0 || id >= p.num_pages) {
+        report_failure(p.status, MDC_DEV_BAD_INDEX, id, blk0 + i, 0, 0);
+        id = -1;
+      }
+    }
+    page_id[i] = id;
   }
   umma::fence_before_sync();
   __syncthreads();
@@ -265,177 +274,209 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   };
 
   if (warp == kCopyWarp) {
-    // ---------------- copy warp
-    if (lane == 0) {
-      for (int tile = 0; tile < n_tiles && !*abort_flag; ++tile) {
-        const int s = tile % kRawStages;
-        if (tile >= kRawStages && !mbar_wait(&raw_empty[s], ((tile / kRawStages) - 1) & 1)) {
-          give_up(0, tile);
-          break;
-        }
-        MDC_TRACE_AT(0, tile, 0);
-        uint32_t bytes = 0;
+    // ---------------- copy warp: lane l owns page l % kTilePages of raw stage l / kTilePages.
+    // The lanes poll their stages' "empty" barriers together without blocking and every lane
+    // whose stage is free issues its page's bulk copy in the same instruction, so the ring is
+    // refilled in whatever order the decode warps release it and no single thread serialises
+    // the address arithmetic of all pages.
+    const int s = lane / PG::kTilePages, pp = lane % PG::kTilePages;
+    int tile = (s < kRawStages) ? s : n_tiles;
+    long long t_last = clock64();
+    while (__any_sync(0xffffffffu, tile < n_tiles) && !*abort_flag) {
+      bool ready = false;
+      if (tile < n_tiles) ready = tile < kRawStages || mbar_test(&raw_empty[s], ((tile / kRawStages) - 1) & 1);
+      ready = __shfl_sync(0xffffffffu, ready, lane - pp);  // the lanes of a stage act on one answer
+      if (ready) {
+        const int i0 = tile * PG::kTilePages;
+        if (pp == 0) {
+          MDC_TRACE_AT(0, tile, 0);
+          uint32_t bytes = 0;
 #pragma unroll
-        for (int pp = 0; pp < PG::kTilePages; ++pp) {
-          const int i = tile * PG::kTilePages + pp;
-          if (i < n_pages && page_ok[i]) bytes += PG::kBytes;
+          for (int k = 0; k < PG::kTilePages; ++k) bytes += page_id[i0 + k] >= 0 ? PG::kBytes : 0;
+          if (bytes == 0) mbar_arrive(&raw_full[s]);
+          else mbar_expect_tx(&raw_full[s], bytes);
         }
-        if (bytes == 0 || MDC_EXP == 4) {
-          mbar_arrive(&raw_full[s]);
-          continue;
+        const int32_t id = page_id[i0 + pp];
+        if (id >= 0) {
+          bulk_g2s(ring + s * PG::kStageBytes + pp * PG::kBytes, p.kv_pages + static_cast<int64_t>(id) * PG::kBytes,
+                   PG::kBytes, &raw_full[s]);
         }
-        mbar_expect_tx(&raw_full[s], bytes);
-#pragma unroll
-        for (int pp = 0; pp < PG::kTilePages; ++pp) {
-          const int i = tile * PG::kTilePages + pp;
-          if (i < n_pages && page_ok[i]) {
-            bulk_g2s(ring + s * PG::kStageBytes + pp * PG::kBytes,
-                     p.kv_pages + static_cast<int64_t>(bt[blk0 + i]) * PG::kBytes, PG::kBytes, &raw_full[s]);
-          }
-        }
-        MDC_TRACE_AT(0, tile, 1);
+        if (pp == 0) MDC_TRACE_AT(0, tile, 1);
+        tile += kRawStages;
+      }
+      if (__any_sync(0xffffffffu, ready)) {
+        t_last = clock64();
+        continue;
+      }
+      __nanosleep(64);  // nothing to refill: do not spin hot beside the decode warps
+      if (clock64() - t_last > kBudget) {
+        if (lane == 0) give_up(0, tile);
+        break;
       }
     }
-  } else if (warp >= kIssueWarp && warp < kIssueWarp + kIssueWarps) {
-    // ---------------- issue warps (tiles are dealt round-robin to them): all lanes walk the loop together, one elected
-    // lane issues (the tensor-core instructions take warp-uniform operands)
+  } else if (warp == kIssueWarp) {
+    // ---------------- issue warp: all lanes walk the loop together, one elected lane issues
+    // (the tensor-core instructions take warp-uniform operands)
     constexpr uint32_t idesc = umma::idesc_f16(kTileTok, N, 0);
     const uint32_t qb_u = smem_u32(qb);
     uint64_t bdesc[8];
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) bdesc[kk] = umma::smem_desc_sw128(qb_u + (kk >> 2) * (N * 128) + (kk & 3) * 32);
-    for (int tile = warp - kIssueWarp; tile < n_tiles && !*abort_flag; tile += kIssueWarps) {
-      const int a = tile % kAStages, c = tile % kAccStages;
-      bool ok = mbar_wait(&a_full[a], (tile / kAStages) & 1);
-      if (ok && tile >= kAccStages) ok = mbar_wait(&acc_empty[c], ((tile / kAccStages) - 1) & 1);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int a = tile % kAStages, c = tile % kAccSt;
+      if (lane == 0) MDC_TRACE_AT(2, tile, 0);
+      // progress counters instead of mbarriers here: an mbarrier wait costs this
+      // thread ~150 cycles even when the phase is long complete
+      bool ok = counter_wait(&a_cnt[a], 4u * (tile / kAStages + 1), kBudget, abort_flag);
+      if (lane == 0) MDC_TRACE_AT(2, tile, 1);
+      if (ok && tile >= kAccSt) ok = counter_wait(&acc_cnt[c], 4u * (tile / kAccSt), kBudget, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) give_up(1, tile);
         break;
       }
       umma::fence_after_sync();
       if (umma::elect_one()) {
-        MDC_TRACE_AT(2, tile, 0);
+        MDC_TRACE_AT(2, tile, 2);
         umma::mma_f16_ts_x8(tmem + kAccBase + c * N, tmem + kABase + a * 64, bdesc, idesc);
-        umma::commit(&a_empty[a]);
-        umma::commit(&acc_full[c]);
-        MDC_TRACE_AT(2, tile, 1);
+        umma::commit(&mma_done[a]);
+        MDC_TRACE_AT(2, tile, 3);
       }
       __syncwarp();
     }
   } else if (warp < kWarps) {
-    // ---------------- decode warps: thread = half a token row of the stage
-    const int quad = warp & 3, dh = warp >> 2;  // TMEM lane quadrant, dim half (0: dims 0..63)
+    // ---------------- decode warps: thread = token row; warps 0-3 take the even stages, 4-7 the odd ones
+    const int quad = warp & 3, grp = warp >> 2;  // TMEM lane quadrant, stage parity
     const int row = quad * 32 + lane;
     const int pp = row / PAGE, tok = row % PAGE;
-    int prev_a = -1;
-    for (int tile = 0; tile < n_tiles && !*abort_flag; ++tile) {
+    const int rot = (lane >> 1) & 3;  // chunk rotation: lanes 2m, 2m+1 start at chunk m (no bank conflicts)
+    const uint32_t t_row = tmem + (static_cast<uint32_t>(quad * 32) << 16) + kABase;
+    // answers of the early probes for the next stage (true = known complete)
+    bool raw_ok = false, a_ok = true;
+    for (int tile = grp; tile < n_tiles; tile += 2) {
       const int s = tile % kRawStages, a = tile % kAStages;
-      if (!mbar_wait(&raw_full[s], (tile / kRawStages) & 1)) {
+      if (tid == 0) MDC_TRACE_AT(1, tile, 0);
+      if (!raw_ok && !mbar_wait(&raw_full[s], (tile / kRawStages) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(3, tile);
         break;
       }
-      if (tile >= kAStages && !mbar_wait(&a_empty[a], ((tile / kAStages) - 1) & 1)) {
+      if (tid == 0) MDC_TRACE_AT(1, tile, 1);
+      const unsigned char* pg = ring + s * PG::kStageBytes + pp * PG::kBytes;
+      const bool ok = page_id[tile * PG::kTilePages + pp] >= 0;
+      uint4 d[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        d[j] = ok ? *reinterpret_cast<const uint4*>(pg + tok * 64 + 16 * ((j + rot) & 3)) : make_uint4(0, 0, 0, 0);
+      uint2 raw_sf = make_uint2(0u, 0u);  // the row's block scales
+      if (ok) {
+        if (FMT == MDC_FMT_NVFP4) raw_sf = *reinterpret_cast<const uint2*>(pg + PG::kData + tok * 8);
+        else raw_sf.x = *reinterpret_cast<const uint32_t*>(pg + PG::kData + (tok % 32) * 16 + (tok / 32) * 4);
+      }
+      // probe the barriers of this group's next stage now; the answers are read at the top of the next iteration
+      const int nt = tile + 2;
+      bool n_raw = false, n_a = true;
+      if (nt < n_tiles) {
+        n_raw = mbar_test(&raw_full[nt % kRawStages], (nt / kRawStages) & 1);
+        if (nt >= kAStages) n_a = mbar_test(&mma_done[nt % kAStages], ((nt / kAStages) - 1) & 1);
+      }
+      if (!a_ok && !mbar_wait(&mma_done[a], ((tile / kAStages) - 1) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(4, tile);
         break;
       }
       umma::fence_after_sync();
-      if (tid == 0) MDC_TRACE_AT(1, tile, 0);
-      const unsigned char* pg = ring + s * PG::kStageBytes + pp * PG::kBytes;
-      const int pidx = tile * PG::kTilePages + pp;
-      const bool ok = pidx < n_pages && page_ok[pidx];
-      uint32_t sc[4];  // fp16x2 block scale of each 16-dim group of this half row, times 2^7
-      if (FMT == MDC_FMT_NVFP4) {
-        const uint32_t raw = ok ? *reinterpret_cast<const uint32_t*>(pg + PG::kData + tok * 8 + 4 * dh) : 0u;
-        const uint32_t x0 = hmul2_u32(e4m3x2_to_f16x2(static_cast<uint16_t>(raw & 0xffff)), kF16x2_2p7);
-        const uint32_t x1 = hmul2_u32(e4m3x2_to_f16x2(static_cast<uint16_t>(raw >> 16)), kF16x2_2p7);
-        sc[0] = bcast_lo(x0); sc[1] = bcast_hi(x0); sc[2] = bcast_lo(x1); sc[3] = bcast_hi(x1);
-      } else {
-        const uint32_t raw =
-            ok ? *reinterpret_cast<const uint16_t*>(pg + PG::kData + (tok % 32) * 16 + (tok / 32) * 4 + 2 * dh) : 0u;
-        sc[0] = sc[1] = ue8m0_to_f16x2_2p7(raw & 0xff);
-        sc[2] = sc[3] = ue8m0_to_f16x2_2p7(raw >> 8);
+      if (tid == 0) MDC_TRACE_AT(1, tile, 2);
+      // the raw stage is in registers: hand it back to the copy warp
+      __syncwarp();
+      mbar_arrive_if(&raw_empty[s], lane == 0);
+      if (tid == 0) MDC_TRACE_AT(1, tile, 3);
+      // undo the rotation in registers (the tensor-memory store takes one column address per
+      // warp, so chunk k has to sit in the same register of every lane): two select stages
+      if (rot & 1) {
+        const uint4 t = d[3];
+        d[3] = d[2]; d[2] = d[1]; d[1] = d[0]; d[0] = t;
       }
-      const uint32_t t_row = tmem + (static_cast<uint32_t>(quad * 32) << 16) + kABase + a * 64 + 32 * dh;
-      uint32_t out[2][16];
+      if (rot & 2) {
+        uint4 t = d[0]; d[0] = d[2]; d[2] = t;
+        t = d[1]; d[1] = d[3]; d[3] = t;
+      }
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {  // 16-byte chunk j of the half row = 32 dims = 16 columns
-        uint4 d = (ok && MDC_EXP != 2 && MDC_EXP != 3) ? *reinterpret_cast<const uint4*>(pg + tok * 64 + 32 * dh + 16 * j) : make_uint4(tile, 0, 0, 0);
-        const uint32_t w4[4] = {d.x, d.y, d.z, d.w};
+      for (int j = 0; j < 4; ++j) {  // 16-byte chunk j = 32 dims = 16 columns
+        uint32_t s_lo, s_hi;  // fp16x2 block scale of dims 0-15 and 16-31 of the chunk
+        if (FMT == MDC_FMT_NVFP4) {
+          const uint32_t two = (j & 2 ? raw_sf.y : raw_sf.x) >> (16 * (j & 1));  // scale bytes 2j, 2j+1
+          const uint32_t x = e4m3x2_to_f16x2(static_cast<uint16_t>(two & 0xffff));
+          s_lo = bcast_lo(x);
+          s_hi = bcast_hi(x);
+        } else {
+          s_lo = s_hi = ue8m0_to_f16x2((raw_sf.x >> (8 * j)) & 0xff);
+        }
+        const uint32_t w4[4] = {d[j].x, d[j].y, d[j].z, d[j].w};
+        uint32_t out[16];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t s16 = sc[2 * j + (q4 >> 1)];
           uint32_t e[4];
-          if (MDC_EXP == 2 || MDC_EXP == 3) { e[0] = e[1] = e[2] = e[3] = w4[q4]; } else
-          e2m1x8_pairs_f16(w4[q4], e);  // e[i] = elements (i, i+4) of the word, times 2^-14
+          e2m1x8_to_f16x2(w4[q4], e);  // e[i] = elements (2i, 2i+1) of the word
 #pragma unroll
-          for (int i = 0; i < 4; ++i) out[j][4 * q4 + i] = hmul2_u32(e[i], s16);
+          for (int i = 0; i < 4; ++i) out[4 * q4 + i] = hmul2_u32(e[i], q4 < 2 ? s_lo : s_hi);
         }
+        umma::tmem_st16(t_row + a * 64 + 16 * j, out);
       }
-      // the raw stage is consumed: hand it back before touching tensor memory
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[s]);
-      // stores of the previous stage were issued one iteration ago: retire them now
-      if (prev_a >= 0) {
-        umma::wait_st();
-        umma::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[prev_a]);
-      }
-      if (MDC_EXP != 3) {
-      umma::tmem_st16(t_row, out[0]);
-      umma::tmem_st16(t_row + 16, out[1]);
-      }
-      prev_a = a;
-      if (tid == 0) MDC_TRACE_AT(1, tile, 1);
-    }
-    if (prev_a >= 0) {
+      if (tid == 0) MDC_TRACE_AT(1, tile, 4);
+      // publish the stage as soon as the stores have landed: the tensor core works on it while
+      // this group decodes its next stage into another A stage
       umma::wait_st();
       umma::fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_full[prev_a]);
+      red_release_cta_shared_inc_if(&a_cnt[a], lane == 0);
+      if (tid == 0) MDC_TRACE_AT(1, tile, 5);
+      raw_ok = n_raw;
+      a_ok = n_a;
     }
   } else {
-    // ---------------- gate warps: thread = token row of the stage
-    const int q = warp - kGateWarp0;
-    const int row = q * 32 + lane;
-    for (int tile = 0; tile < n_tiles && !*abort_flag; ++tile) {
-      const int c = tile % kAccStages;
-      if (!mbar_wait(&acc_full[c], (tile / kAccStages) & 1)) {
+    // ---------------- gate warps: group gg takes the stages gg, gg + GG, ...; thread = token row
+    const int q = (warp - kGateWarp0) & 3, gg = (warp - kGateWarp0) >> 2;
+    const uint32_t t_base = tmem + (static_cast<uint32_t>(q * 32) << 16) + kAccBase;
+    bool done_ok = false;
+    for (int tile = gg; tile < n_tiles; tile += GG) {
+      const int c = tile % kAccSt;
+      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 0);
+      if (!done_ok && !mbar_wait(&mma_done[tile % kAStages], (tile / kAStages) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(5, tile);
         break;
       }
       umma::fence_after_sync();
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 0);
-      const uint32_t t_row = tmem + (static_cast<uint32_t>(q * 32) << 16) + kAccBase + c * N;
+      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 1);
+      const int nt = tile + GG;
+      bool n_done = false;
+      if (nt < n_tiles) n_done = mbar_test(&mma_done[nt % kAStages], (nt / kAStages) & 1);
       float score[T];
 #pragma unroll
-      for (int t = 0; t < T && MDC_EXP != 1; ++t) {
+      for (int t = 0; t < T; ++t) {
+        uint32_t v0[32], v1[32];
+        umma::tmem_ld32(t_base + c * N + t * kIdxHeads, v0);
+        umma::tmem_ld32(t_base + c * N + t * kIdxHeads + 32, v1);
+        umma::wait_ld();
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        const float4* w4 = reinterpret_cast<const float4*>(wsc + t * kIdxHeads);
 #pragma unroll
-        for (int hgrp = 0; hgrp < 2; ++hgrp) {
-          uint32_t v[32];
-          umma::tmem_ld32(t_row + t * kIdxHeads + hgrp * 32, v);
-          umma::wait_ld();
-          const float4* w4 = reinterpret_cast<const float4*>(wsc + t * kIdxHeads + hgrp * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 w = w4[i];
-            const float x0 = __uint_as_float(v[4 * i + 0]), x1 = __uint_as_float(v[4 * i + 1]);
-            const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
-            // x + |x| is exactly 0 or 2x; the weighted sums run as packed fp32 pairs
-            ffma2(s0, s1, x0 + fabsf(x0), x1 + fabsf(x1), w.x, w.y);
-            ffma2(s2, s3, x2 + fabsf(x2), x3 + fabsf(x3), w.z, w.w);
-          }
+        for (int i = 0; i < 16; ++i) {
+          const float4 w = w4[i];
+          const uint32_t* v = i < 8 ? v0 + 4 * i : v1 + 4 * (i - 8);
+          const float x0 = __uint_as_float(v[0]), x1 = __uint_as_float(v[1]);
+          const float x2 = __uint_as_float(v[2]), x3 = __uint_as_float(v[3]);
+          // x + |x| is exactly 0 or 2x; the weighted sums run as packed fp32 pairs
+          ffma2(s0, s1, x0 + fabsf(x0), x1 + fabsf(x1), w.x, w.y);
+          ffma2(s2, s3, x2 + fabsf(x2), x3 + fabsf(x3), w.z, w.w);
         }
         score[t] = (s0 + s1) + (s2 + s3);
       }
+      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 2);
       umma::fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[c]);
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 1);
-      const int local = tile * kTileTok + row;  // position inside the chunk
+      red_release_cta_shared_inc_if(&acc_cnt[c], lane == 0);
+      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 3);
+      const int local = tile * kTileTok + q * 32 + lane;  // position inside the chunk
       if (local < n_pages * PAGE) {
-        const bool ok = page_ok[local / PAGE];
+        const bool ok = page_id[local / PAGE] >= 0;
 #pragma unroll
         for (int t = 0; t < T; ++t) {
           const float val = ok ? score[t] : neg_inf;
@@ -446,6 +487,8 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
           }
         }
       }
+      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 4);
+      done_ok = n_done;
     }
   }
 
@@ -456,7 +499,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   const bool failed = *abort_flag != 0;
   if (warp == kIssueWarp) umma::tmem_dealloc(tmem, kTmemCols);
   if (tid == 0) {  // the shared memory is reused by the next task of a persistent block
-    for (int i = 0; i < 2 * kRawStages + 2 * kAStages + 2 * 4; ++i) mbar_inval(raw_full + i);
+    for (int i = 0; i < 2 * kRawStages + kAStages; ++i) mbar_inval(raw_full + i);
   }
   if (warp >= kWarps || failed) return;
 

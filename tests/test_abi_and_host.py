@@ -53,7 +53,7 @@ def test_launchers_reject_bad_arguments_without_a_gpu():
     c = N.CompressParams()
     assert lib.mdc_compress_step_launch(C.byref(c), None) == -4
     assert lib.mdc_megakernel_launch(None, None) == -4
-    assert lib.mdc_megakernel_threads() == 480 and lib.mdc_megakernel_smem_bytes() > 200 * 1024
+    assert lib.mdc_megakernel_threads() in (448, 480) and lib.mdc_megakernel_smem_bytes() > 200 * 1024
 
 
 def test_missing_library_fails_loudly(tmp_path):
