@@ -15,7 +15,6 @@ namespace mdc {
 
 constexpr int kBlockThreads = 256;   // every tile's worker part is written for 8 warps (warps 0..7)
 constexpr int kWarps = kBlockThreads / 32;
-constexpr int kLaunchThreads = 320;  // blocks that drive tcgen05 add an issue warp and a copy warp
 
 // Barrier among the 256 worker threads only (warps 0..7); blocks may carry
 // extra service warps that never join it.

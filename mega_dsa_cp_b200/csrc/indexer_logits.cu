@@ -8,7 +8,7 @@ __global__ void __launch_bounds__(kLogitsThreads, 1) logits_kernel(const __grid_
   extern __shared__ unsigned char smem_raw[];
   // the UMMA operand block wants a 1024-byte aligned base
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  logits_tile<FMT, PAGE, T, kLogitsGateGroups>(p, blockIdx.y, blockIdx.x, smem);
+  logits_tile<FMT, PAGE, T, kLogitsDecodeGroups, kLogitsGateGroups>(p, blockIdx.y, blockIdx.x, smem);
 }
 
 template <int FMT, int PAGE, int T>

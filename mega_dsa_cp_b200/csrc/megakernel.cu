@@ -20,7 +20,7 @@
 
 namespace mdc {
 
-constexpr int kMegaThreads = logits_threads(1);  // one gate group: leaves 128 registers per thread to the attention op
+constexpr int kMegaThreads = logits_threads(2, 1);  // one gate group: leaves 128 registers per thread to the attention op
 constexpr int kStagedWords = 128;  // queue rows up to this length are staged in shared memory
 constexpr int kMegaTileSmem = MlaSmem<576>::kTotal;  // the largest tile
 
@@ -74,7 +74,7 @@ __device__ inline int compact_local_ids(const int32_t* ids, int n, int cp, int r
 // ------------------------------------------------------------------ layer ops
 template <int FMT, int PAGE>
 __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned char* smem) {
-  logits_tile<FMT, PAGE, 1, 1>(p.layer.logits, b, chunk, smem);
+  logits_tile<FMT, PAGE, 1, 2, 1>(p.layer.logits, b, chunk, smem);
 }
 
 // chunk candidate lists of sequence b -> this rank's top-k, written into the

@@ -76,15 +76,14 @@ constexpr int kIdxDim = 128;
 constexpr int kIdxHeads = 64;
 constexpr int kTileTok = 128;    // tokens per pipeline stage (= UMMA M)
 constexpr int kRawStages = 8;    // raw page ring
-constexpr int kAStages = 4;      // decoded-A ring in tensor memory
+constexpr int kAStages = 6;      // decoded-A ring in tensor memory (at most)
 constexpr int kTmemCols = 512;
 constexpr int kFusedRegE = 32;   // fused top-k keeps up to 256 * 32 scores per query token in registers
-constexpr int kGateWarp0 = 8;    // warps 0-7 decode
 
-// Warp layout for GG gate groups: 8 decode, 4*GG gate, issue, copy.
-constexpr int logits_threads(int gg) { return (8 + 4 * gg + 2) * 32; }
-constexpr int kLogitsGateGroups = 2;                               // the stand-alone kernel
-constexpr int kLogitsThreads = logits_threads(kLogitsGateGroups);  // 576
+// Warp layout for DG decode groups and GG gate groups: 4*DG decode, 4*GG gate, issue, copy.
+constexpr int logits_threads(int dg, int gg) { return (4 * dg + 4 * gg + 2) * 32; }
+constexpr int kLogitsDecodeGroups = 2, kLogitsGateGroups = 2;                      // the stand-alone kernel
+constexpr int kLogitsThreads = logits_threads(kLogitsDecodeGroups, kLogitsGateGroups);  
 
 template <int FMT, int PAGE>
 struct IdxPage {
@@ -111,7 +110,7 @@ __host__ __device__ inline LogitsSmem logits_smem_layout(int q_len, int chunk_to
   off = static_cast<int>(align_up(off, 128));
   L.bars = off;
   off += (2 * kRawStages + kAStages) * 8;
-  L.misc = off;  // [0] tensor-memory base, [1] abort flag, [4..7] and [8..11] progress counters
+  L.misc = off;  // [0] tensor-memory base, [1] abort flag, [4..9] and [10..11] progress counters
   off += 64;
   L.wsc = off;
   off += q_len * kIdxHeads * 4;
@@ -193,17 +192,22 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
 
 // The tile.  smem: dynamic shared memory base (1024 B aligned), laid out by
 // logits_smem_layout.  All logits_threads(GG) threads of the block call it.
-template <int FMT, int PAGE, int T, int GG>
+template <int FMT, int PAGE, int T, int DG, int GG>
 __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsigned char* smem) {
   using PG = IdxPage<FMT, PAGE>;
   constexpr int N = T * kIdxHeads;
-  constexpr int kThreads = logits_threads(GG);
-  constexpr int kIssueWarp = kGateWarp0 + 4 * GG, kCopyWarp = kIssueWarp + 1;
-  // Tensor memory: kAccSt accumulator stages of N columns, then kAStages decoded-A
-  // stages of 64 columns (128 fp16 per row): 512 columns for q_len 1 and 2.
-  constexpr int kAccSt = 4 / T;
+  constexpr int kThreads = logits_threads(DG, GG);
+  constexpr int kGateWarp0 = 4 * DG, kIssueWarp = kGateWarp0 + 4 * GG, kCopyWarp = kIssueWarp + 1;
+  // Tensor memory: two accumulator stages of N columns (a gate warp frees its stage as soon as
+  // the row is in registers), then kASt decoded-A stages of 64 columns (128 fp16 per row):
+  // 512 columns for q_len 1 and 2.
+  constexpr int kAccSt = 2;
+  constexpr int kASt = (T == 1) ? 6 : 4;
   constexpr uint32_t kAccBase = 0, kABase = kAccSt * N;
-  static_assert(kABase + kAStages * 64 <= kTmemCols, "tensor memory over-subscribed");
+  static_assert(kABase + kASt * 64 <= kTmemCols && kASt <= kAStages && kASt > DG, "tensor memory over-subscribed");
+  // A group probes the barriers of its next stage one iteration early with a parity test; the
+  // answer is only unambiguous if the stage's previous user was the same group.
+  static_assert(kRawStages % DG == 0 && kASt % DG == 0 && kASt % GG == 0, "ring sizes must be multiples of the group counts");
   static_assert(kRawStages * PG::kTilePages <= 32, "one copy-warp lane per page of the raw ring");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool fused = p.cand_v != nullptr;
@@ -218,7 +222,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + L.misc);
   volatile uint32_t* abort_flag = misc + 1;
   uint32_t* a_cnt = misc + 4;    // [kAStages] decode warps that finished writing the A stage (monotonic)
-  uint32_t* acc_cnt = misc + 8;  // [kAccSt] gate warps that finished reading the accumulator stage (monotonic)
+  uint32_t* acc_cnt = misc + 10;  // [kAccSt] gate warps that finished reading the accumulator stage (monotonic)
   int32_t* page_id = reinterpret_cast<int32_t*>(smem + L.page_ok);
   float* wsc = reinterpret_cast<float*>(smem + L.wsc);
   SelectScratch& sel = *reinterpret_cast<SelectScratch*>(smem + L.sel);
@@ -308,7 +312,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         t_last = clock64();
         continue;
       }
-      __nanosleep(64);  // nothing to refill: do not spin hot beside the decode warps
+      __nanosleep(200);  // nothing to refill: do not spin hot beside the decode warps
       if (clock64() - t_last > kBudget) {
         if (lane == 0) give_up(0, tile);
         break;
@@ -323,11 +327,11 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) bdesc[kk] = umma::smem_desc_sw128(qb_u + (kk >> 2) * (N * 128) + (kk & 3) * 32);
     for (int tile = 0; tile < n_tiles; ++tile) {
-      const int a = tile % kAStages, c = tile % kAccSt;
+      const int a = tile % kASt, c = tile % kAccSt;
       if (lane == 0) MDC_TRACE_AT(2, tile, 0);
       // progress counters instead of mbarriers here: an mbarrier wait costs this
       // thread ~150 cycles even when the phase is long complete
-      bool ok = counter_wait(&a_cnt[a], 4u * (tile / kAStages + 1), kBudget, abort_flag);
+      bool ok = counter_wait(&a_cnt[a], 4u * (tile / kASt + 1), kBudget, abort_flag);
       if (lane == 0) MDC_TRACE_AT(2, tile, 1);
       if (ok && tile >= kAccSt) ok = counter_wait(&acc_cnt[c], 4u * (tile / kAccSt), kBudget, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) {
@@ -343,17 +347,17 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       }
       __syncwarp();
     }
-  } else if (warp < kWarps) {
-    // ---------------- decode warps: thread = token row; warps 0-3 take the even stages, 4-7 the odd ones
-    const int quad = warp & 3, grp = warp >> 2;  // TMEM lane quadrant, stage parity
+  } else if (warp < kGateWarp0) {
+    // ---------------- decode warps: thread = token row; group g (warps 4g..4g+3) takes the stages g, g + DG, ...
+    const int quad = warp & 3, grp = warp >> 2;  // TMEM lane quadrant, group
     const int row = quad * 32 + lane;
     const int pp = row / PAGE, tok = row % PAGE;
     const int rot = (lane >> 1) & 3;  // chunk rotation: lanes 2m, 2m+1 start at chunk m (no bank conflicts)
     const uint32_t t_row = tmem + (static_cast<uint32_t>(quad * 32) << 16) + kABase;
     // answers of the early probes for the next stage (true = known complete)
     bool raw_ok = false, a_ok = true;
-    for (int tile = grp; tile < n_tiles; tile += 2) {
-      const int s = tile % kRawStages, a = tile % kAStages;
+    for (int tile = grp; tile < n_tiles; tile += DG) {
+      const int s = tile % kRawStages, a = tile % kASt;
       if (tid == 0) MDC_TRACE_AT(1, tile, 0);
       if (!raw_ok && !mbar_wait(&raw_full[s], (tile / kRawStages) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(3, tile);
@@ -372,13 +376,13 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         else raw_sf.x = *reinterpret_cast<const uint32_t*>(pg + PG::kData + (tok % 32) * 16 + (tok / 32) * 4);
       }
       // probe the barriers of this group's next stage now; the answers are read at the top of the next iteration
-      const int nt = tile + 2;
+      const int nt = tile + DG;
       bool n_raw = false, n_a = true;
       if (nt < n_tiles) {
         n_raw = mbar_test(&raw_full[nt % kRawStages], (nt / kRawStages) & 1);
-        if (nt >= kAStages) n_a = mbar_test(&mma_done[nt % kAStages], ((nt / kAStages) - 1) & 1);
+        if (nt >= kASt) n_a = mbar_test(&mma_done[nt % kASt], ((nt / kASt) - 1) & 1);
       }
-      if (!a_ok && !mbar_wait(&mma_done[a], ((tile / kAStages) - 1) & 1, kBudget, abort_flag)) {
+      if (!a_ok && !mbar_wait(&mma_done[a], ((tile / kASt) - 1) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(4, tile);
         break;
       }
@@ -439,7 +443,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     for (int tile = gg; tile < n_tiles; tile += GG) {
       const int c = tile % kAccSt;
       if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 0);
-      if (!done_ok && !mbar_wait(&mma_done[tile % kAStages], (tile / kAStages) & 1, kBudget, abort_flag)) {
+      if (!done_ok && !mbar_wait(&mma_done[tile % kASt], (tile / kASt) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(5, tile);
         break;
       }
@@ -447,7 +451,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 1);
       const int nt = tile + GG;
       bool n_done = false;
-      if (nt < n_tiles) n_done = mbar_test(&mma_done[nt % kAStages], (nt / kAStages) & 1);
+      if (nt < n_tiles) n_done = mbar_test(&mma_done[nt % kASt], (nt / kASt) & 1);
       float score[T];
 #pragma unroll
       for (int t = 0; t < T; ++t) {
@@ -455,6 +459,13 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         umma::tmem_ld32(t_base + c * N + t * kIdxHeads, v0);
         umma::tmem_ld32(t_base + c * N + t * kIdxHeads + 32, v1);
         umma::wait_ld();
+        if (t == T - 1) {  // the row is in registers: the accumulator stage can be overwritten
+          if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 2);
+          umma::fence_before_sync();
+          __syncwarp();
+          red_release_cta_shared_inc_if(&acc_cnt[c], lane == 0);
+          if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 3);
+        }
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         const float4* w4 = reinterpret_cast<const float4*>(wsc + t * kIdxHeads);
 #pragma unroll
@@ -469,11 +480,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         }
         score[t] = (s0 + s1) + (s2 + s3);
       }
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 2);
-      umma::fence_before_sync();
-      __syncwarp();
-      red_release_cta_shared_inc_if(&acc_cnt[c], lane == 0);
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 3);
       const int local = tile * kTileTok + q * 32 + lane;  // position inside the chunk
       if (local < n_pages * PAGE) {
         const bool ok = page_id[local / PAGE] >= 0;
