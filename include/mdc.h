@@ -211,6 +211,18 @@ typedef struct {
 int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* stream);
 int mdc_sparse_mla_smem_bytes(const mdc_sparse_mla_params* p);
 
+/* Same launch, but the split workspace is a fixed block inside the library's own
+ * device data (p->ws_o / p->ws_lse are ignored), so the call enters no allocator.
+ * No counterpart in the reference: it exists for callers that cannot allocate
+ * at launch time (all device memory already given to a cache pool; a thread that
+ * must not take the allocator's lock).  Capacity: B * q_len * n_splits * H <=
+ * MDC_STATIC_WS_MAX_SLOTS, else MDC_ERR_TOO_LARGE and nothing is launched.  The
+ * first call on a device looks the block's address up once: make it before any
+ * stream capture begins.  One block per device: calls whose kernels may overlap
+ * race on it.  Nothing has to be cleared between calls. */
+#define MDC_STATIC_WS_MAX_SLOTS 4096
+int mdc_sparse_mla_launch_static_ws(const mdc_sparse_mla_params* p, void* stream);
+
 
 /* ------------------------------------------------------------------------
  * Event / comm / scheduler device layer and the persistent decode megakernel.

@@ -139,6 +139,7 @@ EXPORTS = [
     "mdc_abi_version", "mdc_status_string", "mdc_last_cuda_error", "mdc_kernel_attrs",
     "mdc_logits_fp4_launch", "mdc_logits_fp4_smem_bytes", "mdc_merge_topk_launch",
     "mdc_lse_merge_launch", "mdc_sparse_mla_launch", "mdc_sparse_mla_smem_bytes",
+    "mdc_sparse_mla_launch_static_ws",
     "mdc_megakernel_launch", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
     "mdc_compress_step_launch", "mdc_compress_finalize_launch", "mdc_hadamard_quant_launch",
 ]

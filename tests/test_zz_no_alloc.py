@@ -1,0 +1,64 @@
+"""The allocation-free sparse-MLA entry point (library-owned split workspace)
+against the caller-workspace entry point, through the C ABI.  Collected last
+on purpose: it has to pass alone and after every other GPU test has used the
+library."""
+
+import math
+
+import pytest
+import torch
+
+from dsa_inputs import mla_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(N, case, o, lse, n_splits, ws_o, ws_l, status):
+    q = case["q"]
+    B, T, H, d_qk = q.shape
+    return N.SparseMlaParams(
+        q=N.ptr(q), kv_win=N.ptr(case["kv_win"]), kv_cmp=N.ptr(case["kv_cmp"]), pt_win=N.ptr(case["pt_win"]),
+        pt_cmp=N.ptr(case["pt_cmp"]), k_valid=N.ptr(case["k_valid"]), win_valid=N.ptr(case["win_valid"]),
+        attn_sink=None, o=N.ptr(o), lse=N.ptr(lse), o_stride=H * 512, lse_stride=H,
+        ws_o=N.ptr(ws_o), ws_lse=N.ptr(ws_l), B=B, q_len=T, H=H, d_qk=d_qk, d_v=512,
+        pages_win=0 if case["kv_win"] is None else case["kv_win"].shape[0], pages_cmp=case["kv_cmp"].shape[0],
+        page_cmp=case["kv_cmp"].shape[1], pt_cols=case["pt_cmp"].shape[1], kv_dtype=N.DT_BF16, out_dtype=N.DT_F32,
+        n_splits=n_splits, fp8_p=0, softmax_scale=1.0 / math.sqrt(d_qk), output_scale=1.0, status=N.ptr(status))
+
+
+def test_static_workspace_matches_caller_workspace():
+    from mega_dsa_cp_b200 import _native as N
+
+    dev = torch.device("cuda:0")
+    B, T, H, splits = 2, 1, 128, 4
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    # two calls in a row on different inputs: the second must not see anything of the first
+    for seed, n_sel in ((11, [700, 1500]), (12, [2048, 3])):
+        case = {k: (v.to(dev) if torch.is_tensor(v) else v)
+                for k, v in mla_case(B, T, H, 576, 4096, n_sel, with_window=True, seed=seed).items()}
+        rows = B * T
+        ws_o = torch.empty(rows, splits, H, 512, device=dev)
+        ws_l = torch.empty(rows, splits, H, device=dev)
+        o_ref = torch.full((rows, H, 512), float("nan"), device=dev)
+        l_ref = torch.full((rows, H), float("nan"), device=dev)
+        o_new, l_new = o_ref.clone(), l_ref.clone()
+        N.call("mdc_sparse_mla_launch", _params(N, case, o_ref, l_ref, splits, ws_o, ws_l, status), None)
+        N.call("mdc_sparse_mla_launch_static_ws", _params(N, case, o_new, l_new, splits, None, None, status), None)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0
+        assert torch.isfinite(o_ref).all()
+        assert torch.equal(o_new, o_ref) and torch.equal(l_new, l_ref)
+
+
+def test_static_workspace_rejects_oversize():
+    from mega_dsa_cp_b200 import _native as N
+
+    dev = torch.device("cuda:0")
+    B, T, H, splits = 3, 1, 128, 16  # 3 * 16 * 128 = 6144 slots > 4096
+    case = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in mla_case(B, T, H, 576, 512, [64] * B).items()}
+    o = torch.zeros(B, H, 512, device=dev)
+    lse = torch.zeros(B, H, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    rc = N.lib().mdc_sparse_mla_launch_static_ws(N.C.byref(_params(N, case, o, lse, splits, None, None, status)), None)
+    assert rc == -6  # MDC_ERR_TOO_LARGE
+    assert "capacity" in N.lib().mdc_status_string(rc).decode()
