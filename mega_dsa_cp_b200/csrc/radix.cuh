@@ -128,7 +128,7 @@ __device__ Threshold<KeyT> block_select_threshold(Src src, int n_pos, int k, Sel
 // are cheap to re-read (shared memory): a bitwise search for the k-th largest
 // key, one block-wide count per bit, no per-element atomics.  key(pos) -> u32.
 template <typename KeyFn>
-__device__ Threshold<uint32_t> block_select_bits(KeyFn key, int n_pos, int k, SelectScratch& sc) {
+__device__ Threshold<uint32_t> block_select_bits(KeyFn key, int n_pos, int k, SelectScratch& sc, int* n_eq_out = nullptr) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   Threshold<uint32_t> th;
   uint32_t kmax = 0u, kmin = 0xffffffffu;
@@ -176,14 +176,23 @@ __device__ Threshold<uint32_t> block_select_bits(KeyFn key, int n_pos, int k, Se
     sync_workers();
     if (static_cast<int>(sc.hist[32 + bit]) >= k) tau = cand;
   }
-  int gt = 0;
-  for (int pos = tid; pos < n_pos; pos += kBlockThreads) gt += key(pos) > tau;
+  int gt = 0, eq = 0;
+  for (int pos = tid; pos < n_pos; pos += kBlockThreads) {
+    const uint32_t kv = key(pos);
+    gt += kv > tau;
+    eq += kv == tau;
+  }
   gt = __reduce_add_sync(0xffffffffu, gt);
-  if (lane == 0) atomicAdd(&sc.hist[96], static_cast<uint32_t>(gt));
+  eq = __reduce_add_sync(0xffffffffu, eq);
+  if (lane == 0) {
+    atomicAdd(&sc.hist[96], static_cast<uint32_t>(gt));
+    atomicAdd(&sc.hist[97], static_cast<uint32_t>(eq));
+  }
   sync_workers();
   th.tau = tau;
   th.need_eq = k - static_cast<int>(sc.hist[96]);
   th.n_sel = k;
+  if (n_eq_out) *n_eq_out = static_cast<int>(sc.hist[97]);  // keys equal to the threshold
   sync_workers();
   return th;
 }

@@ -162,14 +162,12 @@ __device__ inline int merge_lists_regs(const MergeLists& ls, int L, int maxK, in
   return min(n, top_k);
 }
 
-// Shared-memory path for rows of up to `cap` positions: logits and ids are
-// staged once (vb / ib, `cap` words each), selected by bitwise search, and
-// emitted from shared memory.  Ties on the logit are resolved in the same
-// search by a second key: entries above the logit threshold rank highest, tied
-// entries rank by ~id, everything else is out.
+// Stages the padded lists of one row into shared memory: vb[pos] = sortable key
+// of the logit (0 = empty position), ib[pos] = id.  The loads carry no branch
+// (invalid positions read element 0 of their list and are masked afterwards),
+// so a thread's loads of one batch are all in flight together.
 template <bool SYS>
-__device__ inline int merge_lists_smem(const MergeLists& ls, int L, int maxK, int top_k, float* out_v, int32_t* out_i,
-                                       int32_t* out_c, int32_t* dbg, MergeSmem& sm, uint32_t* vb, int32_t* ib) {
+__device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, MergeSmem& sm, uint32_t* vb, int32_t* ib) {
   const int tid = threadIdx.x;
   const int n_pos = L * maxK;
   sync_workers();
@@ -179,25 +177,177 @@ __device__ inline int merge_lists_smem(const MergeLists& ls, int L, int maxK, in
     sm.cnt[l] = max(0, min(c, maxK));
   }
   sync_workers();
-  for (int pos = tid; pos < n_pos; pos += kBlockThreads) {
-    const int l = pos / maxK, j = pos - l * maxK;
-    const bool valid = j < sm.cnt[l];
-    // key 0 marks an empty position; a real logit never maps to 0 after the clamp
-    vb[pos] = valid ? max(sortable_u32(ld_f32(ls.v + l * ls.stride + j, SYS)), 1u) : 0u;
-    ib[pos] = valid ? __float_as_int(ld_f32(reinterpret_cast<const float*>(ls.i + l * ls.stride + j), SYS)) : 0;
+  const bool vec = !SYS && (maxK & 3) == 0 && (ls.stride & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(ls.v) | reinterpret_cast<uintptr_t>(ls.i)) & 15) == 0;
+  if (vec) {
+    // four consecutive positions of one list per 16-byte load, eight loads of each kind in flight per thread
+    constexpr int U = 8;
+    const int n_vec = n_pos >> 2, k4 = maxK >> 2;
+    for (int q0 = tid; q0 < n_vec; q0 += U * kBlockThreads) {
+      float4 v[U];
+      int4 f[U];
+      int cnt[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int qi = min(q0 + u * kBlockThreads, n_vec - 1);
+        const int l = qi / k4, j = (qi - l * k4) << 2;
+        cnt[u] = sm.cnt[l] - j;  // valid positions of this quad: those below cnt
+        const int64_t off = l * ls.stride + j;
+        v[u] = __ldg(reinterpret_cast<const float4*>(ls.v + off));
+        f[u] = __ldg(reinterpret_cast<const int4*>(ls.i + off));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int qi = q0 + u * kBlockThreads;
+        if (qi < n_vec) {
+          uint4 kv;
+          kv.x = cnt[u] > 0 ? max(sortable_u32(v[u].x), 1u) : 0u;
+          kv.y = cnt[u] > 1 ? max(sortable_u32(v[u].y), 1u) : 0u;
+          kv.z = cnt[u] > 2 ? max(sortable_u32(v[u].z), 1u) : 0u;
+          kv.w = cnt[u] > 3 ? max(sortable_u32(v[u].w), 1u) : 0u;
+          reinterpret_cast<uint4*>(vb)[qi] = kv;
+          reinterpret_cast<int4*>(ib)[qi] = f[u];
+        }
+      }
+    }
+    sync_workers();
+    return;
+  }
+  constexpr int U = 8;
+  int l = tid / maxK, j = tid - l * maxK;  // position tid, advanced by 256 per step
+  const int dl = kBlockThreads / maxK, dj = kBlockThreads - dl * maxK;
+  for (int pos0 = tid; pos0 < n_pos; pos0 += U * kBlockThreads) {
+    float v[U], f[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool in = pos0 + u * kBlockThreads < n_pos;
+      ok[u] = in && j < sm.cnt[in ? l : 0];
+      const int64_t off = ok[u] ? l * ls.stride + j : 0;
+      v[u] = ld_f32(ls.v + off, SYS);
+      f[u] = ld_f32(reinterpret_cast<const float*>(ls.i) + off, SYS);
+      l += dl;
+      j += dj;
+      if (j >= maxK) {
+        j -= maxK;
+        ++l;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pos = pos0 + u * kBlockThreads;
+      if (pos < n_pos) {
+        // key 0 marks an empty position; a real logit never maps to 0 after the clamp
+        vb[pos] = ok[u] ? max(sortable_u32(v[u]), 1u) : 0u;
+        ib[pos] = ok[u] ? __float_as_int(f[u]) : 0;
+      }
+    }
   }
   sync_workers();
-  Threshold<uint32_t> th = block_select_bits([&](int pos) { return vb[pos]; }, n_pos, top_k, sm.sel);
+}
+
+__device__ inline int workers_sum(int x, int32_t* wcnt) {
+  x = __reduce_add_sync(0xffffffffu, x);
+  sync_workers();
+  if ((threadIdx.x & 31) == 0) wcnt[threadIdx.x >> 5] = x;
+  sync_workers();
+  int t = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) t += wcnt[w];
+  return t;
+}
+
+__device__ inline float unsortable_f32(uint32_t kv) {
+  return __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
+}
+
+// Staged rows of up to 256 * E positions: keys live in registers for the
+// select (one read of shared memory), a second u32 select on ~id runs only
+// when equal logits straddle the boundary, and the emit reads shared memory.
+template <int E>
+__device__ inline int merge_staged_regs(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
+                                        MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
+  const int tid = threadIdx.x;
+  uint32_t key[E];
+#pragma unroll
+  for (int it = 0; it < E; ++it) {
+    const int pos = it * kBlockThreads + tid;
+    key[it] = pos < n_pos ? vb[pos] : 0u;
+  }
+  const Threshold<uint32_t> th = block_select_regs<E>(key, top_k, sm.rsel);
+  uint32_t sure_m = 0u, tie_m = 0u;  // bit it = element it of this thread
+  int need = 0;
+  if (th.need_eq == 0x7fffffff) {
+#pragma unroll
+    for (int it = 0; it < E; ++it) sure_m |= static_cast<uint32_t>(key[it] != 0u) << it;
+  } else {
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      sure_m |= static_cast<uint32_t>(key[it] > th.tau) << it;
+      tie_m |= static_cast<uint32_t>(key[it] == th.tau) << it;
+    }
+    // distinct logits at the boundary (the usual case): need_eq == 1 and exactly one tied entry
+    const int ties = workers_sum(__popc(tie_m), sm.rsel.wcnt);
+    if (ties == th.need_eq) {
+      sure_m |= tie_m;
+      tie_m = 0u;
+    } else {
+#pragma unroll
+      for (int it = 0; it < E; ++it) {
+        const int pos = it * kBlockThreads + tid;
+        key[it] = ((tie_m >> it) & 1u) ? max(~static_cast<uint32_t>(ib[pos]), 1u) : 0u;
+      }
+      const Threshold<uint32_t> t2 = block_select_regs<E>(key, th.need_eq, sm.rsel);
+      uint32_t tie2 = 0u;
+#pragma unroll
+      for (int it = 0; it < E; ++it) {
+        if (t2.need_eq == 0x7fffffff) {
+          sure_m |= static_cast<uint32_t>(key[it] != 0u) << it;
+        } else {
+          sure_m |= static_cast<uint32_t>(key[it] > t2.tau) << it;
+          tie2 |= static_cast<uint32_t>(t2.need_eq > 0 && key[it] != 0u && key[it] == t2.tau) << it;
+        }
+      }
+      tie_m = tie2;
+      need = (t2.need_eq == 0x7fffffff) ? 0 : t2.need_eq;
+    }
+  }
+  int slot[E];
+  const int n = block_emit_regs<E>(
+      need, sm.rsel, [&](int it) { return ((sure_m >> it) & 1u) != 0; }, [&](int it) { return ((tie_m >> it) & 1u) != 0; }, slot);
+#pragma unroll
+  for (int it = 0; it < E; ++it) {
+    if (slot[it] >= 0 && slot[it] < top_k) {
+      const int pos = it * kBlockThreads + tid;
+      out_v[slot[it]] = unsortable_f32(vb[pos]);
+      out_i[slot[it]] = ib[pos];
+    }
+  }
+  if (tid == 0) {
+    *out_c = min(n, top_k);
+    if (n != th.n_sel && dbg) atomicAdd(dbg, 1);
+  }
+  return min(n, top_k);
+}
+
+// Staged rows of any size: bitwise search over the shared-memory keys.  Ties on
+// the logit are resolved in the same search by a second key: entries above the
+// logit threshold rank highest, tied entries rank by ~id, everything else is out.
+__device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
+                                        MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
+  const int tid = threadIdx.x;
+  int n_eq = 0;
+  Threshold<uint32_t> th = block_select_bits([&](int pos) { return vb[pos]; }, n_pos, top_k, sm.sel, &n_eq);
   const int expect = th.n_sel;
   int n;
   auto put = [&](int pos, int slot) {
     if (slot < top_k) {
-      const uint32_t kv = vb[pos];
-      out_v[slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
+      out_v[slot] = unsortable_f32(vb[pos]);
       out_i[slot] = ib[pos];
     }
   };
-  if (th.need_eq == 0x7fffffff) {
+  if (th.need_eq == 0x7fffffff || n_eq == th.need_eq) {
+    // everything valid, or every entry tied at the threshold is taken (distinct logits: the usual case)
     n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, th,
                                       sm.sel, put);
   } else {
@@ -217,18 +367,24 @@ __device__ inline int merge_lists_smem(const MergeLists& ls, int L, int maxK, in
   return min(n, top_k);
 }
 
-// picks the fastest path the row size allows: registers, shared memory (when
-// `stage` offers 8 bytes per position), else re-reading global memory per pass
+// Picks the fastest path the row size allows: staged in shared memory (when
+// `stage` offers 8 bytes per position) with register or shared-memory keys,
+// else register keys read from global memory, else re-reading global memory per pass.
 template <bool SYS>
 __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, int top_k, float* out_v, int32_t* out_i,
                                        int32_t* out_c, int32_t* dbg, MergeSmem& sm, unsigned char* stage = nullptr,
                                        int stage_bytes = 0) {
   const int n_pos = L * maxK;
+  if (stage && n_pos * 8 <= stage_bytes && maxK >= 1) {
+    uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
+    int32_t* ib = reinterpret_cast<int32_t*>(stage) + n_pos;
+    merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
+    if (n_pos <= kBlockThreads * kMergeRegE)
+      return merge_staged_regs<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
+    return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
+  }
   if (n_pos <= kBlockThreads * kMergeRegE)
     return merge_lists_regs<kMergeRegE, SYS>(ls, L, maxK, top_k, out_v, out_i, out_c, dbg, sm);
-  if (stage && n_pos * 8 <= stage_bytes)
-    return merge_lists_smem<SYS>(ls, L, maxK, top_k, out_v, out_i, out_c, dbg, sm, reinterpret_cast<uint32_t*>(stage),
-                                 reinterpret_cast<int32_t*>(stage) + n_pos);
   return merge_lists_tile<SYS>(ls, L, maxK, top_k, out_v, out_i, out_c, dbg, sm);
 }
 
