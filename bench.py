@@ -97,13 +97,13 @@ class ClockSampler:
 CFG2 = dict(B=32, S=32768, page=64, top_k=2048, q_len=1, copies=4, blocks_per_chunk=128)
 
 
-def cfg2_algorithmic_bytes(c) -> int:
+def cfg2_algorithmic_bytes(c, row_mode=True) -> int:
     """Bytes one logits launch must move: 72 B per (sequence, token) of NVFP4
     index-K, 4 B per page-table entry, 16640 B of bf16 query + weights per
-    sequence, 8 B per emitted candidate."""
+    sequence, 8 B per emitted entry (top-k per row in row mode, per chunk otherwise)."""
     B, S, P, K = c["B"], c["S"], c["page"], c["top_k"]
-    n_chunks = (S // P) // c["blocks_per_chunk"]
-    return B * S * 72 + B * (S // P) * 4 + B * 16640 + B * n_chunks * K * 8
+    n_lists = 1 if row_mode else (S // P) // c["blocks_per_chunk"]
+    return B * S * 72 + B * (S // P) * 4 + B * 16640 + B * n_lists * K * 8
 
 
 def build_cfg2_device(c, device, seed=0):
@@ -150,14 +150,22 @@ def run_gpu_cfg2(args):
     oc = torch.empty(B, T, dtype=torch.int32, device=dev)
     status = torch.zeros(8, dtype=torch.int32, device=dev)
 
-    def logits_only(i, qq=q, ww=w):
-        r = i % c["copies"]
-        run_fp4_paged_mqa_logits(caches[r], qq, None, ww, tables[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
-                                 top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
+    two = args.two_kernel  # reference-shaped path: chunk candidates, then the merge kernel
 
-    def step(i, qq=q, ww=w):
-        logits_only(i, qq, ww)
-        run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
+    def logits_only(i, qq=q, ww=w, tables_=None):
+        r = i % c["copies"]
+        bt = tables[r] if tables_ is None else tables_[r]
+        if two:
+            run_fp4_paged_mqa_logits(caches[r], qq, None, ww, bt, None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
+                                     top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
+        else:  # one launch: the four blocks of a sequence select across their chunks as a cluster
+            run_fp4_paged_mqa_logits(caches[r], qq, None, ww, bt, None, bpc, top_k=K, fmt="nvfp4",
+                                     page_tokens=c["page"], status=status, row_topk=(ov, oi, oc))
+
+    def step(i, qq=q, ww=w, tables_=None):
+        logits_only(i, qq, ww, tables_)
+        if two:
+            run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
 
     for i in range(max(args.warmup, c["copies"])):
         step(i)
@@ -207,39 +215,74 @@ def run_gpu_cfg2(args):
     # end to end: per-step tensors start in pinned host memory (query, gate
     # weights, page table), the selected ids come back; the index cache is
     # resident state, like model weights, and is not re-sent.
-    hq = q.cpu().pin_memory()
-    hw = w.cpu().pin_memory()
-    hbt = [t.cpu().pin_memory() for t in tables]
-    dq, dw = torch.empty_like(q), torch.empty_like(w)
-    dbt = [torch.empty_like(t) for t in tables]
-    h_ids = torch.empty(B, T, K, dtype=torch.int32).pin_memory()
-    h_cnt = torch.empty(B, T, dtype=torch.int32).pin_memory()
+    # One pinned host block [q | w | page table] per cache copy goes down in one copy, one block
+    # [ids | counts] comes back: the latency of each copy, not its bytes, is what costs at this size.
+    nq, nw, nbt = q.numel() * 2, w.numel() * 4, tables[0].numel() * 4
+    hin, din, dq, dw, dbt = [], [], [], [], []
+    for r in range(c["copies"]):
+        h = torch.empty(nq + nw + nbt, dtype=torch.uint8).pin_memory()
+        h[:nq].copy_(q.cpu().view(torch.uint8).reshape(-1))
+        h[nq:nq + nw].copy_(w.cpu().view(torch.uint8).reshape(-1))
+        h[nq + nw:].copy_(tables[r].cpu().view(torch.uint8).reshape(-1))
+        d = torch.empty_like(h, device=dev)
+        hin.append(h)
+        din.append(d)
+        dq.append(d[:nq].view(torch.bfloat16).view_as(q))
+        dw.append(d[nq:nq + nw].view(torch.float32).view_as(w))
+        dbt.append(d[nq + nw:].view(torch.int32).view_as(tables[r]))
+    dout = torch.empty(B * T * K + B * T, dtype=torch.int32, device=dev)
+    e_oi, e_oc = dout[:B * T * K].view(B, T, K), dout[B * T * K:].view(B, T)
+    e_ov = torch.empty(B, T, K, device=dev)
+    hout = torch.empty(B * T * K + B * T, dtype=torch.int32).pin_memory()
+    h_cnt = hout[B * T * K:]
+
+    def e2e_body(r):
+        din[r].copy_(hin[r], non_blocking=True)
+        if two:
+            run_fp4_paged_mqa_logits(caches[r], dq[r], None, dw[r], dbt[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
+                                     top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
+            run_merge_topk(cv, ci, cc, e_ov, e_oi, e_oc, None, top_k=K)
+        else:
+            run_fp4_paged_mqa_logits(caches[r], dq[r], None, dw[r], dbt[r], None, bpc, top_k=K, fmt="nvfp4",
+                                     page_tokens=c["page"], status=status, row_topk=(e_ov, e_oi, e_oc))
+        hout.copy_(dout, non_blocking=True)
 
     def e2e_step(i):
-        r = i % c["copies"]
-        dq.copy_(hq, non_blocking=True)
-        dw.copy_(hw, non_blocking=True)
-        dbt[r].copy_(hbt[r], non_blocking=True)
-        run_fp4_paged_mqa_logits(caches[r], dq, None, dw, dbt[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
-                                 top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
-        run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
-        h_ids.copy_(oi, non_blocking=True)
-        h_cnt.copy_(oc, non_blocking=True)
+        e2e_body(i % c["copies"])
         torch.cuda.current_stream().synchronize()
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, c["copies"])):
         e2e_step(i)
     torch.cuda.synchronize()
+    e2e_graphs = None
+    if not args.no_graph:
+        # the whole step (H2D copy from pinned memory, the launch, D2H copy) as one graph per cache copy
+        e2e_graphs = []
+        for r in range(c["copies"]):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                e2e_body(r)
+            e2e_graphs.append(g)
+
+        def e2e_step(i):  # noqa: F811  (replaces the eager version for the timed loop)
+            e2e_graphs[i % c["copies"]].replay()
+            torch.cuda.current_stream().synchronize()
+
+        for i in range(args.warmup):
+            e2e_step(i)
+        torch.cuda.synchronize()
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(args.warmup + i)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    h2d = hq.numel() * 2 + hw.numel() * 4 + hbt[0].numel() * 4
-    d2h = h_ids.numel() * 4 + h_cnt.numel() * 4
+    assert status[0].item() == 0 and int(h_cnt.min()) == K, "end-to-end step returned an incomplete selection"
+    h2d = hin[0].numel()
+    d2h = hout.numel() * 4
 
     peak, peak_kind = measured_peaks()
-    algo = cfg2_algorithmic_bytes(c)
+    algo = cfg2_algorithmic_bytes(c, row_mode=not two)
+    n_kernels = 2 if two else 1
     achieved = algo / (ms_logits * 1e-3) / 1e9
     cpu = None if args.skip_cpu else cpu_baseline_cfg2(sample_seqs=1, reps=3)
     tokens = B * T
@@ -250,16 +293,17 @@ def run_gpu_cfg2(args):
         "config": {"workload": "cfg2: indexer logits + exact top-k 2048, B=32, ctx 32768, NVFP4 64-token pages, "
                                "random page tables, bf16 q (64 heads x 128)",
                    "l2": f"rotating {c['copies']} cache copies ({c['copies'] * 75.5:.0f} MB > 126 MB L2)",
-                   "parallelism": "cp1", "kernels_per_step": 2,
+                   "parallelism": "cp1", "kernels_per_step": n_kernels,
                    "launch": "eager" if graphs is None else "CUDA graph replay (one graph per cache copy)"},
         "step_us": ms_step * 1e3,
         "indexer_us": ms_logits * 1e3,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": n_kernels * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "kernel": "logits_kernel<NVFP4,64,1>", "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES},
+                     "kernel": "logits_kernel<NVFP4,64,1>" if two else "logits_row_kernel<NVFP4,64,1>",
+                     "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES},
         "cpu_baseline": cpu,
         "clocks": clk.summary(),
     }
@@ -459,6 +503,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--copies", type=int, default=None, help="rotation copies of the index cache (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--two-kernel", action="store_true",
+                    help="N=1: chunk candidates + merge kernel (the reference's two launches) instead of the one-launch row mode")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()
     if args.copies:

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MDC_ABI_VERSION 1
+#define MDC_ABI_VERSION 2
 
 /* host-side return codes */
 #define MDC_OK 0
@@ -117,6 +117,14 @@ typedef struct {
   int32_t window_exclude;    /* reference: 128 (sliding-window tokens skipped)      */
   int32_t id_mul, id_add;
   int32_t* status;           /* 8 words or NULL                                     */
+  /* Row mode (ABI 2, no counterpart in the reference): when row_v is set, the n_chunks blocks
+   * of a request run as one thread-block cluster (n_chunks in {1,2,4,8}, chunk <= 8192 tokens)
+   * and select the exact top_k of the WHOLE row across their chunks, written in position order:
+   * the same result as fused candidates followed by mdc_merge_topk_launch, in one launch.
+   * cand_* are ignored in this mode. */
+  float* row_v;              /* (B, q_len, top_k) or NULL                           */
+  int32_t* row_i;            /* (B, q_len, top_k)                                   */
+  int32_t* row_c;            /* (B, q_len)                                          */
 } mdc_logits_params;
 int mdc_logits_fp4_launch(const mdc_logits_params* p, void* stream);
 /* dynamic shared memory the launch above will request (bytes), or <0 */

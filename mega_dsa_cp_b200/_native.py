@@ -12,7 +12,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("MDC_LIB_PATH") or os.path.join(_PKG, "libmdc.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 FMT_MXFP4, FMT_NVFP4 = 0, 1
 Q_FP4, Q_BF16 = 0, 1
 DT_F32, DT_BF16, DT_E4M3 = 0, 1, 2
@@ -32,6 +32,7 @@ class LogitsParams(C.Structure):
         ("cand_v", p_void), ("cand_i", p_void), ("cand_c", p_void), ("top_k", i32),
         ("B", i32), ("q_len", i32), ("heads", i32), ("blocks_per_chunk", i32), ("n_chunks", i32),
         ("window_exclude", i32), ("id_mul", i32), ("id_add", i32), ("status", p_void),
+        ("row_v", p_void), ("row_i", p_void), ("row_c", p_void),
     ]
 
 

@@ -11,8 +11,37 @@ __global__ void __launch_bounds__(kLogitsThreads, 1) logits_kernel(const __grid_
   logits_tile<FMT, PAGE, T, kLogitsDecodeGroups, kLogitsGateGroups>(p, blockIdx.y, blockIdx.x, smem);
 }
 
+// Row mode: the blocks of one request form a cluster and select across their chunks.
+template <int FMT, int PAGE, int T>
+__global__ void __launch_bounds__(kLogitsThreads, 1) logits_row_kernel(const __grid_constant__ mdc_logits_params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  logits_tile<FMT, PAGE, T, kLogitsDecodeGroups, kLogitsGateGroups, true>(p, blockIdx.y, blockIdx.x, smem);
+}
+
+template <int FMT, int PAGE, int T>
+static int launch_logits_row(const mdc_logits_params& p, cudaStream_t st, int smem) {
+  auto kern = logits_row_kernel<FMT, PAGE, T>;
+  MDC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.n_chunks, p.B);
+  cfg.blockDim = dim3(kLogitsThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.n_chunks;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MDC_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  return MDC_OK;
+}
+
 template <int FMT, int PAGE, int T>
 static int launch_logits(const mdc_logits_params& p, cudaStream_t st, int smem) {
+  if (p.row_v) return launch_logits_row<FMT, PAGE, T>(p, st, smem);
   auto kern = logits_kernel<FMT, PAGE, T>;
   MDC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid(p.n_chunks, p.B);
@@ -32,8 +61,13 @@ static int logits_check(const mdc_logits_params* p) {
   if (p->heads != kIdxHeads || (p->q_len != 1 && p->q_len != 2)) return MDC_ERR_BAD_SHAPE;
   if (p->B < 1 || p->n_chunks < 1 || p->blocks_per_chunk < 1 || p->max_pages < 1) return MDC_ERR_BAD_SHAPE;
   if (p->n_chunks > 65535 * 32 || p->B > 65535) return MDC_ERR_BAD_SHAPE;
-  const bool fused = p->cand_v != nullptr;
-  if (fused) {
+  const bool fused = p->cand_v != nullptr && !p->row_v;
+  if (p->row_v) {
+    if (!p->row_i || !p->row_c) return MDC_ERR_NULL;
+    if (p->top_k < 1 || p->id_mul < 1) return MDC_ERR_BAD_SHAPE;
+    if (p->n_chunks != 1 && p->n_chunks != 2 && p->n_chunks != 4 && p->n_chunks != 8) return MDC_ERR_BAD_SHAPE;
+    if (p->blocks_per_chunk * p->page_tokens > kBlockThreads * kFusedRegE) return MDC_ERR_TOO_LARGE;
+  } else if (fused) {
     if (!p->cand_i || !p->cand_c) return MDC_ERR_NULL;
     if (p->top_k < 1) return MDC_ERR_BAD_SHAPE;
     if (p->id_mul < 1) return MDC_ERR_BAD_SHAPE;
@@ -46,7 +80,7 @@ static int logits_check(const mdc_logits_params* p) {
 }
 
 static int logits_smem(const mdc_logits_params* p) {
-  const bool fused = p->cand_v != nullptr;
+  const bool fused = p->cand_v != nullptr || p->row_v != nullptr;
   const int ct = p->blocks_per_chunk * p->page_tokens;
   int total;
   if (p->fmt == MDC_FMT_MXFP4) total = logits_smem_layout<MDC_FMT_MXFP4, 128>(p->q_len, ct, fused).total;

@@ -52,6 +52,8 @@
 // common exit (tensor memory is freed there).
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "fp4.cuh"
 #include "radix.cuh"
@@ -94,9 +96,17 @@ struct IdxPage {
   static constexpr int kStageBytes = kTilePages * kBytes;
 };
 
+// Scratch of the cluster-wide row select (read by the other blocks of the cluster).
+struct RowSelectScratch {
+  uint32_t hist[2][256];   // digit histograms of this block, double buffered over the radix passes
+  int32_t cnt_gt, cnt_eq;  // this block's counts above / at the row threshold
+  int32_t digit, excl;     // result of a pass: boundary digit, number of keys in higher bins
+  int32_t wsum[kWarps];
+};
+
 struct LogitsSmem {
   // byte offsets inside the tile's dynamic shared memory (base 1024 B aligned)
-  int qb, ring, bars, misc, page_ok, wsc, sel, scores, total;
+  int qb, ring, bars, misc, page_ok, wsc, sel, row, scores, total;
 };
 
 template <int FMT, int PAGE>
@@ -118,6 +128,8 @@ __host__ __device__ inline LogitsSmem logits_smem_layout(int q_len, int chunk_to
   L.sel = off;
   off += static_cast<int>(align_up(sizeof(SelectScratch) > sizeof(RegSelectScratch<kFusedRegE>) ? sizeof(SelectScratch)
                                                                                              : sizeof(RegSelectScratch<kFusedRegE>), 16));
+  L.row = off;
+  off += static_cast<int>(align_up(sizeof(RowSelectScratch), 16));
   L.page_ok = off;  // page id per page of the chunk (-1 = not usable)
   off += static_cast<int>(align_up((chunk_tokens / PAGE + 4) * 4, 16));
   L.scores = off;
@@ -190,9 +202,143 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
   }
 }
 
+// Exact top-k of a whole request row across the blocks of a thread-block
+// cluster (block rank = chunk).  Every block holds its chunk's scores in shared
+// memory; the k-th largest key of the row is found by a 4-pass byte radix
+// search whose histograms are summed over the cluster through distributed
+// shared memory (every block computes the same sums, so no result has to be
+// sent back), then each block emits its selected entries in position order at
+// the offset given by the lower ranks' counts.  Ties at the threshold go to the
+// smaller position.  The number of cluster barriers is fixed (6 per query
+// token) and does not depend on the data.  Called by the 256 worker threads of
+// every block of the cluster; n_local = 0 for a block that has nothing to offer.
+template <int T>
+__device__ void logits_row_select(const mdc_logits_params& p, int b, int chunk, int n_local, int base_pos, int limit,
+                                  int chunk_tokens, const float* scores, RegSelectScratch<kFusedRegE>& rsel,
+                                  RowSelectScratch& rs) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int nr = static_cast<int>(cluster.num_blocks());
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int E = kFusedRegE;
+  for (int t = 0; t < T; ++t) {
+    const float* sc_row = scores + t * chunk_tokens;
+    uint32_t key[E];
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      const int pos = it * kBlockThreads + tid;
+      key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+    }
+    uint32_t prefix = 0u;
+    int kk = p.top_k;
+    bool all = false;
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass, buf = pass & 1;
+      rs.hist[buf][tid] = 0u;
+      sync_workers();
+      // run-length over this thread's keys: equal digits in a row cost one atomic
+      uint32_t run_d = 0xffffffffu, run_n = 0u;
+#pragma unroll
+      for (int it = 0; it < E; ++it) {
+        const bool in = key[it] != 0u && (pass == 0 || (key[it] >> (shift + 8)) == prefix);
+        const uint32_t d = in ? (key[it] >> shift) & 255u : 0xffffffffu;
+        if (d != run_d) {
+          if (run_n) atomicAdd(&rs.hist[buf][run_d], run_n);
+          run_d = d;
+          run_n = 0u;
+        }
+        run_n += in;
+      }
+      if (run_n) atomicAdd(&rs.hist[buf][run_d], run_n);
+      cluster.sync();
+      // thread tid owns bin 255 - tid, summed over the cluster
+      const int bin = 255 - tid;
+      uint32_t g = 0u;
+      for (int r = 0; r < nr; ++r) g += cluster.map_shared_rank(&rs.hist[buf][0], r)[bin];
+      // inclusive scan over tid = number of keys in bins >= bin
+      uint32_t inc = g;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += y;
+      }
+      if (lane == 31) rs.wsum[warp] = static_cast<int32_t>(inc);
+      if (tid == 0) rs.digit = -1;
+      sync_workers();
+      uint32_t before = 0u, total = 0u;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        if (w < warp) before += static_cast<uint32_t>(rs.wsum[w]);
+        total += static_cast<uint32_t>(rs.wsum[w]);
+      }
+      inc += before;
+      const uint32_t exc = inc - g;
+      if (!all && static_cast<int>(exc) < kk && kk <= static_cast<int>(inc)) {
+        rs.digit = bin;
+        rs.excl = static_cast<int32_t>(exc);
+      }
+      sync_workers();
+      if (pass == 0 && static_cast<int>(total) <= kk) all = true;  // fewer valid entries than k: take all
+      if (!all) {
+        prefix = (prefix << 8) | static_cast<uint32_t>(rs.digit);
+        kk -= rs.excl;
+      }
+    }
+    // kk = entries to take among those equal to the threshold key `prefix`
+    const uint32_t tau = all ? 0u : prefix;
+    int c_gt = 0, c_eq = 0;
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      c_gt += all ? key[it] != 0u : key[it] > tau;
+      c_eq += !all && key[it] == tau;
+    }
+    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
+    if (tid == 0) rs.cnt_gt = rs.cnt_eq = 0;
+    sync_workers();
+    if (lane == 0) {
+      atomicAdd(&rs.cnt_gt, c_gt);
+      atomicAdd(&rs.cnt_eq, c_eq);
+    }
+    cluster.sync();
+    int gt_before = 0, eq_before = 0, gt_all = 0, eq_all = 0, eq_mine = 0;
+    for (int r = 0; r < nr; ++r) {
+      const RowSelectScratch* o = cluster.map_shared_rank(&rs, r);
+      const int g1 = o->cnt_gt, e1 = o->cnt_eq;
+      if (r < chunk) {
+        gt_before += g1;
+        eq_before += e1;
+      }
+      if (r == chunk) eq_mine = e1;
+      gt_all += g1;
+      eq_all += e1;
+    }
+    const int need_row = all ? 0 : kk;
+    const int need = max(0, min(need_row - eq_before, eq_mine));   // ties this block contributes
+    const int base = gt_before + min(eq_before, need_row);         // entries selected in lower chunks
+    int slot[E];
+    block_emit_regs<E>(
+        need, rsel, [&](int it) { return all ? key[it] != 0u : key[it] > tau; },
+        [&](int it) { return !all && key[it] == tau; }, slot);
+    const int64_t out0 = (static_cast<int64_t>(b) * T + t) * p.top_k;
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      const int o = base + slot[it];
+      if (slot[it] >= 0 && o < p.top_k) {
+        const int pos = it * kBlockThreads + tid;
+        p.row_v[out0 + o] = sc_row[pos];
+        p.row_i[out0 + o] = (base_pos + pos) * p.id_mul + p.id_add;
+      }
+    }
+    if (chunk == 0 && tid == 0) p.row_c[static_cast<int64_t>(b) * T + t] = min(p.top_k, gt_all + min(eq_all, need_row));
+    cluster.sync();  // counts and histograms are reused by the next query token; nobody leaves while a peer may read
+  }
+}
+
 // The tile.  smem: dynamic shared memory base (1024 B aligned), laid out by
 // logits_smem_layout.  All logits_threads(GG) threads of the block call it.
-template <int FMT, int PAGE, int T, int DG, int GG>
+template <int FMT, int PAGE, int T, int DG, int GG, bool ROWK = false>
 __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsigned char* smem) {
   using PG = IdxPage<FMT, PAGE>;
   constexpr int N = T * kIdxHeads;
@@ -210,7 +356,8 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   static_assert(kRawStages % DG == 0 && kASt % DG == 0 && kASt % GG == 0, "ring sizes must be multiples of the group counts");
   static_assert(kRawStages * PG::kTilePages <= 32, "one copy-warp lane per page of the raw ring");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool fused = p.cand_v != nullptr;
+  const bool row_mode = ROWK && p.row_v != nullptr;
+  const bool fused = p.cand_v != nullptr || row_mode;
   const int chunk_tokens = p.blocks_per_chunk * PAGE;
   const LogitsSmem L = logits_smem_layout<FMT, PAGE>(T, chunk_tokens, fused);
 
@@ -507,7 +654,15 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
   if (tid == 0) {  // the shared memory is reused by the next task of a persistent block
     for (int i = 0; i < 2 * kRawStages + kAStages; ++i) mbar_inval(raw_full + i);
   }
-  if (warp >= kWarps || failed) return;
+  if (warp >= kWarps) return;
+  if (ROWK && row_mode) {
+    // every block of the cluster walks the same barriers, also one whose pipeline gave up
+    logits_row_select<T>(p, b, chunk, failed ? 0 : n_pages * PAGE, blk0 * PAGE, limit, chunk_tokens, scores,
+                         *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel),
+                         *reinterpret_cast<RowSelectScratch*>(smem + L.row));
+    return;
+  }
+  if (failed) return;
 
   if (fused) {
     const int n_local = n_pages * PAGE;

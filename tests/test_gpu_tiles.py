@@ -296,3 +296,43 @@ def test_sparse_mla_bf16_partial_output_and_paged_pool():
     ro, rl = mla_oracle(case, None, scale)
     assert (o - ro).abs().max() < 2e-2
     assert (l - rl).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("fmt,P,T,K,bpc,S,seq,wex", [
+    ("nvfp4", 64, 1, 2048, 128, 32768, 32768, 0),    # BASELINE config 2 row: 4 chunks of 8192
+    ("nvfp4", 64, 1, 2048, 64, 32768, 30011, 0),     # 8 chunks, ragged length
+    ("nvfp4", 64, 1, 512, 32, 4096, 4096, 0),        # 2 chunks
+    ("nvfp4", 64, 1, 2048, 16, 1024, 1024, 0),       # 1 chunk, fewer entries than k
+    ("mxfp4", 128, 2, 1024, 32, 16384, 16000, 128),  # reference format, two query tokens, window excluded
+])
+def test_row_topk_equals_fused_plus_merge(fmt, P, T, K, bpc, S, seq, wex):
+    """One-launch row mode (cluster-wide select) against fused candidates + merge: same
+    entries in the same order, bit for bit."""
+    from mega_dsa_cp_b200.tiles.logits import run_fp4_paged_mqa_logits
+    from mega_dsa_cp_b200.tiles.merge import run_merge_topk
+
+    B = 3
+    case = indexer_case(B, S, P, fmt, q_len=T, q_fp4=(fmt == "mxfp4"), seed=5)
+    seq_lens = torch.tensor([seq, max(seq - 1234, 1), min(seq, 700)], dtype=torch.int32)
+    cv, ci, cc = _run_logits(case, bpc, fused_k=K, seq_lens=seq_lens, window_exclude=wex, id_mul=2, id_add=1)
+    ov = torch.empty(B, T, K, device=DEV)
+    oi = torch.empty(B, T, K, dtype=torch.int32, device=DEV)
+    oc = torch.empty(B, T, dtype=torch.int32, device=DEV)
+    run_merge_topk(cv.to(DEV), ci.to(DEV), cc.to(DEV), ov, oi, oc, None, top_k=K)
+    rv = torch.full((B, T, K), float("nan"), device=DEV)
+    ri = torch.full((B, T, K), -1, dtype=torch.int32, device=DEV)
+    rc = torch.zeros(B, T, dtype=torch.int32, device=DEV)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    q_sf = None if case["q_sf"] is None else case["q_sf"].to(DEV)
+    for _ in range(2):  # twice: the second launch must not depend on what the first left behind
+        run_fp4_paged_mqa_logits(case["fused"].to(DEV), case["q"].to(DEV), q_sf, case["w"].to(DEV), case["bt"].to(DEV),
+                                 None, bpc, seq_lens=seq_lens.to(DEV), top_k=K, window_exclude=wex, id_mul=2, id_add=1,
+                                 fmt=fmt, page_tokens=P, status=status, row_topk=(rv, ri, rc))
+    torch.cuda.synchronize()
+    assert status[0].item() == 0, status.tolist()
+    assert torch.equal(rc, oc)
+    for b in range(B):
+        for t in range(T):
+            n = int(oc[b, t])
+            assert torch.equal(ri[b, t, :n], oi[b, t, :n]), (b, t)
+            assert torch.equal(rv[b, t, :n].view(torch.int32), ov[b, t, :n].view(torch.int32)), (b, t)
