@@ -314,6 +314,11 @@ typedef struct {
   int64_t test_off;            /* arena offset of the test region (PUSH / VERIFY) */
   int32_t test_slot_bytes;
   mdc_layer_params layer;
+  /* Optional task timeline (NULL = off): trace[0] counts entries; entry i occupies the four
+   * words trace[4+4i..]: (block << 32 | op << 24 | (c0 & 0xfff) << 12 | (c1 & 0xfff)),
+   * globaltimer ns at task start, after its waits, at its end (after the notifies). */
+  unsigned long long* trace;
+  int32_t trace_cap;           /* entries                                        */
 } mdc_mega_params;
 int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
 int mdc_megakernel_smem_bytes(void);

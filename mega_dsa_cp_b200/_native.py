@@ -89,6 +89,7 @@ class MegaParams(C.Structure):
         ("scopes", p_void), ("n_events", i32), ("events", EventSetC), ("arena", PeerBufferC),
         ("wait_budget_ns", i64), ("status", p_void), ("log", p_void), ("log_cap", i32),
         ("test_off", i64), ("test_slot_bytes", i32), ("layer", LayerParams),
+        ("trace", p_void), ("trace_cap", i32),
     ]
 
 

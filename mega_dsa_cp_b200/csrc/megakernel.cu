@@ -17,12 +17,14 @@
 #include "tile_lse_merge.cuh"
 #include "tile_merge.cuh"
 #include "tile_mla.cuh"
+#include "tile_mla_umma.cuh"
 
 namespace mdc {
 
 constexpr int kMegaThreads = logits_threads(2, 1);  // one gate group: leaves 128 registers per thread to the attention op
+static_assert(kMegaThreads == kMuThreads, "the attention tile and the logits tile share one warp layout");
 constexpr int kStagedWords = 128;  // queue rows up to this length are staged in shared memory
-constexpr int kMegaTileSmem = MlaSmem<576>::kTotal;  // the largest tile
+constexpr int kMegaTileSmem = MlaUmmaSmem<576>::kTotal > MlaSmem<576>::kTotal ? MlaUmmaSmem<576>::kTotal : MlaSmem<576>::kTotal;  // the largest tile
 
 struct MegaShared {
   int32_t row[kStagedWords];
@@ -129,10 +131,12 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
 }
 
-// attention of 64 heads of sequence b over this rank's share of the selection;
-// the normalised partial (bf16) and its log2-LSE go straight into the owner's inbox
+// attention of sequence b over this rank's share of the selection; the normalised partial
+// (bf16) and its log2-LSE go straight into the owner's inbox.  With bf16 operands and heads in
+// blocks of 128 a task is 128 heads x 128 output columns on the tcgen05 tile (task index =
+// 4 * head block + column block, all threads take part); otherwise 64 heads x 256 columns on
+// the mma.sync tile (task index = 2 * head block + column half, worker threads only).
 __device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, unsigned long long phase, unsigned char* smem) {
-  const int hb = hbv >> 1, dv0 = (hbv & 1) * 256;  // task = 64 heads x 256 output columns
   const mdc_layer_params& L = p.layer;
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
                          p.arena.mc_base};
@@ -141,6 +145,13 @@ __device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, unsigne
                       (static_cast<int64_t>(b / L.cp) * L.cp + L.rank) * inbox_slice_bytes(L);
   unsigned char* slot = arena.peer_ptr(off, owner);
   float* lse_row = reinterpret_cast<float*>(slot + static_cast<int64_t>(L.H) * kMlaDv * 2);
+  if (L.mla.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
+    if (L.mla.d_qk == 576) mla_umma_tile<576>(L.mla, b, hbv >> 2, hbv & 3, 0, 1, smem, slot, lse_row);
+    else mla_umma_tile<512>(L.mla, b, hbv >> 2, hbv & 3, 0, 1, smem, slot, lse_row);
+    return;
+  }
+  if (threadIdx.x >= kBlockThreads) return;
+  const int hb = hbv >> 1, dv0 = (hbv & 1) * 256;
   if (L.mla.d_qk == 576 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
   else if (L.mla.d_qk == 512 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
   else if (L.mla.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
@@ -223,6 +234,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
   const mdc_layer_params& L = p.layer;
 
   for (TaskInfo t = cur.read(0); t.valid(); t = cur.advance(t)) {
+    unsigned long long tr0 = 0, tr1 = 0;
+    if (p.trace && tid == 0) tr0 = global_timer_ns();
     // ---- waits: thread 0 polls, the barrier publishes
     if (tid == 0) {
       if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) sh.fail = 1;
@@ -238,6 +251,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     }
     __syncthreads();
     if (sh.fail) break;
+    if (p.trace && tid == 0) tr1 = global_timer_ns();
 
     // ---- the task body
     switch (t.op) {
@@ -258,7 +272,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         }
         break;
       case MDC_OP_ATTN:
-        if (worker) op_attn(p, t.c0, t.c1, cur.phase, smem);
+        op_attn(p, t.c0, t.c1, cur.phase, smem);
         break;
       case MDC_OP_LSE_MERGE:
         if (worker) {
@@ -302,6 +316,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
           if (e >= 0 && e < p.n_events && dst < ev.world) ev.notify_1t(e, dst);
           else report_failure(p.status, MDC_DEV_BAD_OP, e, dst, 0, 0);
         }
+      }
+    }
+    if (p.trace && tid == 0) {
+      const unsigned long long slot = atomicAdd(p.trace, 1ull);
+      if (slot < static_cast<unsigned long long>(p.trace_cap)) {
+        unsigned long long* e = p.trace + 4 + 4 * slot;
+        e[0] = (static_cast<unsigned long long>(blockIdx.x) << 32) | (static_cast<unsigned long long>(t.op & 0xff) << 24) |
+               (static_cast<unsigned long long>(t.c0 & 0xfff) << 12) | static_cast<unsigned long long>(t.c1 & 0xfff);
+        e[1] = tr0;
+        e[2] = tr1;
+        e[3] = global_timer_ns();
       }
     }
     __syncthreads();

@@ -1,6 +1,9 @@
 // Launch wrapper of the sparse-MLA tile (see tile_mla.cuh) and of the split
 // combine that follows it when the slot range is split.
+#include <cstdlib>
+
 #include "tile_mla.cuh"
+#include "tile_mla_umma.cuh"
 #include "tile_lse_merge.cuh"
 
 namespace mdc {
@@ -15,6 +18,32 @@ __global__ void __launch_bounds__(kBlockThreads) mla_combine_kernel(const __grid
   __shared__ float scale[kLseMaxSlices * 16];
   const int h0 = blockIdx.y * 16;
   lse_merge_tile<false>(p, blockIdx.x, h0, min(16, p.H - h0), scale);
+}
+
+// tcgen05 path: bf16 operands, blocks of 128 heads x 128 output columns
+template <int DQK>
+__global__ void __launch_bounds__(kMuThreads, 1) mla_umma_kernel(const __grid_constant__ mdc_sparse_mla_params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int hb = blockIdx.y >> 2, dq = blockIdx.y & 3;
+  mla_umma_tile<DQK>(p, blockIdx.z, hb, dq, blockIdx.x, gridDim.x, smem);
+}
+
+template <int DQK>
+static int launch_mla_umma(const mdc_sparse_mla_params& p, cudaStream_t st) {
+  auto kern = mla_umma_kernel<DQK>;
+  const int smem = MlaUmmaSmem<DQK>::kTotal + 1024;
+  MDC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid(p.n_splits, (p.H / kMuHeads) * (kMlaDv / kMuDv), p.B * p.q_len);
+  kern<<<grid, kMuThreads, smem, st>>>(p);
+  MDC_CUDA_OK(cudaGetLastError());
+  return MDC_OK;
+}
+
+// The tensor-memory path takes bf16 operands with heads in blocks of 128 and exact (unrounded) probabilities.
+static bool mla_use_umma(const mdc_sparse_mla_params& p) {
+  static const bool legacy = std::getenv("MDC_MLA_LEGACY") != nullptr;  // A/B switch for measurements
+  return !legacy && p.kv_dtype == MDC_DT_BF16 && p.H % kMuHeads == 0 && p.fp8_p == 0;
 }
 
 template <int DQK, int KVDT>
@@ -63,7 +92,8 @@ extern "C" int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* strea
   int rc = mla_check(p);
   if (rc != MDC_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->d_qk == 576 && p->kv_dtype == MDC_DT_BF16) rc = launch_mla<576, MDC_DT_BF16>(*p, st);
+  if (mla_use_umma(*p)) rc = p->d_qk == 576 ? launch_mla_umma<576>(*p, st) : launch_mla_umma<512>(*p, st);
+  else if (p->d_qk == 576 && p->kv_dtype == MDC_DT_BF16) rc = launch_mla<576, MDC_DT_BF16>(*p, st);
   else if (p->d_qk == 512 && p->kv_dtype == MDC_DT_BF16) rc = launch_mla<512, MDC_DT_BF16>(*p, st);
   else if (p->d_qk == 576) rc = launch_mla<576, MDC_DT_E4M3>(*p, st);
   else rc = launch_mla<512, MDC_DT_E4M3>(*p, st);

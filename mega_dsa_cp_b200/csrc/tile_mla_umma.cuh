@@ -1,0 +1,402 @@
+// Sparse MLA decode-attention tile on the 5th-generation tensor cores: 128
+// query heads of one (b, t) row against a range of KV slots, 128 of the 512
+// output columns per block (four blocks cover a row's output; each repeats the
+// cheap-to-issue Q.K^T so that the output accumulator fits tensor memory).
+//
+// Tensor memory (512 columns x 128 lanes, lane = head):
+//   Q   DQK/2 columns   bf16 pairs, the A operand of S = Q K^T, loaded once
+//   O   128 columns     fp32 output accumulator
+//   S   64 columns      fp32 logits of the current 64-slot tile
+//   P   32 columns      bf16 probabilities, the A operand of O += P V
+// Shared memory: a ring of KV tiles, each 64 slots x DQK bf16 stored as DQK/64
+// panels of 64 rows x 128 bytes with the 128-byte swizzle.  One image serves
+// both products: a panel is a K-major B operand for Q K^T (row = slot, 64 dims
+// per row) and, read "MN-major", the B operand of P V (for a fixed slot the 64
+// output columns are contiguous), so V needs no transposed copy.
+//
+// Roles (448 threads): warps 0-3 softmax (thread = head: no cross-thread
+// reductions; reads S with tcgen05.ld, writes P with tcgen05.st, rescales O
+// only when the running maximum grew by more than 2^8), warps 4-11 gather KV
+// rows with 16-byte cp.async (a warp instruction reads 512 contiguous bytes of
+// one row), warp 12 issues the MMAs.  Per tile: 36 x (M128 N64 K16) for Q K^T,
+// 4 x (M128 N128 K16) for P V.  All waits are bounded.
+#pragma once
+
+#include "common.cuh"
+#include "tile_mla.cuh"
+#include "umma.cuh"
+
+namespace mdc {
+
+constexpr int kMuHeads = 128;   // heads per block (= UMMA M)
+constexpr int kMuTile = 64;     // slots per tile
+constexpr int kMuDv = 128;      // output columns per block
+constexpr int kMuThreads = 448;
+constexpr int kMuGatherWarp0 = 4, kMuGatherWarps = 8, kMuIssueWarp = 12;
+
+template <int DQK>
+struct MlaUmmaSmem {
+  static constexpr int kPanels = DQK / 64;
+  static constexpr int kStageBytes = kPanels * kMuTile * 128;
+  // as many stages as fit beside ~3 KB of bookkeeping in 226 KB
+  static constexpr int kStages = (226 * 1024 - 3072) / kStageBytes >= 3 ? 3 : 2;
+  static constexpr int kK = 0;
+  static constexpr int kBars = kStages * kStageBytes;   // full[S], free[S], s_ready, p_ready, q_ready, o_final
+  static constexpr int kMisc = kBars + (2 * kStages + 4) * 8;  // [0] tmem base, [1] abort flag
+  static constexpr int kValid = kMisc + 64;                     // [S][8] bytes: validity bits of 8 slots per gather warp
+  static constexpr int kTotal = kValid + kStages * 8 + 56;
+};
+
+namespace umma {
+// Shared-memory B operand read MN-major with the 128-byte swizzle: for one K index (row of 128
+// bytes) 64 consecutive N elements; 8 K rows form a 1024-byte atom.  lbo = bytes between
+// consecutive 64-element N blocks, sbo = bytes between consecutive groups of 8 K rows.
+__device__ inline uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3fff) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// kind::f16 instruction descriptor, bf16 operands, fp32 accumulator; b_mn = B operand MN-major
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ inline void tmem_ld32_f(uint32_t taddr, float (&v)[32]) {
+  uint32_t u[32];
+  tmem_ld32(taddr, u);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(u[i]);
+}
+}  // namespace umma
+
+// Gather one 64-slot tile: this warp's 8 rows.  Returns the validity bits of its rows.
+template <int DQK>
+__device__ inline uint32_t mla_umma_gather_rows(const mdc_sparse_mla_params& p, int r, int slot0, int k_valid, int win_valid,
+                                                unsigned char* stage, int gw, int lane) {
+  constexpr int kChunks = DQK / 8;  // 16-byte chunks per row
+  uint32_t bits = 0;
+#pragma unroll 2
+  for (int rr = 0; rr < 8; ++rr) {
+    const int s = gw * 8 + rr;
+    const unsigned char* src = mla_slot_ptr<DQK, 2>(p, r, slot0 + s, k_valid, win_valid);
+    bits |= static_cast<uint32_t>(src != nullptr) << rr;
+    const unsigned char* base = src ? src : static_cast<const unsigned char*>(p.kv_cmp);
+#pragma unroll
+    for (int ch = lane; ch < kChunks; ch += 32) {
+      unsigned char* dst = stage + (ch >> 3) * (kMuTile * 128) + s * 128 + (((ch & 7) ^ (s & 7)) << 4);
+      cp_async16_zfill(dst, base + ch * 16, src != nullptr);
+    }
+  }
+  cp_async_commit();
+  return bits;
+}
+
+// r = b*q_len + t, hb = block of 128 heads, dq = block of 128 output columns,
+// split / n_splits = slice of the slot range.  o_row / lse_row, when given,
+// replace p.o / p.lse for this row (they point at the row's (H, d_v) block and
+// (H,) vector, possibly in a peer GPU's memory).  All kMuThreads threads call it.
+template <int DQK>
+__device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int dq, int split, int n_splits,
+                              unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr) {
+  using SM = MlaUmmaSmem<DQK>;
+  constexpr int S = SM::kStages;
+  constexpr uint32_t kQCols = DQK / 2, kOCol = kQCols, kSCol = kOCol + kMuDv, kPCol = kSCol + kMuTile;
+  static_assert(kPCol + kMuTile / 2 <= 512, "tensor memory over-subscribed");
+  constexpr long long kBudget = 1ll << 31;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned char* kst = smem + SM::kK;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::kBars);
+  uint64_t* free_ = full + S;
+  uint64_t* s_ready = free_ + S;
+  uint64_t* p_ready = s_ready + 1;
+  uint64_t* q_ready = p_ready + 1;
+  uint64_t* o_final = q_ready + 1;
+  uint32_t* misc = reinterpret_cast<uint32_t*>(smem + SM::kMisc);
+  volatile uint32_t* abort_flag = misc + 1;
+  unsigned char* validb = smem + SM::kValid;
+  const float neg_inf = __int_as_float(0xff800000);
+  const float c2 = p.softmax_scale * kLog2e;
+
+  const int k_valid = min(max(p.k_valid[r], 0), kWinSlots + p.pt_cols * p.page_cmp);
+  const int win_valid = p.win_valid ? min(max(p.win_valid[r], 0), kWinSlots) : 0;
+  const int n_tiles_all = ceil_div(k_valid, kMuTile);
+  const int first = (win_valid > 0 && p.kv_win) ? 0 : min(n_tiles_all, kWinSlots / kMuTile);
+  const int per = ceil_div(max(n_tiles_all - first, 0), n_splits);
+  const int t_begin = first + split * per;
+  const int n_my = max(0, min(n_tiles_all, t_begin + per) - t_begin);
+
+  __syncthreads();  // shared memory may be in use by the previous task of this block
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], kMuGatherWarps);
+      mbar_init(&free_[s], 1);
+    }
+    mbar_init(s_ready, 1);
+    mbar_init(p_ready, 4);
+    mbar_init(q_ready, 4);
+    mbar_init(o_final, 1);
+    misc[1] = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMuIssueWarp) umma::tmem_alloc(misc, 512);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = misc[0];
+  auto give_up = [&](int what, int idx) {
+    report_failure(p.status, MDC_DEV_COPY_TIMEOUT, 16 + what, idx, 0, 0);
+    *abort_flag = 1;
+  };
+
+  if (warp < 4) {
+    // ---------------- softmax warps: thread = head
+    const int h = hb * kMuHeads + warp * 32 + lane;
+    const uint32_t t_lane = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    {  // Q row -> tensor memory (bf16 pairs, 16 columns per store)
+      const uint4* qsrc = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.q) +
+                                                         (static_cast<int64_t>(r) * p.H + h) * DQK * 2);
+#pragma unroll 2
+      for (int j = 0; j < static_cast<int>(kQCols) / 16; ++j) {
+        uint32_t v[16];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint4 x = __ldg(qsrc + 4 * j + u);
+          v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
+        }
+        umma::tmem_st16(t_lane + 16 * j, v);
+      }
+      umma::wait_st();
+      umma::fence_before_sync();
+      __syncwarp();
+      mbar_arrive_if(q_ready, lane == 0);
+    }
+    float m_used = neg_inf, l = 0.f;
+    if (p.attn_sink && split == 0) {
+      const float sk = p.attn_sink[h];
+      if (sk != neg_inf) {
+        m_used = sk;
+        l = 1.f;
+      }
+    }
+    bool ok = true;
+    for (int i = 0; i < n_my; ++i) {
+      if (!mbar_wait(s_ready, i & 1, kBudget, abort_flag)) {
+        if (lane == 0) give_up(0, i);
+        ok = false;
+        break;
+      }
+      umma::fence_after_sync();
+      float sv[kMuTile];
+      {
+        float a[32], b[32];
+        umma::tmem_ld32_f(t_lane + kSCol, a);
+        umma::tmem_ld32_f(t_lane + kSCol + 32, b);
+        umma::wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = a[j];
+          sv[32 + j] = b[j];
+        }
+      }
+      const uint2 vb = *reinterpret_cast<const uint2*>(validb + (i % S) * 8);
+      float tmax = neg_inf;
+#pragma unroll
+      for (int j = 0; j < kMuTile; ++j) {
+        const bool valid = ((j < 32 ? vb.x >> j : vb.y >> (j - 32)) & 1u) != 0;
+        sv[j] = valid ? sv[j] : neg_inf;
+        tmax = fmaxf(tmax, sv[j]);
+      }
+      // the reference maximum moves only when the tile maximum exceeds it by more than 2^8
+      if (tmax > m_used && (m_used == neg_inf || (tmax - m_used) * c2 > 8.f)) {
+        const float corr = (m_used == neg_inf) ? 0.f : exp2f((m_used - tmax) * c2);
+        l *= corr;
+        if (i > 0) {
+#pragma unroll 1
+          for (int cb = 0; cb < kMuDv / 32; ++cb) {
+            uint32_t o[32];
+            umma::tmem_ld32(t_lane + kOCol + 32 * cb, o);
+            umma::wait_ld();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              lo[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+              hi[j] = __float_as_uint(__uint_as_float(o[16 + j]) * corr);
+            }
+            umma::tmem_st16(t_lane + kOCol + 32 * cb, lo);
+            umma::tmem_st16(t_lane + kOCol + 32 * cb + 16, hi);
+          }
+        }
+        m_used = tmax;
+      }
+      float ps = 0.f;
+      uint32_t pk[kMuTile / 2];
+#pragma unroll
+      for (int j = 0; j < kMuTile / 2; ++j) {
+        const float p0 = (m_used == neg_inf) ? 0.f : exp2f((sv[2 * j] - m_used) * c2);
+        const float p1 = (m_used == neg_inf) ? 0.f : exp2f((sv[2 * j + 1] - m_used) * c2);
+        ps += p0 + p1;
+        pk[j] = pack_bf16x2(p0, p1);
+      }
+      l += ps;
+      {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          lo[j] = pk[j];
+          hi[j] = pk[16 + j];
+        }
+        umma::tmem_st16(t_lane + kPCol, lo);
+        umma::tmem_st16(t_lane + kPCol + 16, hi);
+      }
+      umma::wait_st();
+      umma::fence_before_sync();
+      __syncwarp();
+      mbar_arrive_if(p_ready, lane == 0);
+    }
+    if (ok && n_my > 0 && !mbar_wait(o_final, 0, kBudget, abort_flag)) {
+      if (lane == 0) give_up(1, n_my);
+      ok = false;
+    }
+    umma::fence_after_sync();
+    if (ok) {
+      const bool live = l > 0.f;
+      const float inv = live ? p.output_scale / l : 0.f;
+      const float lse = live ? log2f(l) + c2 * m_used : neg_inf;
+      const bool direct = n_splits == 1;
+      if (dq == 0) {
+        if (direct) {
+          if (lse_row) lse_row[h] = lse;
+          else if (p.lse) p.lse[static_cast<int64_t>(r) * p.lse_stride + h] = lse;
+        } else {
+          p.ws_lse[(static_cast<int64_t>(r) * n_splits + split) * p.H + h] = lse;
+        }
+      }
+      const int col0 = dq * kMuDv;
+#pragma unroll 1
+      for (int cb = 0; cb < kMuDv / 32; ++cb) {
+        float o[32];
+        if (n_my > 0) {
+          umma::tmem_ld32_f(t_lane + kOCol + 32 * cb, o);
+          umma::wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= inv;
+        const int col = col0 + 32 * cb;
+        if (!direct) {
+          float4* dst = reinterpret_cast<float4*>(p.ws_o + ((static_cast<int64_t>(r) * n_splits + split) * p.H + h) * kMlaDv + col);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        } else if (p.out_dtype == MDC_DT_F32) {
+          float* base = (o_row ? static_cast<float*>(o_row) : static_cast<float*>(p.o) + static_cast<int64_t>(r) * p.o_stride) +
+                        static_cast<int64_t>(h) * kMlaDv + col;
+          float4* dst = reinterpret_cast<float4*>(base);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        } else {
+          __nv_bfloat16* base = (o_row ? static_cast<__nv_bfloat16*>(o_row)
+                                       : static_cast<__nv_bfloat16*>(p.o) + static_cast<int64_t>(r) * p.o_stride) +
+                                static_cast<int64_t>(h) * kMlaDv + col;
+          uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(pack_bf16x2(o[8 * j], o[8 * j + 1]), pack_bf16x2(o[8 * j + 2], o[8 * j + 3]),
+                                pack_bf16x2(o[8 * j + 4], o[8 * j + 5]), pack_bf16x2(o[8 * j + 6], o[8 * j + 7]));
+        }
+      }
+    }
+  } else if (warp >= kMuGatherWarp0 && warp < kMuGatherWarp0 + kMuGatherWarps) {
+    // ---------------- gather warps: 8 rows of every tile each, up to two tiles in flight per warp
+    const int gw = warp - kMuGatherWarp0;
+    bool ok = true;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int st = i % S;
+      if (i >= S && !mbar_wait(&free_[st], ((i / S) - 1) & 1, kBudget, abort_flag)) {
+        if (lane == 0) give_up(2, i);
+        ok = false;
+        break;
+      }
+      const uint32_t bits = mla_umma_gather_rows<DQK>(p, r, (t_begin + i) * kMuTile, k_valid, win_valid,
+                                                      kst + st * SM::kStageBytes, gw, lane);
+      if (lane == 0) validb[st * 8 + gw] = static_cast<unsigned char>(bits);
+      if (i >= 1) {
+        cp_async_wait<1>();
+        fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        mbar_arrive_if(&full[(i - 1) % S], lane == 0);
+      }
+    }
+    cp_async_wait<0>();
+    if (ok && n_my > 0) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      mbar_arrive_if(&full[(n_my - 1) % S], lane == 0);
+    }
+  } else if (warp == kMuIssueWarp) {
+    // ---------------- issue warp
+    constexpr uint32_t idesc_qk = umma::idesc_bf16(kMuHeads, kMuTile, false);
+    constexpr uint32_t idesc_pv = umma::idesc_bf16(kMuHeads, kMuDv, true);
+    const uint32_t kst_u = smem_u32(kst);
+    bool ok = mbar_wait(q_ready, 0, kBudget, abort_flag);
+    if (!ok && lane == 0) give_up(3, 0);
+    auto issue_pv = [&](int i) {  // O (+)= P V of tile i: 4 K-steps of 16 slots
+      const uint32_t base = kst_u + (i % S) * SM::kStageBytes + (dq * kMuDv / 64) * (kMuTile * 128);
+#pragma unroll
+      for (int kk = 0; kk < kMuTile / 16; ++kk) {
+        const uint64_t bdesc = umma::smem_desc_mn_sw128(base + kk * 2048, kMuTile * 128, 1024);
+        umma::mma_f16_ts(tmem + kOCol, tmem + kPCol + 8 * kk, bdesc, idesc_pv, i > 0 || kk > 0);
+      }
+      umma::commit(&free_[i % S]);
+    };
+    for (int i = 0; i < n_my && ok; ++i) {
+      ok = mbar_wait(&full[i % S], (i / S) & 1, kBudget, abort_flag);
+      if (ok && i > 0) ok = mbar_wait(p_ready, (i - 1) & 1, kBudget, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) give_up(4, i);
+        ok = false;
+        break;
+      }
+      umma::fence_after_sync();
+      if (umma::elect_one()) {
+        if (i > 0) issue_pv(i - 1);
+        const uint32_t base = kst_u + (i % S) * SM::kStageBytes;
+#pragma unroll 4
+        for (int k = 0; k < DQK / 16; ++k) {
+          const uint64_t bdesc = umma::smem_desc_sw128(base + (k >> 2) * (kMuTile * 128) + (k & 3) * 32);
+          umma::mma_f16_ts(tmem + kSCol, tmem + 8 * k, bdesc, idesc_qk, k > 0);
+        }
+        umma::commit(s_ready);
+      }
+      __syncwarp();
+    }
+    if (ok && n_my > 0) {
+      ok = mbar_wait(p_ready, (n_my - 1) & 1, kBudget, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) give_up(5, n_my);
+      } else {
+        umma::fence_after_sync();
+        if (umma::elect_one()) {
+          issue_pv(n_my - 1);
+          umma::commit(o_final);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  if (warp == kMuIssueWarp) umma::tmem_dealloc(tmem, 512);
+  if (tid == 0) {
+    for (int i = 0; i < 2 * S + 4; ++i) mbar_inval(full + i);
+  }
+}
+
+}  // namespace mdc

@@ -156,12 +156,12 @@ class DsaDecodeLayer:
         L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
         self._params, self._inputs = L, x
 
-    def step(self, wait_budget_ns: int = 2_000_000_000, stream=None) -> None:
+    def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None) -> None:
         """Launches one layer-step (asynchronous).  Every rank must call it with the same phase."""
         assert self._params is not None, "bind() inputs first"
         self.dsched.scalars[0:1].fill_(self.phase)
         launch_megakernel(self.dsched, self.events, self.arena, self.status, layer=self._params,
-                          wait_budget_ns=wait_budget_ns, stream=stream)
+                          wait_budget_ns=wait_budget_ns, stream=stream, trace=trace)
         self.phase += 1
 
     def owned_rows(self):

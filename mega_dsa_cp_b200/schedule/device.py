@@ -47,8 +47,9 @@ def upload_schedule(schedule: Schedule, device="cuda", n_scalars: int = 8) -> De
 def launch_megakernel(ds: DeviceSchedule, events: EventBuffer, arena: SymmetricArena | None, status: torch.Tensor,
                       layer: N.LayerParams | None = None, log: torch.Tensor | None = None,
                       wait_budget_ns: int = 2_000_000_000, test_off: int = 0, test_slot_bytes: int = 0,
-                      stream=None) -> None:
-    """One launch of the persistent kernel on this rank (asynchronous)."""
+                      stream=None, trace: torch.Tensor | None = None) -> None:
+    """One launch of the persistent kernel on this rank (asynchronous).  `trace`: optional int64
+    tensor of 4 + 4 * entries words that receives the task timeline (word 0 = entry count)."""
     p = N.MegaParams()
     p.queue, p.row_words, p.n_ctas = N.ptr(ds.queue), ds.row_words, ds.n_ctas
     p.scalars, p.arity, p.scopes, p.n_events = N.ptr(ds.scalars), N.ptr(ds.arity), N.ptr(ds.scopes), ds.n_events
@@ -65,4 +66,6 @@ def launch_megakernel(ds: DeviceSchedule, events: EventBuffer, arena: SymmetricA
     p.test_off, p.test_slot_bytes = test_off, test_slot_bytes
     if layer is not None:
         p.layer = layer
+    p.trace = N.ptr(trace)
+    p.trace_cap = 0 if trace is None else (trace.numel() - 4) // 4
     N.call("mdc_megakernel_launch", p, stream)
