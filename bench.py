@@ -307,6 +307,10 @@ def run_gpu_cfg2(args):
         "cpu_baseline": cpu,
         "clocks": clk.summary(),
     }
+    if not args.skip_layer:
+        caches.clear()
+        torch.cuda.empty_cache()
+        line["decode_step_cp1"] = cp1_layer_step(min(args.steps, 20), args.warmup, dev)
     print(json.dumps(line))
 
 
@@ -317,6 +321,48 @@ def cp_config(n):
     """128K-token context sharded over n ranks, 8 sequences per rank (BASELINE
     config 4 at n = 8: B = 64, 16384 tokens per rank per sequence)."""
     return dict(B=8 * n, S=131072, page=64, top_k=2048, H=128, d_qk=576, cp=n, copies=2, blocks_per_chunk=128)
+
+
+def cp1_layer_step(steps, warmup, dev):
+    """The full decode layer-step at CP=1 (B = 8 sequences of 128 K tokens, one megakernel launch),
+    reported beside the N=1 line so that the CP=2/4/8 runs have their single-GPU counterpart."""
+    import torch
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+
+    c = cp_config(1)
+    B, P, K, H, DQK, S = c["B"], c["page"], c["top_k"], c["H"], c["d_qk"], c["S"]
+    pages = S // P
+    g = torch.Generator(device=dev).manual_seed(1000)
+    q_idx = torch.randn(B, 64, 128, generator=g, device=dev).to(torch.bfloat16)
+    w_idx = (torch.randn(B, 64, generator=g, device=dev) / 64.0).contiguous()
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    seq = torch.full((B,), S, dtype=torch.int32, device=dev)
+    layers = []
+    for _ in range(c["copies"]):
+        parts = [fuse_pages(torch.randn(B * S // 8, 128, generator=g, device=dev), "nvfp4", P)[0] for _ in range(8)]
+        cache = torch.cat(parts)
+        bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages).contiguous()
+        kv = (torch.randn(B * S, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+        layer = DsaDecodeLayer(B, cp=1, rank=0, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
+                               blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S, device=dev)
+        layer.bind(LayerInputs(cache, bt, seq, q_idx, w_idx, q_mla, kv))
+        layers.append(layer)
+    for i in range(max(warmup, len(layers))):
+        layers[i % len(layers)].step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        layers[i % len(layers)].step()
+    e1.record()
+    torch.cuda.synchronize()
+    for l in layers:
+        l.check_status()
+    ms = e0.elapsed_time(e1) / steps
+    return {"step_us": ms * 1e3, "tokens_per_s": B / (ms * 1e-3), "gpu_launches_per_step": 1,
+            "config": f"full DSA decode layer-step, CP=1: B={B}, ctx {S}, indexer + top-k {K} + sparse MLA "
+                      f"(128 heads, 512+64) + LSE merge, one persistent kernel"}
 
 
 def run_gpu_cp(args):
@@ -503,6 +549,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--copies", type=int, default=None, help="rotation copies of the index cache (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
+    ap.add_argument("--skip-layer", action="store_true", help="N=1: omit the CP=1 full layer-step leg")
     ap.add_argument("--two-kernel", action="store_true",
                     help="N=1: chunk candidates + merge kernel (the reference's two launches) instead of the one-launch row mode")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying CUDA graphs")

@@ -259,8 +259,8 @@ typedef struct {
 #define MDC_OP_LOGITS 1     /* c0 = b, c1 = chunk                                  */
 #define MDC_OP_MERGE_L1 2   /* c0 = b: chunk lists -> local top-k -> every rank    */
 #define MDC_OP_MERGE_L2 3   /* c0 = b: cp lists -> global top-k + local gather list */
-#define MDC_OP_ATTN 4       /* c0 = b, c1 = 2*head block + output-column half: partial -> owner inbox */
-#define MDC_OP_LSE_MERGE 5  /* c0 = b (owned): inbox slices -> output              */
+#define MDC_OP_ATTN 4       /* c0 = b, c1 = head/column block (see megakernel.cu), c2 = slot split: partial -> owner inbox */
+#define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
 #define MDC_OP_PUSH 18      /* c1 = dst rank, c2 = slot: bulk push a pattern (test op) */
@@ -278,7 +278,7 @@ typedef struct {
   int32_t cp, rank, B, top_k, H;
   int32_t n_chunks;             /* chunks per sequence in `logits`             */
   int32_t kv_seq_stride;        /* KV pool row of local token l of sequence b = b*kv_seq_stride + l */
-  int32_t reserved0;
+  int32_t attn_splits;          /* ATTN tasks per (b, block) over the slot range (0 or 1 = no split); inbox holds cp * attn_splits slices per sequence */
   mdc_logits_params logits;     /* fused mode; cand_* = chunk candidate scratch */
   mdc_sparse_mla_params mla;    /* local KV pool; pt_cmp/k_valid = local gather list written by MERGE_L2 */
   int64_t cand_off, inbox_off;  /* byte offsets of the regions inside one phase */

@@ -75,7 +75,7 @@ class PeerBufferC(C.Structure):
 class LayerParams(C.Structure):
     _fields_ = [
         ("cp", i32), ("rank", i32), ("B", i32), ("top_k", i32), ("H", i32), ("n_chunks", i32),
-        ("kv_seq_stride", i32), ("reserved0", i32),
+        ("kv_seq_stride", i32), ("attn_splits", i32),
         ("logits", LogitsParams), ("mla", SparseMlaParams),
         ("cand_off", i64), ("inbox_off", i64), ("phase_bytes", i64), ("phases", i32),
         ("sel_v", p_void), ("sel_i", p_void), ("sel_c", p_void), ("out", p_void), ("out_lse", p_void),

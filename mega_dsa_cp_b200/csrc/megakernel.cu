@@ -136,42 +136,52 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
 // blocks of 128 a task is 128 heads x 128 output columns on the tcgen05 tile (task index =
 // 4 * head block + column block, all threads take part); otherwise 64 heads x 256 columns on
 // the mma.sync tile (task index = 2 * head block + column half, worker threads only).
-__device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, unsigned long long phase, unsigned char* smem) {
+__device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, int split, unsigned long long phase,
+                               unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
                          p.arena.mc_base};
   const int owner = b % L.cp;
+  const int ns = max(1, L.attn_splits);
+  split = min(max(split, 0), ns - 1);
   const int64_t off = phase_offset(p, phase) + L.inbox_off +
-                      (static_cast<int64_t>(b / L.cp) * L.cp + L.rank) * inbox_slice_bytes(L);
+                      ((static_cast<int64_t>(b / L.cp) * L.cp + L.rank) * ns + split) * inbox_slice_bytes(L);
   unsigned char* slot = arena.peer_ptr(off, owner);
   float* lse_row = reinterpret_cast<float*>(slot + static_cast<int64_t>(L.H) * kMlaDv * 2);
   if (L.mla.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
-    if (L.mla.d_qk == 576) mla_umma_tile<576>(L.mla, b, hbv >> 2, hbv & 3, 0, 1, smem, slot, lse_row);
-    else mla_umma_tile<512>(L.mla, b, hbv >> 2, hbv & 3, 0, 1, smem, slot, lse_row);
+    if (L.mla.d_qk == 576) mla_umma_tile<576>(L.mla, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
+    else mla_umma_tile<512>(L.mla, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
     return;
   }
   if (threadIdx.x >= kBlockThreads) return;
   const int hb = hbv >> 1, dv0 = (hbv & 1) * 256;
-  if (L.mla.d_qk == 576 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
-  else if (L.mla.d_qk == 512 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
-  else if (L.mla.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
-  else mla_tile<512, MDC_DT_E4M3, 256>(L.mla, b, hb, 0, 1, smem, slot, lse_row, dv0);
+  if (L.mla.d_qk == 576 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else if (L.mla.d_qk == 512 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else if (L.mla.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else mla_tile<512, MDC_DT_E4M3, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
 }
 
 // owner of sequence b: cp inbox slices -> merged output
+// (task = head group hq of n_groups: the merge of one sequence is spread over several blocks)
 template <bool SYS>
-__device__ inline void op_lse_merge(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+__device__ inline void op_lse_merge(const mdc_mega_params& p, int b, int hq, int n_groups, unsigned long long phase,
+                                    unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
-  const int64_t off = phase_offset(p, phase) + L.inbox_off + static_cast<int64_t>(b / L.cp) * L.cp * inbox_slice_bytes(L);
+  n_groups = max(1, min(n_groups, L.H));
+  const int nh = ceil_div(L.H, n_groups);
+  const int h0 = min(max(hq, 0), n_groups - 1) * nh;
+  const int n_heads = max(0, min(nh, L.H - h0));
+  const int ns = max(1, L.attn_splits);
+  const int64_t off = phase_offset(p, phase) + L.inbox_off + static_cast<int64_t>(b / L.cp) * L.cp * ns * inbox_slice_bytes(L);
   LseSrc src;
   src.o = static_cast<const unsigned char*>(p.arena.base) + off;
   src.lse = reinterpret_cast<const float*>(src.o + static_cast<int64_t>(L.H) * kMlaDv * 2);
   src.o_stride = inbox_slice_bytes(L);
   src.lse_stride = inbox_slice_bytes(L) / 4;
   const int osz = (L.out_dtype == MDC_DT_F32) ? 4 : 2;
-  lse_merge_rows<SYS>(src, L.cp, L.H, kMlaDv, MDC_DT_BF16, L.out_dtype,
+  lse_merge_rows<SYS>(src, L.cp * ns, L.H, kMlaDv, MDC_DT_BF16, L.out_dtype,
                       static_cast<unsigned char*>(L.out) + static_cast<int64_t>(b) * L.H * kMlaDv * osz,
-                      L.out_lse ? L.out_lse + static_cast<int64_t>(b) * L.H : nullptr, 0, L.H,
+                      L.out_lse ? L.out_lse + static_cast<int64_t>(b) * L.H : nullptr, h0, n_heads,
                       reinterpret_cast<float*>(smem));
 }
 
@@ -272,12 +282,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         }
         break;
       case MDC_OP_ATTN:
-        op_attn(p, t.c0, t.c1, cur.phase, smem);
+        op_attn(p, t.c0, t.c1, t.c2, cur.phase, smem);
         break;
       case MDC_OP_LSE_MERGE:
         if (worker) {
-          if (L.cp > 1) op_lse_merge<true>(p, t.c0, cur.phase, smem);
-          else op_lse_merge<false>(p, t.c0, cur.phase, smem);
+          if (L.cp > 1) op_lse_merge<true>(p, t.c0, t.c1, t.c2, cur.phase, smem);
+          else op_lse_merge<false>(p, t.c0, t.c1, t.c2, cur.phase, smem);
         }
         break;
       case MDC_OP_SLEEP:

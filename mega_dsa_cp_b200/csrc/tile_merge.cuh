@@ -18,10 +18,13 @@ constexpr int kMergeMaxLists = 256;
 
 constexpr int kMergeRegE = 32;  // register path: up to 256 * 32 = 8192 candidate positions per row
 
+constexpr int kMergeBigE = 64;  // keys of up to 256 * 64 = 16384 positions stay in registers for the search
+
 struct MergeSmem {
   union {
     SelectScratch sel;
     RegSelectScratch<kMergeRegE> rsel;
+    RegSelectScratch<kMergeBigE> rsel_big;
   };
   int32_t cnt[kMergeMaxLists];
 };
@@ -330,6 +333,69 @@ __device__ inline int merge_staged_regs(int n_pos, int top_k, float* out_v, int3
   return min(n, top_k);
 }
 
+// Staged rows of up to 256 * E positions, E too large to also keep the output
+// slots in registers: the search runs on register keys (no shared-memory
+// traffic per bit), the emit walks shared memory.
+template <int E>
+__device__ inline int merge_staged_hybrid(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
+                                          MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
+  const int tid = threadIdx.x;
+  auto put = [&](int pos, int slot) {
+    if (slot < top_k) {
+      out_v[slot] = unsortable_f32(vb[pos]);
+      out_i[slot] = ib[pos];
+    }
+  };
+  Threshold<uint32_t> th;
+  int n_eq = 0;
+  {
+    uint32_t key[E];
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      const int pos = it * kBlockThreads + tid;
+      key[it] = pos < n_pos ? vb[pos] : 0u;
+    }
+    th = block_select_regs<E>(key, top_k, sm.rsel_big);
+    if (th.need_eq != 0x7fffffff) {
+      int c = 0;
+#pragma unroll
+      for (int it = 0; it < E; ++it) c += key[it] == th.tau;
+      n_eq = workers_sum(c, sm.rsel_big.wcnt);
+    }
+  }
+  const int expect = th.n_sel;
+  int n;
+  sync_workers();
+  if (th.need_eq == 0x7fffffff || n_eq == th.need_eq) {
+    n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, th,
+                                      sm.sel, put);
+  } else {
+    const uint32_t tau = th.tau;
+    auto key2 = [&](int pos) -> uint32_t {
+      const uint32_t kv = vb[pos];
+      return kv > tau ? 0xffffffffu : (kv == tau ? max(~static_cast<uint32_t>(ib[pos]), 1u) : 0u);
+    };
+    Threshold<uint32_t> t2;
+    {
+      uint32_t k2[E];
+#pragma unroll
+      for (int it = 0; it < E; ++it) {
+        const int pos = it * kBlockThreads + tid;
+        k2[it] = pos < n_pos ? key2(pos) : 0u;
+      }
+      t2 = block_select_regs<E>(k2, top_k, sm.rsel_big);
+    }
+    sync_workers();
+    n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { const uint32_t k2 = key2(pos); valid = k2 != 0u; return k2; },
+                                      n_pos, t2, sm.sel, put);
+  }
+  if (tid == 0) {
+    *out_c = min(n, top_k);
+    if (n != expect && dbg) atomicAdd(dbg, 1);
+  }
+  return min(n, top_k);
+}
+
 // Staged rows of any size: bitwise search over the shared-memory keys.  Ties on
 // the logit are resolved in the same search by a second key: entries above the
 // logit threshold rank highest, tied entries rank by ~id, everything else is out.
@@ -381,6 +447,8 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
     merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
     if (n_pos <= kBlockThreads * kMergeRegE)
       return merge_staged_regs<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
+    if (n_pos <= kBlockThreads * kMergeBigE)
+      return merge_staged_hybrid<kMergeBigE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
   }
   if (n_pos <= kBlockThreads * kMergeRegE)

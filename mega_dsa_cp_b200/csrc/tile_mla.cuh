@@ -148,7 +148,7 @@ __device__ inline void mla_load_tile(const mdc_sparse_mla_params& p, int r, int 
 // half the accumulator registers, for blocks whose register budget is 128).
 template <int DQK, int KVDT, int NDV = kMlaDv>
 __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int split, int n_splits,
-                         unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr, int dv0 = 0) {
+                         unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr, int dv0 = 0, bool to_row = false) {
   constexpr int NT = NDV / 16;            // 8-column accumulator tiles per warp
   const int col0 = dv0 + (NDV / 2) * (static_cast<int>(threadIdx.x) >> 7);  // first output column of this warp
   using SM = MlaSmem<DQK>;
@@ -348,7 +348,7 @@ __device__ void mla_tile(const mdc_sparse_mla_params& p, int r, int hb, int spli
     sSum[half * 64 + 16 * mt + g + 8] = run_sum[1];
   }
   sync_workers();
-  const bool direct = n_splits == 1;
+  const bool direct = n_splits == 1 || to_row;  // a split partial may also go to o_row / lse_row
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = 16 * mt + g + 8 * i;

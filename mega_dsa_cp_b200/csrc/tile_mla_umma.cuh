@@ -98,10 +98,11 @@ __device__ inline uint32_t mla_umma_gather_rows(const mdc_sparse_mla_params& p, 
 // r = b*q_len + t, hb = block of 128 heads, dq = block of 128 output columns,
 // split / n_splits = slice of the slot range.  o_row / lse_row, when given,
 // replace p.o / p.lse for this row (they point at the row's (H, d_v) block and
-// (H,) vector, possibly in a peer GPU's memory).  All kMuThreads threads call it.
+// (H,) vector, possibly in a peer GPU's memory); with to_row a split's partial goes there too
+// instead of the split workspace.  All kMuThreads threads call it.
 template <int DQK>
 __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int dq, int split, int n_splits,
-                              unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr) {
+                              unsigned char* smem, void* o_row = nullptr, float* lse_row = nullptr, bool to_row = false) {
   using SM = MlaUmmaSmem<DQK>;
   constexpr int S = SM::kStages;
   constexpr uint32_t kQCols = DQK / 2, kOCol = kQCols, kSCol = kOCol + kMuDv, kPCol = kSCol + kMuTile;
@@ -266,7 +267,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       const bool live = l > 0.f;
       const float inv = live ? p.output_scale / l : 0.f;
       const float lse = live ? log2f(l) + c2 * m_used : neg_inf;
-      const bool direct = n_splits == 1;
+      const bool direct = n_splits == 1 || to_row;  // a split partial may also go to o_row / lse_row
       if (dq == 0) {
         if (direct) {
           if (lse_row) lse_row[h] = lse;
@@ -386,6 +387,15 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           umma::commit(o_final);
         }
         __syncwarp();
+        // The "free" arrivals of the last tiles have no consumer.  They are asynchronous: wait for
+        // them here, or one could land after the barriers are invalidated below, on shared memory
+        // that the block's next task already uses for something else.
+        for (int i = max(0, n_my - S); i < n_my; ++i) {
+          if (!mbar_wait(&free_[i % S], (i / S) & 1, kBudget, abort_flag)) {
+            if (lane == 0) give_up(6, i);
+            break;
+          }
+        }
       }
     }
   }

@@ -9,7 +9,8 @@ Per rank r of cp ranks (token t lives on rank t % cp at local index t // cp):
                    this rank's gather list (ids with id % cp == r)
     ATTN(b, j)     sparse MLA over the local share, 64 heads x 256 columns per
                    task; bf16 partial + log2-LSE stored into the owner's inbox
-    LSE_MERGE(b)   on owner b % cp: cp partials -> output row
+    LSE_MERGE(b)   on owner b % cp: cp (x attention splits) partials -> output row,
+                   4 tasks of 32 heads
 
 wired by events l1[b], cand[b], topk[b], part[b] (docs/phase1.4-comm-tasks.md
 section 3 of the reference; its design never got assembled there).  The task
@@ -32,9 +33,10 @@ from .schedule.codegen import codegen_schedule
 from .schedule.device import launch_megakernel, upload_schedule
 
 D_V = 512
+LSE_GROUPS = 4
 
 
-def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128):
+def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1):
     """Tasks / events of one layer-step for ALL ranks, plus op codes by task name."""
     cross = SCOPE_SYS if cp > 1 else SCOPE_LOCAL
     events, tasks, ops = [], [], {}
@@ -59,20 +61,22 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128):
             ops[name] = N.OP_MERGE_L2
         for b in range(B):
             for j in range(n_attn):
-                name = f"attn[{r},{b},{j}]"
-                tasks.append(TaskSpec(name, r, (WaitEdge(f"topk[{b}]"),), (NotifyEdge(f"part[{b}]", b % cp),), (b, j, 0)))
-                ops[name] = N.OP_ATTN
+                for s in range(attn_splits):
+                    name = f"attn[{r},{b},{j},{s}]"
+                    tasks.append(TaskSpec(name, r, (WaitEdge(f"topk[{b}]"),), (NotifyEdge(f"part[{b}]", b % cp),), (b, j, s)))
+                    ops[name] = N.OP_ATTN
         for b in range(B):
             if b % cp == r:
-                name = f"lse_merge[{r},{b}]"
-                tasks.append(TaskSpec(name, r, (WaitEdge(f"part[{b}]"),), (), (b, 0, 0)))
-                ops[name] = N.OP_LSE_MERGE
+                for hq in range(LSE_GROUPS):  # head groups: the merge of one sequence runs on several blocks
+                    name = f"lse_merge[{r},{b},{hq}]"
+                    tasks.append(TaskSpec(name, r, (WaitEdge(f"part[{b}]"),), (), (b, hq, LSE_GROUPS)))
+                    ops[name] = N.OP_LSE_MERGE
     return tasks, events, ops
 
 
-def arena_regions(B: int, cp: int, top_k: int, heads: int = 128):
+def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1):
     cand = B * cp * (top_k * 8 + 16)
-    inbox = -(-B // cp) * cp * (heads * D_V * 2 + heads * 4)
+    inbox = -(-B // cp) * cp * attn_splits * (heads * D_V * 2 + heads * 4)
     return {"cand": cand, "inbox": inbox}
 
 
@@ -93,7 +97,8 @@ class DsaDecodeLayer:
     def __init__(self, B: int, cp: int = 1, rank: int = 0, top_k: int = 2048, heads: int = 128, d_qk: int = 576,
                  fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
-                 device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None):
+                 device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
+                 attn_splits: int | None = None):
         self.B, self.cp, self.rank, self.K, self.H, self.d_qk = B, cp, rank, top_k, heads, d_qk
         self.fmt, self.P, self.max_pages, self.bpc = fmt, page_tokens, max_pages, blocks_per_chunk
         self.n_chunks = -(-max_pages // blocks_per_chunk)
@@ -104,11 +109,17 @@ class DsaDecodeLayer:
         if n_ctas is None:
             n_ctas = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.n_ctas = n_ctas
-        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads)
+        if attn_splits is None:
+            # split the local slot range until the attention tasks about fill the blocks; a split
+            # should keep a few 64-slot tiles, and the LSE merge takes at most 16 slices
+            tiles = -(-(top_k // cp + 128) // 64)
+            attn_splits = max(1, min(tiles // 4, n_ctas // max(1, B * 4 * (heads // 128 or 1)), 16 // cp))
+        self.attn_splits = attn_splits
+        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits)
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
         self.dsched = upload_schedule(self.schedule, self.device)
         self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
-        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads), phases, rank, cp, group_name, self.device)
+        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits), phases, rank, cp, group_name, self.device)
         dev = self.device
         C, K = self.n_chunks, top_k
         self.cand_v = torch.empty(B, 1, C, K, device=dev)
@@ -148,6 +159,7 @@ class DsaDecodeLayer:
         L = N.LayerParams()
         L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = self.cp, self.rank, B, K, self.H, self.n_chunks
         L.kv_seq_stride = self.kv_seq_stride
+        L.attn_splits = self.attn_splits
         L.logits, L.mla = lp, mp
         L.cand_off, L.inbox_off = self.arena.regions["cand"], self.arena.regions["inbox"]
         L.phase_bytes, L.phases = self.arena.nbytes_per_phase, self.phases
