@@ -260,6 +260,7 @@ typedef struct {
 #define MDC_OP_MERGE_L1 2   /* c0 = b: chunk lists -> local top-k -> every rank    */
 #define MDC_OP_MERGE_L2 3   /* c0 = b: cp lists -> global top-k + local gather list */
 #define MDC_OP_ATTN 4       /* c0 = b, c1 = head/column block (see megakernel.cu), c2 = slot split: partial -> owner inbox */
+#define MDC_OP_MERGE_L1A 6  /* c0 = b, c1 = group: chunk lists of the group -> mid list              */
 #define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
@@ -290,6 +291,12 @@ typedef struct {
   void* out;                    /* (B, H, 512) merged attention output (owned rows only) */
   float* out_lse;               /* (B, H)                                        */
   int32_t out_dtype;            /* MDC_DT_F32 | MDC_DT_BF16                      */
+  /* two-level local merge: with l1_groups > 1 MERGE_L1A tasks first merge the chunk lists of one
+   * group (ceil(n_chunks / l1_groups) lists each) into mid_*, and MERGE_L1 merges the groups */
+  int32_t l1_groups;
+  float* mid_v;                 /* (B, l1_groups, top_k)                         */
+  int32_t* mid_i;               /* (B, l1_groups, top_k)                         */
+  int32_t* mid_c;               /* (B, l1_groups)                                */
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

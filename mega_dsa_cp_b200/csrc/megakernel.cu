@@ -79,18 +79,38 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
   logits_tile<FMT, PAGE, 1, 2, 1>(p.layer.logits, b, chunk, smem);
 }
 
-// chunk candidate lists of sequence b -> this rank's top-k, written into the
+// first level of a two-level local merge: the chunk lists of group g of sequence b -> one list
+__device__ inline void op_merge_l1a(const mdc_mega_params& p, int b, int g, unsigned char* smem) {
+  const mdc_layer_params& L = p.layer;
+  MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
+  const int K = L.top_k, C = L.n_chunks, G = max(1, L.l1_groups);
+  const int per = ceil_div(C, G);
+  const int c0 = min(max(g, 0), G - 1) * per, n = max(0, min(per, C - c0));
+  MergeLists ls;
+  ls.v = L.logits.cand_v + (static_cast<int64_t>(b) * C + c0) * K;
+  ls.i = L.logits.cand_i + (static_cast<int64_t>(b) * C + c0) * K;
+  ls.c = L.logits.cand_c + static_cast<int64_t>(b) * C + c0;
+  ls.stride = K;
+  ls.c_stride = 1;
+  const int64_t o = static_cast<int64_t>(b) * G + g;
+  merge_lists_auto<false>(ls, n, K, K, L.mid_v + o * K, L.mid_i + o * K, L.mid_c + o, nullptr, sm, smem + 8192,
+                          kMegaTileSmem - 8192);
+}
+
+// chunk (or group) candidate lists of sequence b -> this rank's top-k, written into the
 // own slice of the candidate region and copied to every peer's arena
 __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
                          p.arena.mc_base};
-  const int K = L.top_k, C = L.n_chunks;
+  const int K = L.top_k;
+  const bool two_level = L.l1_groups > 1 && L.mid_v != nullptr;
+  const int C = two_level ? L.l1_groups : L.n_chunks;  // lists to merge: the groups' lists, or the chunks'
   MergeLists ls;
-  ls.v = L.logits.cand_v + static_cast<int64_t>(b) * C * K;
-  ls.i = L.logits.cand_i + static_cast<int64_t>(b) * C * K;
-  ls.c = L.logits.cand_c + static_cast<int64_t>(b) * C;
+  ls.v = (two_level ? L.mid_v : L.logits.cand_v) + static_cast<int64_t>(b) * C * K;
+  ls.i = (two_level ? L.mid_i : L.logits.cand_i) + static_cast<int64_t>(b) * C * K;
+  ls.c = (two_level ? L.mid_c : L.logits.cand_c) + static_cast<int64_t>(b) * C;
   ls.stride = K;
   ls.c_stride = 1;
   const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
@@ -274,6 +294,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         break;
       case MDC_OP_MERGE_L1:
         if (worker) op_merge_l1(p, t.c0, cur.phase, smem);
+        break;
+      case MDC_OP_MERGE_L1A:
+        if (worker && L.mid_v && L.mid_i && L.mid_c) op_merge_l1a(p, t.c0, t.c1, smem);
         break;
       case MDC_OP_MERGE_L2:
         if (worker) {

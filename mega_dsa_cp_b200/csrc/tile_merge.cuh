@@ -209,7 +209,7 @@ __device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, 
           kv.z = cnt[u] > 2 ? max(sortable_u32(v[u].z), 1u) : 0u;
           kv.w = cnt[u] > 3 ? max(sortable_u32(v[u].w), 1u) : 0u;
           reinterpret_cast<uint4*>(vb)[qi] = kv;
-          reinterpret_cast<int4*>(ib)[qi] = f[u];
+          if (ib) reinterpret_cast<int4*>(ib)[qi] = f[u];
         }
       }
     }
@@ -242,7 +242,7 @@ __device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, 
       if (pos < n_pos) {
         // key 0 marks an empty position; a real logit never maps to 0 after the clamp
         vb[pos] = ok[u] ? max(sortable_u32(v[u]), 1u) : 0u;
-        ib[pos] = ok[u] ? __float_as_int(f[u]) : 0;
+        if (ib) ib[pos] = ok[u] ? __float_as_int(f[u]) : 0;
       }
     }
   }
@@ -399,8 +399,9 @@ __device__ inline int merge_staged_hybrid(int n_pos, int top_k, float* out_v, in
 // Staged rows of any size: bitwise search over the shared-memory keys.  Ties on
 // the logit are resolved in the same search by a second key: entries above the
 // logit threshold rank highest, tied entries rank by ~id, everything else is out.
+template <typename IdFn>
 __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
-                                        MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
+                                        MergeSmem& sm, const uint32_t* vb, IdFn id_of) {
   const int tid = threadIdx.x;
   int n_eq = 0;
   Threshold<uint32_t> th = block_select_bits([&](int pos) { return vb[pos]; }, n_pos, top_k, sm.sel, &n_eq);
@@ -409,7 +410,7 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
   auto put = [&](int pos, int slot) {
     if (slot < top_k) {
       out_v[slot] = unsortable_f32(vb[pos]);
-      out_i[slot] = ib[pos];
+      out_i[slot] = id_of(pos);
     }
   };
   if (th.need_eq == 0x7fffffff || n_eq == th.need_eq) {
@@ -420,7 +421,7 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
     const uint32_t tau = th.tau;
     auto key2 = [&](int pos) -> uint32_t {
       const uint32_t kv = vb[pos];
-      return kv > tau ? 0xffffffffu : (kv == tau ? max(~static_cast<uint32_t>(ib[pos]), 1u) : 0u);
+      return kv > tau ? 0xffffffffu : (kv == tau ? max(~static_cast<uint32_t>(id_of(pos)), 1u) : 0u);
     };
     Threshold<uint32_t> t2 = block_select_bits(key2, n_pos, top_k, sm.sel);
     n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { const uint32_t k2 = key2(pos); valid = k2 != 0u; return k2; },
@@ -449,7 +450,16 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
       return merge_staged_regs<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     if (n_pos <= kBlockThreads * kMergeBigE)
       return merge_staged_hybrid<kMergeBigE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
+    return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; });
+  }
+  if (stage && n_pos * 4 <= stage_bytes && maxK >= 1) {
+    // too long for keys + ids: stage the keys only, fetch the few ids that are needed from global memory
+    uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
+    merge_stage_lists<SYS>(ls, L, maxK, sm, vb, nullptr);
+    return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) {
+      const int l = pos / maxK, j = pos - l * maxK;
+      return __float_as_int(ld_f32(reinterpret_cast<const float*>(ls.i + l * ls.stride + j), SYS));
+    });
   }
   if (n_pos <= kBlockThreads * kMergeRegE)
     return merge_lists_regs<kMergeRegE, SYS>(ls, L, maxK, top_k, out_v, out_i, out_c, dbg, sm);

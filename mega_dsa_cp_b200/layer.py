@@ -4,7 +4,8 @@ single persistent-kernel launch per rank.
 Per rank r of cp ranks (token t lives on rank t % cp at local index t // cp):
 
     LOGITS(b, c)   indexer logits + exact local top-k of chunk c     (x B x C)
-    MERGE_L1(b)    C chunk lists -> rank-local top-k, stored into every rank's arena
+    MERGE_L1A(b,g) (more than 4 chunks only) the chunk lists of group g -> one list
+    MERGE_L1(b)    chunk (or group) lists -> rank-local top-k, stored into every rank's arena
     MERGE_L2(b)    cp lists -> global top-k (bit-identical on all ranks) and
                    this rank's gather list (ids with id % cp == r)
     ATTN(b, j)     sparse MLA over the local share, 64 heads x 256 columns per
@@ -36,20 +37,35 @@ D_V = 512
 LSE_GROUPS = 4
 
 
-def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1):
+def l1_groups_for(n_chunks: int) -> int:
+    """Groups of the two-level local merge: at most 4 chunk lists per first-level task."""
+    return 1 if n_chunks <= 4 else -(-n_chunks // 4)
+
+
+def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1):
     """Tasks / events of one layer-step for ALL ranks, plus op codes by task name."""
     cross = SCOPE_SYS if cp > 1 else SCOPE_LOCAL
     events, tasks, ops = [], [], {}
     for b in range(B):
+        if l1_groups > 1:
+            events += [EventSpec(f"l1a[{b},{g}]", SCOPE_LOCAL) for g in range(l1_groups)]
         events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL), EventSpec(f"cand[{b}]", cross),
                    EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
     n_attn = 2 * (heads // 64)
+    per = -(-n_chunks // l1_groups)
     for r in range(cp):
         for b in range(B):
             for c in range(n_chunks):
                 name = f"logits[{r},{b},{c}]"
-                tasks.append(TaskSpec(name, r, (), (NotifyEdge(f"l1[{b}]", r),), (b, c, 0)))
+                ev = f"l1a[{b},{c // per}]" if l1_groups > 1 else f"l1[{b}]"
+                tasks.append(TaskSpec(name, r, (), (NotifyEdge(ev, r),), (b, c, 0)))
                 ops[name] = N.OP_LOGITS
+        if l1_groups > 1:
+            for b in range(B):
+                for g in range(l1_groups):
+                    name = f"merge_l1a[{r},{b},{g}]"
+                    tasks.append(TaskSpec(name, r, (WaitEdge(f"l1a[{b},{g}]"),), (NotifyEdge(f"l1[{b}]", r),), (b, g, 0)))
+                    ops[name] = N.OP_MERGE_L1A
         for b in range(B):
             name = f"merge_l1[{r},{b}]"
             tasks.append(TaskSpec(name, r, (WaitEdge(f"l1[{b}]"),),
@@ -115,7 +131,8 @@ class DsaDecodeLayer:
             tiles = -(-(top_k // cp + 128) // 64)
             attn_splits = max(1, min(tiles // 4, n_ctas // max(1, B * 4 * (heads // 128 or 1)), 16 // cp))
         self.attn_splits = attn_splits
-        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits)
+        self.l1_groups = l1_groups_for(self.n_chunks)
+        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups)
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
         self.dsched = upload_schedule(self.schedule, self.device)
         self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
@@ -125,6 +142,10 @@ class DsaDecodeLayer:
         self.cand_v = torch.empty(B, 1, C, K, device=dev)
         self.cand_i = torch.empty(B, 1, C, K, dtype=torch.int32, device=dev)
         self.cand_c = torch.zeros(B, 1, C, dtype=torch.int32, device=dev)
+        G = self.l1_groups
+        self.mid_v = torch.empty(B, G, K, device=dev)
+        self.mid_i = torch.empty(B, G, K, dtype=torch.int32, device=dev)
+        self.mid_c = torch.zeros(B, G, dtype=torch.int32, device=dev)
         self.sel_v = torch.zeros(B, K, device=dev)
         self.sel_i = torch.zeros(B, K, dtype=torch.int32, device=dev)
         self.sel_c = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -160,6 +181,8 @@ class DsaDecodeLayer:
         L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = self.cp, self.rank, B, K, self.H, self.n_chunks
         L.kv_seq_stride = self.kv_seq_stride
         L.attn_splits = self.attn_splits
+        L.l1_groups = self.l1_groups
+        L.mid_v, L.mid_i, L.mid_c = N.ptr(self.mid_v), N.ptr(self.mid_i), N.ptr(self.mid_c)
         L.logits, L.mla = lp, mp
         L.cand_off, L.inbox_off = self.arena.regions["cand"], self.arena.regions["inbox"]
         L.phase_bytes, L.phases = self.arena.nbytes_per_phase, self.phases

@@ -139,3 +139,34 @@ def test_layer_dag_two_ranks_gloo(tmp_path):
            "--master-port", "29611", str(script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert "HOST_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+@pytest.mark.parametrize("n_chunks,cp,splits", [(2, 1, 1), (4, 2, 2), (8, 2, 4), (16, 4, 1), (5, 8, 2)])
+def test_layer_dag_variants_validate(n_chunks, cp, splits):
+    """Two-level local merge (more than 4 chunks), attention slot splits and the four LSE head
+    groups: every variant is a valid DAG on every rank, with the arities the kernels rely on."""
+    from mega_dsa_cp_b200.events import validate
+    from mega_dsa_cp_b200.layer import LSE_GROUPS, arena_regions, build_layer_dag, l1_groups_for
+    from mega_dsa_cp_b200.schedule.codegen import codegen_schedule
+
+    B, heads = 5, 128
+    G = l1_groups_for(n_chunks)
+    assert (G == 1) == (n_chunks <= 4) and G * 4 >= n_chunks
+    tasks, events, ops = build_layer_dag(B, n_chunks, cp, heads, splits, G)
+    errors, table = validate(tasks, events, cp)
+    assert not errors, errors[:3]
+    for r in range(cp):
+        s = codegen_schedule(tasks, events, rank=r, n_ctas=7, world_size=cp, op_of=ops)
+        mine = [t for t in tasks if t.rank == r]
+        assert len(s.topo) == len(mine)
+        names = {e.name: i for i, e in enumerate(events)}
+        for b in range(B):
+            # part[b] is notified by every rank's attention tasks, only into its owner
+            want = cp * 4 * splits if b % cp == r else 0
+            assert s.arity[names[f"part[{b}]"]] == want
+            assert s.arity[names[f"l1[{b}]"]] == (G if G > 1 else n_chunks)
+            assert s.arity[names[f"cand[{b}]"]] == cp
+        n_lse = sum(1 for t in mine if t.name.startswith("lse_merge"))
+        assert n_lse == LSE_GROUPS * sum(1 for b in range(B) if b % cp == r)
+    reg = arena_regions(B, cp, 2048, heads, splits)
+    assert reg["inbox"] == -(-B // cp) * cp * splits * (heads * 512 * 2 + heads * 4)
