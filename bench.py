@@ -518,24 +518,47 @@ def run_reference(args):
         return
     from dsa_inputs import indexer_case
 
-    c = CFG2
-    seqs = 2
-    case = indexer_case(seqs, c["S"], c["page"], "nvfp4", seed=0)
-    for _ in range(min(args.warmup, 2)):
-        cpu_cfg2_once(case, c["top_k"])
-    steps = min(args.steps, 20)
+    world = max(args.gpus, int(os.environ.get("WORLD_SIZE", "1")))
+    warm = max(3, min(args.warmup, 3))
+    if world > 1:
+        # the arm's workload at N > 1: the full decode layer-step at CP = N; sample = one sequence per step
+        from oracle import dsa_oracle as orc
+        cc = cp_config(world)
+        S, K, H, DQK = cc["S"], cc["top_k"], cc["H"], cc["d_qk"]
+        g = torch.Generator().manual_seed(0)
+        kd = torch.randn(S, 128, generator=g)
+        data, sf = orc.quant_nvfp4(kd)
+        kd = orc.dequant_fp4(data, sf, "nvfp4")
+        q_idx = torch.randn(64, 128, generator=g).bfloat16().float()
+        w_idx = torch.randn(64, generator=g) / 64.0
+        q_mla = (torch.randn(H, DQK, generator=g) * 0.5).bfloat16()
+        kv = (torch.randn(S, DQK, generator=g) * 0.5).bfloat16()
+        once = lambda: orc.decode_step_ref(q_idx, w_idx, kd, q_mla.float(), kv.float(), S, K, 1.0 / math.sqrt(DQK), cp=world)
+        seqs, steps = 1, min(args.steps, 5)
+        workload = (f"sample on host cores of the full DSA decode layer-step at CP={world}: 1 of the {cc['B']} sequences, "
+                    f"ctx {S}, indexer + top-k {K} + sparse MLA + LSE merge")
+        sample = f"1 of the {cc['B']} sequences per step, {steps} steps"
+    else:
+        c = CFG2
+        seqs = 2
+        case = indexer_case(seqs, c["S"], c["page"], "nvfp4", seed=0)
+        once = lambda: cpu_cfg2_once(case, c["top_k"])
+        steps = min(args.steps, 20)
+        workload = "cfg2 sample on host cores: indexer logits + top-k 2048, ctx 32768"
+        sample = f"{seqs} of the 32 sequences of cfg2 per step, {steps} steps"
+    for _ in range(warm):
+        once()
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu_cfg2_once(case, c["top_k"])
+        once()
     ms = (time.perf_counter() - t0) * 1e3 / steps
     val = seqs / (ms * 1e-3)
-    cpu = {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-           "sample": f"{seqs} of the 32 sequences of cfg2 per step, {steps} steps"}
+    cpu = {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg2 sample on host cores: indexer logits + top-k 2048, ctx 32768"},
+        "config": {"workload": workload},
         "cpu_baseline": cpu,
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
