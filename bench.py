@@ -361,8 +361,36 @@ def cp1_layer_step(steps, warmup, dev):
         l.check_status()
     ms = e0.elapsed_time(e1) / steps
     return {"step_us": ms * 1e3, "tokens_per_s": B / (ms * 1e-3), "gpu_launches_per_step": 1,
+            "timeline": task_timeline(layers[0], dev),
             "config": f"full DSA decode layer-step, CP=1: B={B}, ctx {S}, indexer + top-k {K} + sparse MLA "
                       f"(128 heads, 512+64) + LSE merge, one persistent kernel"}
+
+
+OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE", 6: "MERGE_L1A"}
+
+
+def task_timeline(layer, dev):
+    """One traced layer-step: per op the task count, mean wait / body time and the time its last task
+    ended (us from the first task's start), from the megakernel's optional trace buffer."""
+    import torch
+
+    trace = torch.zeros(4 + 4 * 8192, dtype=torch.int64, device=dev)
+    layer.step(trace=trace)
+    torch.cuda.synchronize()
+    t = trace.cpu()
+    n = min(int(t[0]), 8192)
+    e = t[4:4 + 4 * n].reshape(n, 4)
+    if n == 0:
+        return {}
+    t0 = int(e[:, 1].min())
+    out = {}
+    for op in sorted(set(((e[:, 0] >> 24) & 0xff).tolist())):
+        m = ((e[:, 0] >> 24) & 0xff) == op
+        a, b, c = e[m, 1].double(), e[m, 2].double(), e[m, 3].double()
+        out[OP_NAMES.get(op, str(op))] = {"tasks": int(m.sum()), "wait_us": round(float((b - a).mean()) / 1e3, 1),
+                                          "body_us": round(float((c - b).mean()) / 1e3, 1),
+                                          "last_end_us": round(float(c.max() - t0) / 1e3, 1)}
+    return out
 
 
 def run_gpu_cp(args):
@@ -423,6 +451,9 @@ def run_gpu_cp(args):
         time.sleep(0.1)
     for l in layers:
         l.check_status()
+    dist.barrier()
+    timeline = task_timeline(layers[0], dev)   # every rank steps (the ranks wait on each other); rank 0 reports
+    layers[0].check_status()
     # end to end: query tensors from pinned host memory each step, merged output rows read back
     hq, hw, hm = q_idx.cpu().pin_memory(), w_idx.cpu().pin_memory(), q_mla.cpu().pin_memory()
     owned = layers[0].owned_rows()
@@ -465,7 +496,7 @@ def run_gpu_cp(args):
             "step_us": ms_step * 1e3,
             "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps, "timeline_rank0": timeline,
             "roofline": {"bound": "hbm", "achieved": algo / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": algo / (ms_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
                          "kernel": "mega_kernel (whole step; indexer bytes only)", "algorithmic_bytes": algo, "traffic": None},

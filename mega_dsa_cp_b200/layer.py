@@ -11,7 +11,7 @@ Per rank r of cp ranks (token t lives on rank t % cp at local index t // cp):
     ATTN(b, j)     sparse MLA over the local share, 64 heads x 256 columns per
                    task; bf16 partial + log2-LSE stored into the owner's inbox
     LSE_MERGE(b)   on owner b % cp: cp (x attention splits) partials -> output row,
-                   4 tasks of 32 heads
+                   8 tasks of 16 heads
 
 wired by events l1[b], cand[b], topk[b], part[b] (docs/phase1.4-comm-tasks.md
 section 3 of the reference; its design never got assembled there).  The task
@@ -34,7 +34,7 @@ from .schedule.codegen import codegen_schedule
 from .schedule.device import launch_megakernel, upload_schedule
 
 D_V = 512
-LSE_GROUPS = 4
+LSE_GROUPS = 8
 
 
 def l1_groups_for(n_chunks: int) -> int:

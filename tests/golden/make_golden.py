@@ -23,7 +23,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("MDC_REF_PATH", "/root/reference")
+REF = os.environ.get("MDC_REF_PATH")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set MDC_REF_PATH to a checkout of the reference (mega-dsa-cp)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "tests"))
