@@ -37,6 +37,13 @@ struct EventSet {
     if (dst == my_rank) red_release_gpu_add_u64(cell(ev), 1ull);
     else red_release_sys_add_u64(peer_cell(ev, dst), 1ull);
   }
+  // notify after the whole block has fenced (system scope) and met at a barrier: the ordering is
+  // already established, so the reduction itself carries none.  A release per notify would make a
+  // task with one notify per rank pay a system-scope fence per rank.
+  __device__ void notify_1t_fenced(int ev, int dst) const {
+    if (dst == my_rank) red_relaxed_gpu_add_u64(cell(ev), 1ull);
+    else red_relaxed_sys_add_u64(peer_cell(ev, dst), 1ull);
+  }
   // single-thread bounded poll; returns the last value seen through *seen
   __device__ bool poll_1t(int ev, unsigned long long target, bool sys, long long budget_ns,
                           unsigned long long* seen) const {

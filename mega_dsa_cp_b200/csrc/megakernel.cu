@@ -120,8 +120,13 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
   if (L.cp > 1) {
     __threadfence();
     sync_workers();
-    for (int dst = 0; dst < L.cp; ++dst) {
-      if (dst != L.rank) copy_to_peer(arena.peer_ptr(off, dst), slice, cand_slice_bytes(L));
+    // every 16-byte piece is read once and stored to all peers (posted stores, no load in between)
+    const int n16 = cand_slice_bytes(L) / 16;
+    for (int i = threadIdx.x; i < n16; i += kBlockThreads) {
+      const uint4 v = reinterpret_cast<const uint4*>(slice)[i];
+      for (int dst = 0; dst < L.cp; ++dst) {
+        if (dst != L.rank) reinterpret_cast<uint4*>(arena.peer_ptr(off, dst))[i] = v;
+      }
     }
   }
 }
@@ -346,7 +351,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         for (int i = 0; i < t.n_notifies; ++i) {
           const int w = cur.notify_word(t, i);
           const int e = w >> 8, dst = w & 0xFF;
-          if (e >= 0 && e < p.n_events && dst < ev.world) ev.notify_1t(e, dst);
+          if (e >= 0 && e < p.n_events && dst < ev.world) ev.notify_1t_fenced(e, dst);
           else report_failure(p.status, MDC_DEV_BAD_OP, e, dst, 0, 0);
         }
       }

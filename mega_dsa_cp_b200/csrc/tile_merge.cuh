@@ -191,7 +191,7 @@ __device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, 
     sm.cnt[l] = max(0, min(c, maxK));
   }
   sync_workers();
-  const bool vec = !SYS && (maxK & 3) == 0 && (ls.stride & 3) == 0 &&
+  const bool vec = (maxK & 3) == 0 && (ls.stride & 3) == 0 &&
                    ((reinterpret_cast<uintptr_t>(ls.v) | reinterpret_cast<uintptr_t>(ls.i)) & 15) == 0;
   if (vec) {
     // four consecutive positions of one list per 16-byte load, eight loads of each kind in flight per thread
@@ -207,8 +207,15 @@ __device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, 
         const int l = qi / k4, j = (qi - l * k4) << 2;
         cnt[u] = sm.cnt[l] - j;  // valid positions of this quad: those below cnt
         const int64_t off = l * ls.stride + j;
-        v[u] = __ldg(reinterpret_cast<const float4*>(ls.v + off));
-        f[u] = __ldg(reinterpret_cast<const int4*>(ls.i + off));
+        if (SYS) {  // lists written by peer GPUs: system-scope loads that bypass the L1
+          const uint4 a = ld_sys_u4(reinterpret_cast<const uint4*>(ls.v + off));
+          const uint4 b = ld_sys_u4(reinterpret_cast<const uint4*>(ls.i + off));
+          v[u] = make_float4(__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w));
+          f[u] = make_int4(static_cast<int>(b.x), static_cast<int>(b.y), static_cast<int>(b.z), static_cast<int>(b.w));
+        } else {
+          v[u] = __ldg(reinterpret_cast<const float4*>(ls.v + off));
+          f[u] = __ldg(reinterpret_cast<const int4*>(ls.i + off));
+        }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {

@@ -41,8 +41,8 @@ struct MlaUmmaSmem {
   // as many stages as fit beside ~3 KB of bookkeeping in 226 KB
   static constexpr int kStages = (226 * 1024 - 3072) / kStageBytes >= 3 ? 3 : 2;
   static constexpr int kK = 0;
-  static constexpr int kBars = kStages * kStageBytes;   // full[S], free[S], s_ready, p_ready, q_ready, o_final
-  static constexpr int kMisc = kBars + (2 * kStages + 4) * 8;  // [0] tmem base, [1] abort flag
+  static constexpr int kBars = kStages * kStageBytes;   // full[S], free[S], s_ready, p_ready, q_ready, o_final, qs_ready
+  static constexpr int kMisc = kBars + (2 * kStages + 6) * 8;  // [0] tmem base, [1] abort flag
   static constexpr int kValid = kMisc + 64;                     // [S][8] bytes: validity bits of 8 slots per gather warp
   static constexpr int kTotal = kValid + kStages * 8 + 56;
 };
@@ -107,6 +107,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
   constexpr int S = SM::kStages;
   constexpr uint32_t kQCols = DQK / 2, kOCol = kQCols, kSCol = kOCol + kMuDv, kPCol = kSCol + kMuTile;
   static_assert(kPCol + kMuTile / 2 <= 512, "tensor memory over-subscribed");
+  static_assert(SM::kPanels * kMuHeads * 128 <= S * SM::kStageBytes, "the staged query must fit the KV ring");
   constexpr long long kBudget = 1ll << 31;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* kst = smem + SM::kK;
@@ -116,6 +117,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
   uint64_t* p_ready = s_ready + 1;
   uint64_t* q_ready = p_ready + 1;
   uint64_t* o_final = q_ready + 1;
+  uint64_t* qs_ready = o_final + 1;  // the query rows are staged in shared memory
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + SM::kMisc);
   volatile uint32_t* abort_flag = misc + 1;
   unsigned char* validb = smem + SM::kValid;
@@ -140,6 +142,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     mbar_init(p_ready, 4);
     mbar_init(q_ready, 4);
     mbar_init(o_final, 1);
+    mbar_init(qs_ready, kMuGatherWarps);
     misc[1] = 0;
     mbar_fence_init();
   }
@@ -157,15 +160,19 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     // ---------------- softmax warps: thread = head
     const int h = hb * kMuHeads + warp * 32 + lane;
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    {  // Q row -> tensor memory (bf16 pairs, 16 columns per store)
-      const uint4* qsrc = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.q) +
-                                                         (static_cast<int64_t>(r) * p.H + h) * DQK * 2);
+    {  // Q row -> tensor memory (bf16 pairs, 16 columns per store), from the copy the gather warps staged
+      // in the (still empty) KV ring as DQK/64 panels of 128 rows x 128 bytes, 128-byte swizzle
+      bool okq = mbar_wait(qs_ready, 0, kBudget, abort_flag);
+      if (!okq && lane == 0) give_up(7, 0);
+      const int row = warp * 32 + lane;
 #pragma unroll 2
       for (int j = 0; j < static_cast<int>(kQCols) / 16; ++j) {
         uint32_t v[16];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const uint4 x = __ldg(qsrc + 4 * j + u);
+          const int ch = 4 * j + u;
+          const uint4 x = *reinterpret_cast<const uint4*>(kst + (ch >> 3) * (kMuHeads * 128) + row * 128 +
+                                                          (((ch & 7) ^ (row & 7)) << 4));
           v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
         }
         umma::tmem_st16(t_lane + 16 * j, v);
@@ -316,6 +323,28 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     // ---------------- gather warps: 8 rows of every tile each, up to two tiles in flight per warp
     const int gw = warp - kMuGatherWarp0;
     bool ok = true;
+    {  // stage the 128 query rows (coalesced: a warp instruction copies 512 contiguous bytes of a row)
+      constexpr int kChunks = DQK / 8;
+      const unsigned char* q0 = static_cast<const unsigned char*>(p.q) +
+                                (static_cast<int64_t>(r) * p.H + hb * kMuHeads) * DQK * 2;
+      for (int rr = 0; rr < kMuHeads / kMuGatherWarps; ++rr) {
+        const int row = gw * (kMuHeads / kMuGatherWarps) + rr;
+#pragma unroll
+        for (int ch = lane; ch < kChunks; ch += 32) {
+          cp_async16_zfill(kst + (ch >> 3) * (kMuHeads * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4),
+                           q0 + static_cast<int64_t>(row) * DQK * 2 + ch * 16, true);
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      mbar_arrive_if(qs_ready, lane == 0);
+      // the ring is free for KV tiles once the softmax warps have moved the rows into tensor memory
+      if (!mbar_wait(q_ready, 0, kBudget, abort_flag)) {
+        if (lane == 0) give_up(8, 0);
+        ok = false;
+      }
+    }
     for (int i = 0; i < n_my && ok; ++i) {
       const int st = i % S;
       if (i >= S && !mbar_wait(&free_[st], ((i / S) - 1) & 1, kBudget, abort_flag)) {
@@ -405,7 +434,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
   umma::fence_after_sync();
   if (warp == kMuIssueWarp) umma::tmem_dealloc(tmem, 512);
   if (tid == 0) {
-    for (int i = 0; i < 2 * S + 4; ++i) mbar_inval(full + i);
+    for (int i = 0; i < 2 * S + 5; ++i) mbar_inval(full + i);
   }
 }
 
