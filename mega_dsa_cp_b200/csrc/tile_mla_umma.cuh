@@ -284,6 +284,11 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         }
       }
       const int col0 = dq * kMuDv;
+      // A bf16 row that goes to o_row (the owner's inbox, possibly on a peer GPU) is staged in shared
+      // memory (the KV ring is idle now) and leaves as ONE 256-byte bulk copy per head: sixteen
+      // 16-byte stores per thread over NVLink take an order of magnitude longer.
+      const bool bulk_out = direct && o_row != nullptr && p.out_dtype != MDC_DT_F32;
+      unsigned char* stage_row = kst + (warp * 32 + lane) * (kMuDv * 2);
 #pragma unroll 1
       for (int cb = 0; cb < kMuDv / 32; ++cb) {
         float o[32];
@@ -297,7 +302,13 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
 #pragma unroll
         for (int j = 0; j < 32; ++j) o[j] *= inv;
         const int col = col0 + 32 * cb;
-        if (!direct) {
+        if (bulk_out) {
+          uint4* dst = reinterpret_cast<uint4*>(stage_row + 64 * cb);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(pack_bf16x2(o[8 * j], o[8 * j + 1]), pack_bf16x2(o[8 * j + 2], o[8 * j + 3]),
+                                pack_bf16x2(o[8 * j + 4], o[8 * j + 5]), pack_bf16x2(o[8 * j + 6], o[8 * j + 7]));
+        } else if (!direct) {
           float4* dst = reinterpret_cast<float4*>(p.ws_o + ((static_cast<int64_t>(r) * n_splits + split) * p.H + h) * kMlaDv + col);
 #pragma unroll
           for (int j = 0; j < 8; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
@@ -317,6 +328,13 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
             dst[j] = make_uint4(pack_bf16x2(o[8 * j], o[8 * j + 1]), pack_bf16x2(o[8 * j + 2], o[8 * j + 3]),
                                 pack_bf16x2(o[8 * j + 4], o[8 * j + 5]), pack_bf16x2(o[8 * j + 6], o[8 * j + 7]));
         }
+      }
+      if (bulk_out) {
+        fence_proxy_async_smem();  // the copy engine reads the staged row through the async proxy
+        bulk_s2g(static_cast<__nv_bfloat16*>(o_row) + static_cast<int64_t>(h) * kMlaDv + col0, stage_row, kMuDv * 2);
+        bulk_commit();
+        bulk_wait_all();           // the row has been written before this thread reaches the block's notify
+        fence_proxy_async_global();
       }
     }
   } else if (warp >= kMuGatherWarp0 && warp < kMuGatherWarp0 + kMuGatherWarps) {
