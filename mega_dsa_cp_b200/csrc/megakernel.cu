@@ -397,8 +397,3 @@ extern "C" int mdc_megakernel_launch(const mdc_mega_params* p, void* stream) {
   return MDC_OK;
 }
 
-#ifdef MDC_TRACE
-extern "C" int mdc_debug_merge_trace(unsigned long long* host_out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mdc::g_merge_trace, sizeof(mdc::g_merge_trace)));
-}
-#endif

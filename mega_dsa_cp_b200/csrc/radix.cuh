@@ -295,127 +295,6 @@ __device__ inline Threshold<uint32_t> block_select_bits_smem(const uint32_t* key
   return th;
 }
 
-// K-th largest key of a u32 key array in shared memory (0 = empty position; 16-byte aligned;
-// n_pos < 65536) by a most-significant-digit radix search with 4-bit digits: per round every
-// thread buckets its keys that still match the decided prefix into 16 packed per-thread
-// counters, the warps add them up (two 16-bit counters per word) and one shared atomic per word
-// and warp builds the block histogram; everybody reads it and picks the digit.  A quarter of the
-// block-wide synchronisation rounds of the bit-by-bit search, which is what that search's time
-// goes into.  Same result (tau, need_eq, n_sel; *n_eq_out = keys equal to tau).
-__device__ inline Threshold<uint32_t> block_select_r16_smem(const uint32_t* keys, int n_pos, int k, SelectScratch& sc,
-                                                            int* n_eq_out = nullptr) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n4 = n_pos >> 2;
-  const uint4* k4 = reinterpret_cast<const uint4*>(keys);
-  Threshold<uint32_t> th;
-  uint32_t kmax = 0u, kmin = 0xffffffffu;
-  int mine = 0;
-#pragma unroll 2
-  for (int i = tid; i < n4; i += kBlockThreads) {
-    const uint4 q = k4[i];
-    const uint32_t v[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      mine += v[j] != 0u;
-      kmax = max(kmax, v[j]);
-      kmin = min(kmin, v[j] != 0u ? v[j] : 0xffffffffu);
-    }
-  }
-  for (int i = (n4 << 2) + tid; i < n_pos; i += kBlockThreads) {
-    const uint32_t v = keys[i];
-    mine += v != 0u;
-    kmax = max(kmax, v);
-    kmin = min(kmin, v != 0u ? v : 0xffffffffu);
-  }
-  mine = __reduce_add_sync(0xffffffffu, mine);
-  kmax = __reduce_max_sync(0xffffffffu, kmax);
-  kmin = __reduce_min_sync(0xffffffffu, kmin);
-  sync_workers();
-  if (lane == 0) {
-    sc.wgt[warp] = mine;
-    sc.hist[warp] = kmax;
-    sc.hist[8 + warp] = kmin;
-  }
-  for (int i = tid; i < 128; i += kBlockThreads) sc.hist[32 + i] = 0;
-  sync_workers();
-  int total = 0;
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    total += sc.wgt[w];
-    kmax = max(kmax, sc.hist[w]);
-    kmin = min(kmin, sc.hist[8 + w]);
-  }
-  if (total <= k) {
-    th.tau = 0;
-    th.need_eq = 0x7fffffff;
-    th.n_sel = total;
-    sync_workers();
-    return th;
-  }
-  // bits above `hi` are decided (equal to tau's); all valid keys agree above the highest differing bit
-  int hi = 32 - __clz(static_cast<int>((kmax ^ kmin) | 1u));
-  uint32_t tau = hi >= 32 ? 0u : (kmax >> hi) << hi;
-  int k_rem = k, n_eq = 0, round = 0;
-#pragma unroll 1
-  while (hi > 0) {
-    const int shift = max(hi - 4, 0);
-    const uint32_t mask = (1u << (hi - shift)) - 1u;
-    const uint32_t pre = hi >= 32 ? 0u : tau >> hi;
-    unsigned long long lo = 0ull, hi8 = 0ull;  // per-thread counts of buckets 0-7 / 8-15, 8 bits each
-    auto add = [&](uint32_t key) {
-      const bool m = key != 0u && (hi >= 32 || (key >> hi) == pre);
-      const uint32_t bkt = (key >> shift) & mask;
-      const unsigned long long inc = m ? 1ull << (8 * (bkt & 7u)) : 0ull;
-      lo += bkt < 8u ? inc : 0ull;
-      hi8 += bkt < 8u ? 0ull : inc;
-    };
-#pragma unroll 2
-    for (int i = tid; i < n4; i += kBlockThreads) {
-      const uint4 q = k4[i];
-      add(q.x); add(q.y); add(q.z); add(q.w);
-    }
-    for (int i = (n4 << 2) + tid; i < n_pos; i += kBlockThreads) add(keys[i]);
-    uint32_t* hist = &sc.hist[32 + 8 * (round & 7)];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {  // word j = buckets 2j (low half) and 2j + 1 (high half)
-      const unsigned long long src = j < 4 ? lo : hi8;
-      const int sh = 16 * (j & 3);
-      uint32_t w = static_cast<uint32_t>((src >> sh) & 0xffull) | (static_cast<uint32_t>((src >> (sh + 8)) & 0xffull) << 16);
-      w = __reduce_add_sync(0xffffffffu, w);
-      if (lane == 0 && w) atomicAdd(&hist[j], w);
-    }
-    sync_workers();
-    // pick the digit: the largest bucket d with count(bucket > d) < k_rem
-    int above = 0, d = 0, cnt_d = 0;
-    bool found = false;
-#pragma unroll
-    for (int j = 7; j >= 0; --j) {
-      const uint32_t w = hist[j];
-      const int c1 = static_cast<int>(w >> 16), c0 = static_cast<int>(w & 0xffffu);
-      if (!found && above + c1 >= k_rem) { found = true; d = 2 * j + 1; cnt_d = c1; }
-      if (!found) above += c1;
-      if (!found && above + c0 >= k_rem) { found = true; d = 2 * j; cnt_d = c0; }
-      if (!found) above += c0;
-    }
-    k_rem -= above;
-    n_eq = cnt_d;
-    tau |= static_cast<uint32_t>(d) << shift;
-    hi = shift;
-    ++round;
-    if ((round & 7) == 0) {  // the scratch words are reused after 8 rounds (never reached with 32-bit keys)
-      sync_workers();
-      for (int i = tid; i < 64; i += kBlockThreads) sc.hist[32 + i] = 0;
-      sync_workers();
-    }
-  }
-  th.tau = tau;
-  th.need_eq = k_rem;
-  th.n_sel = k;
-  if (n_eq_out) *n_eq_out = n_eq;
-  sync_workers();
-  return th;
-}
-
 // Deterministic emit of the selected elements in position order.
 // emit(pos, slot) is called once per selected element; returns the count.
 template <typename KeyT, typename Src, typename Emit>

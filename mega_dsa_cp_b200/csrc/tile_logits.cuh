@@ -675,10 +675,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       };
       const int64_t slot0 = ((static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk) * p.top_k;
       int n;
-#ifndef MDC_FUSED_COMPACT
-#define MDC_FUSED_COMPACT 1
-#endif
-      if (MDC_FUSED_COMPACT && n_local <= kBlockThreads * kFusedRegE) {
+      if (n_local <= kBlockThreads * kFusedRegE) {
         // the search runs on register keys; the scores become sortable keys in place (0 = not a
         // candidate) and the position-ordered emit is a rolled loop over them: straight-line code that
         // a block executes once per task is bound by instruction fetch, so only the hot search is unrolled
@@ -708,29 +705,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
               p.cand_v[slot0 + slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
               p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
             });
-      } else if (n_local <= kBlockThreads * kFusedRegE) {
-        // register-resident select: one pass over shared memory, ties resolved by position
-        RegSelectScratch<kFusedRegE>& rsel = *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel);
-        uint32_t key[kFusedRegE];
-#pragma unroll
-        for (int it = 0; it < kFusedRegE; ++it) {
-          const int pos = it * kBlockThreads + tid;
-          key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
-        }
-        const Threshold<uint32_t> th = block_select_regs<kFusedRegE>(key, p.top_k, rsel);
-        const bool all = th.need_eq == 0x7fffffff;
-        int slot[kFusedRegE];
-        n = block_emit_regs<kFusedRegE>(
-            all ? 0 : th.need_eq, rsel, [&](int it) { return all ? key[it] != 0u : key[it] > th.tau; },
-            [&](int it) { return !all && key[it] == th.tau; }, slot);
-#pragma unroll
-        for (int it = 0; it < kFusedRegE; ++it) {
-          if (slot[it] >= 0) {
-            const int pos = it * kBlockThreads + tid;
-            p.cand_v[slot0 + slot[it]] = sc_row[pos];
-            p.cand_i[slot0 + slot[it]] = (base_pos + pos) * p.id_mul + p.id_add;
-          }
-        }
       } else {
         Threshold<uint32_t> th = block_select_threshold<uint32_t>(src, n_local, p.top_k, sel);
         n = block_emit_selected<uint32_t>(src, n_local, th, sel, [&](int pos, int slot) {

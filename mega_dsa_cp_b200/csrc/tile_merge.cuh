@@ -16,16 +16,6 @@ namespace mdc {
 
 constexpr int kMergeMaxLists = 256;
 
-#ifdef MDC_TRACE
-// Debug builds only: globaltimer stamps of the merge phases, [block][point].
-__device__ unsigned long long g_merge_trace[256 * 8];
-#define MDC_MTRACE(point)                                                                     \
-  do {                                                                                         \
-    if (threadIdx.x == 0 && blockIdx.x < 256) g_merge_trace[blockIdx.x * 8 + (point)] = global_timer_ns(); \
-  } while (0)
-#else
-#define MDC_MTRACE(point) do { } while (0)
-#endif
 
 constexpr int kMergeRegE = 32;  // register path: up to 256 * 32 = 8192 candidate positions per row
 
@@ -282,83 +272,10 @@ __device__ inline float unsortable_f32(uint32_t kv) {
   return __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
 }
 
-// Staged rows of up to 256 * E positions: keys live in registers for the
-// select (one read of shared memory), a second u32 select on ~id runs only
-// when equal logits straddle the boundary, and the emit reads shared memory.
-template <int E>
-__device__ inline int merge_staged_regs(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
-                                        MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
-  const int tid = threadIdx.x;
-  uint32_t key[E];
-#pragma unroll
-  for (int it = 0; it < E; ++it) {
-    const int pos = it * kBlockThreads + tid;
-    key[it] = pos < n_pos ? vb[pos] : 0u;
-  }
-  MDC_MTRACE(2);
-  const Threshold<uint32_t> th = block_select_regs<E>(key, top_k, sm.rsel);
-  MDC_MTRACE(3);
-  uint32_t sure_m = 0u, tie_m = 0u;  // bit it = element it of this thread
-  int need = 0;
-  if (th.need_eq == 0x7fffffff) {
-#pragma unroll
-    for (int it = 0; it < E; ++it) sure_m |= static_cast<uint32_t>(key[it] != 0u) << it;
-  } else {
-#pragma unroll
-    for (int it = 0; it < E; ++it) {
-      sure_m |= static_cast<uint32_t>(key[it] > th.tau) << it;
-      tie_m |= static_cast<uint32_t>(key[it] == th.tau) << it;
-    }
-    // distinct logits at the boundary (the usual case): need_eq == 1 and exactly one tied entry
-    const int ties = workers_sum(__popc(tie_m), sm.rsel.wcnt);
-    if (ties == th.need_eq) {
-      sure_m |= tie_m;
-      tie_m = 0u;
-    } else {
-#pragma unroll
-      for (int it = 0; it < E; ++it) {
-        const int pos = it * kBlockThreads + tid;
-        key[it] = ((tie_m >> it) & 1u) ? max(~static_cast<uint32_t>(ib[pos]), 1u) : 0u;
-      }
-      const Threshold<uint32_t> t2 = block_select_regs<E>(key, th.need_eq, sm.rsel);
-      uint32_t tie2 = 0u;
-#pragma unroll
-      for (int it = 0; it < E; ++it) {
-        if (t2.need_eq == 0x7fffffff) {
-          sure_m |= static_cast<uint32_t>(key[it] != 0u) << it;
-        } else {
-          sure_m |= static_cast<uint32_t>(key[it] > t2.tau) << it;
-          tie2 |= static_cast<uint32_t>(t2.need_eq > 0 && key[it] != 0u && key[it] == t2.tau) << it;
-        }
-      }
-      tie_m = tie2;
-      need = (t2.need_eq == 0x7fffffff) ? 0 : t2.need_eq;
-    }
-  }
-  int slot[E];
-  MDC_MTRACE(4);
-  const int n = block_emit_regs<E>(
-      need, sm.rsel, [&](int it) { return ((sure_m >> it) & 1u) != 0; }, [&](int it) { return ((tie_m >> it) & 1u) != 0; }, slot);
-  MDC_MTRACE(5);
-#pragma unroll
-  for (int it = 0; it < E; ++it) {
-    if (slot[it] >= 0 && slot[it] < top_k) {
-      const int pos = it * kBlockThreads + tid;
-      out_v[slot[it]] = unsortable_f32(vb[pos]);
-      out_i[slot[it]] = ib[pos];
-    }
-  }
-  MDC_MTRACE(6);
-  if (tid == 0) {
-    *out_c = min(n, top_k);
-    if (n != th.n_sel && dbg) atomicAdd(dbg, 1);
-  }
-  return min(n, top_k);
-}
-
-// Staged rows of up to 256 * E positions, E too large to also keep the output
-// slots in registers: the search runs on register keys (no shared-memory
-// traffic per bit), the emit walks shared memory.
+// Staged rows of up to 256 * E positions: the search runs on register keys (no
+// shared-memory traffic per bit; this loop is hot), the position-ordered emit is a
+// rolled loop over shared memory.  Work that a block does once per task is bound by
+// instruction fetch when it is fully unrolled, so only the hot search is.
 template <int E>
 __device__ inline int merge_staged_hybrid(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
                                           MergeSmem& sm, const uint32_t* vb, const int32_t* ib) {
@@ -427,9 +344,7 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
                                         MergeSmem& sm, const uint32_t* vb, IdFn id_of) {
   const int tid = threadIdx.x;
   int n_eq = 0;
-  MDC_MTRACE(2);
   Threshold<uint32_t> th = block_select_bits_smem(vb, n_pos, top_k, sm.sel, &n_eq);
-  MDC_MTRACE(3);
   const int expect = th.n_sel;
   int n;
   auto put = [&](int pos, int slot) {
@@ -452,7 +367,6 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
     n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { const uint32_t k2 = key2(pos); valid = k2 != 0u; return k2; },
                                       n_pos, t2, sm.sel, put);
   }
-  MDC_MTRACE(6);
   if (tid == 0) {
     *out_c = min(n, top_k);
     if (n != expect && dbg) atomicAdd(dbg, 1);
@@ -471,18 +385,10 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
   if (stage && n_pos * 8 <= stage_bytes && maxK >= 1) {
     uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
     int32_t* ib = reinterpret_cast<int32_t*>(stage) + n_pos;
-    MDC_MTRACE(0);
     merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
-    MDC_MTRACE(1);
-#ifndef MDC_MERGE_PATH
-#define MDC_MERGE_PATH 1
-#endif
-    // 0: register search + register emit; 1: register search + rolled shared-memory emit; 2: rolled search + emit
-    if (MDC_MERGE_PATH == 0 && n_pos <= kBlockThreads * kMergeRegE)
-      return merge_staged_regs<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    if (MDC_MERGE_PATH <= 1 && n_pos <= kBlockThreads * kMergeRegE)
+    if (n_pos <= kBlockThreads * kMergeRegE)
       return merge_staged_hybrid<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    if (MDC_MERGE_PATH <= 1 && n_pos <= kBlockThreads * kMergeBigE)
+    if (n_pos <= kBlockThreads * kMergeBigE)
       return merge_staged_hybrid<kMergeBigE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; });
   }
