@@ -118,16 +118,23 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
   merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
                           reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm, smem + 8192, kMegaTileSmem - 8192);
   if (L.cp > 1) {
+    // The slice goes to every peer as ONE bulk copy each (the copy engine keeps NVLink busy with
+    // large packets; thousands of 16-byte stores per task do not): stage it in shared memory first.
     __threadfence();
     sync_workers();
-    // every 16-byte piece is read once and stored to all peers (posted stores, no load in between)
+    unsigned char* stage = smem + 8192;
     const int n16 = cand_slice_bytes(L) / 16;
-    for (int i = threadIdx.x; i < n16; i += kBlockThreads) {
-      const uint4 v = reinterpret_cast<const uint4*>(slice)[i];
-      for (int dst = 0; dst < L.cp; ++dst) {
-        if (dst != L.rank) reinterpret_cast<uint4*>(arena.peer_ptr(off, dst))[i] = v;
-      }
+    for (int i = threadIdx.x; i < n16; i += kBlockThreads)
+      reinterpret_cast<uint4*>(stage)[i] = reinterpret_cast<const uint4*>(slice)[i];
+    fence_proxy_async_smem();
+    sync_workers();
+    if (threadIdx.x < L.cp && static_cast<int>(threadIdx.x) != L.rank) {
+      bulk_s2g(arena.peer_ptr(off, threadIdx.x), stage, cand_slice_bytes(L));
+      bulk_commit();
+      bulk_wait_all();
+      fence_proxy_async_global();
     }
+    sync_workers();  // the staging area is reused by the block's next task
   }
 }
 
