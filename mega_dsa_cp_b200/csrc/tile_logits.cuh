@@ -101,6 +101,7 @@ struct RowSelectScratch {
   uint32_t hist[2][256];   // digit histograms of this block, double buffered over the radix passes
   int32_t cnt_gt, cnt_eq;  // this block's counts above / at the row threshold
   int32_t digit, excl;     // result of a pass: boundary digit, number of keys in higher bins
+  int32_t bin_cnt, pad0;   // keys in the boundary bin
   int32_t wsum[kWarps];
 };
 
@@ -232,6 +233,7 @@ __device__ void logits_row_select(const mdc_logits_params& p, int b, int chunk, 
     uint32_t prefix = 0u;
     int kk = p.top_k;
     bool all = false;
+    int low_bits = 0;  // undecided low bits when the search stopped early (the boundary bin is taken whole)
 #pragma unroll 1
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass, buf = pass & 1;
@@ -277,16 +279,26 @@ __device__ void logits_row_select(const mdc_logits_params& p, int b, int chunk, 
       if (!all && static_cast<int>(exc) < kk && kk <= static_cast<int>(inc)) {
         rs.digit = bin;
         rs.excl = static_cast<int32_t>(exc);
+        rs.bin_cnt = static_cast<int32_t>(g);
       }
       sync_workers();
       if (pass == 0 && static_cast<int>(total) <= kk) all = true;  // fewer valid entries than k: take all
-      if (!all) {
-        prefix = (prefix << 8) | static_cast<uint32_t>(rs.digit);
-        kk -= rs.excl;
+      if (all) break;  // (every block of the cluster sees the same sums and takes the same exit)
+      prefix = (prefix << 8) | static_cast<uint32_t>(rs.digit);
+      kk -= rs.excl;
+      if (rs.bin_cnt == kk && shift > 0) {  // the whole boundary bin is selected: no finer digit needed
+        low_bits = shift;
+        break;
       }
     }
-    // kk = entries to take among those equal to the threshold key `prefix`
-    const uint32_t tau = all ? 0u : prefix;
+    // Threshold key: entries above it are selected outright, kk of those equal to it in position
+    // order.  After an early stop everything at or above prefix << low_bits is selected.
+    uint32_t tau = all ? 0u : prefix;
+    if (low_bits > 0) {
+      tau = (prefix << low_bits) - 1u;
+      kk = 0;
+      if ((prefix << low_bits) == 0u) all = true;
+    }
     int c_gt = 0, c_eq = 0;
 #pragma unroll
     for (int it = 0; it < E; ++it) {
