@@ -386,6 +386,9 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
     uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
     int32_t* ib = reinterpret_cast<int32_t*>(stage) + n_pos;
     merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
+    // the smallest register budget that holds the row: the search's cost goes with E, not with n_pos
+    if (n_pos <= kBlockThreads * 8) return merge_staged_hybrid<8>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
+    if (n_pos <= kBlockThreads * 16) return merge_staged_hybrid<16>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     if (n_pos <= kBlockThreads * kMergeRegE)
       return merge_staged_hybrid<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     if (n_pos <= kBlockThreads * kMergeBigE)
