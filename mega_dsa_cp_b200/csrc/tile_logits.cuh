@@ -203,6 +203,36 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
   }
 }
 
+// Exact top-k of one chunk's scores (shared memory): the search runs on register keys; the
+// scores become sortable keys in place (0 = not a candidate) and the position-ordered emit is a
+// rolled loop over them.  Straight-line code that a block executes once per task is bound by
+// instruction fetch, so only the hot search is unrolled.  Ties at the threshold go to the
+// smaller position.  Returns the number of entries emitted.
+template <int E, typename Emit>
+__device__ inline int fused_chunk_select(const float* sc_row, uint32_t* keys, int n_local, int base_pos, int limit, int top_k,
+                                         RegSelectScratch<kFusedRegE>& rsel, SelectScratch& sel, Emit emit) {
+  const int tid = threadIdx.x;
+  Threshold<uint32_t> th;
+  {
+    uint32_t key[E];
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      const int pos = it * kBlockThreads + tid;
+      key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+    }
+    sync_workers();
+#pragma unroll
+    for (int it = 0; it < E; ++it) {
+      const int pos = it * kBlockThreads + tid;
+      if (pos < n_local) keys[pos] = key[it];
+    }
+    th = block_select_regs<E>(key, top_k, rsel);
+  }
+  sync_workers();
+  return block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = keys[pos] != 0u; return keys[pos]; }, n_local,
+                                       th, sel, emit);
+}
+
 // Exact top-k of a whole request row across the blocks of a thread-block
 // cluster (block rank = chunk).  Every block holds its chunk's scores in shared
 // memory; the k-th largest key of the row is found by a 4-pass byte radix
@@ -687,36 +717,22 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       };
       const int64_t slot0 = ((static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk) * p.top_k;
       int n;
-      if (n_local <= kBlockThreads * kFusedRegE) {
-        // the search runs on register keys; the scores become sortable keys in place (0 = not a
-        // candidate) and the position-ordered emit is a rolled loop over them: straight-line code that
-        // a block executes once per task is bound by instruction fetch, so only the hot search is unrolled
-        RegSelectScratch<kFusedRegE>& rsel = *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel);
-        uint32_t* keys = reinterpret_cast<uint32_t*>(scores + t * chunk_tokens);
-        Threshold<uint32_t> th;
-        {
-          uint32_t key[kFusedRegE];
-#pragma unroll
-          for (int it = 0; it < kFusedRegE; ++it) {
-            const int pos = it * kBlockThreads + tid;
-            key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
-          }
-          sync_workers();
-#pragma unroll
-          for (int it = 0; it < kFusedRegE; ++it) {
-            const int pos = it * kBlockThreads + tid;
-            if (pos < n_local) keys[pos] = key[it];
-          }
-          th = block_select_regs<kFusedRegE>(key, p.top_k, rsel);
-        }
-        sync_workers();
-        n = block_emit_selected<uint32_t>(
-            [&](int pos, bool& valid) { valid = keys[pos] != 0u; return keys[pos]; }, n_local, th, sel,
-            [&](int pos, int slot) {
-              const uint32_t kv = keys[pos];
-              p.cand_v[slot0 + slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
-              p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
-            });
+      // the smallest register budget that holds the chunk (the search's cost goes with E)
+      RegSelectScratch<kFusedRegE>& rsel = *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel);
+      uint32_t* keys = reinterpret_cast<uint32_t*>(scores + t * chunk_tokens);
+      auto emit = [&](int pos, int slot) {
+        const uint32_t kv = keys[pos];
+        p.cand_v[slot0 + slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
+        p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
+      };
+      if (n_local <= kBlockThreads * 8) {
+        n = fused_chunk_select<8>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
+      } else if (n_local <= kBlockThreads * 16) {
+        n = fused_chunk_select<16>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
+      } else if (n_local <= kBlockThreads * 32) {
+        n = fused_chunk_select<32>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
+      } else if (n_local <= kBlockThreads * 64) {
+        n = fused_chunk_select<64>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
       } else {
         Threshold<uint32_t> th = block_select_threshold<uint32_t>(src, n_local, p.top_k, sel);
         n = block_emit_selected<uint32_t>(src, n_local, th, sel, [&](int pos, int slot) {

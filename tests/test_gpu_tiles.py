@@ -83,6 +83,7 @@ def test_logits_vs_oracle(fmt, P, T, q_fp4, B, S, bpc):
     ("nvfp4", 64, 1, 2048, 128, 16384, 16384, 0),  # K = 2048 from 8192-token chunks
     ("nvfp4", 64, 1, 2048, 16, 4096, 4000, 0),     # chunk smaller than K: everything is a candidate
     ("nvfp4", 64, 1, 256, 64, 8192, 5000, 0),      # chunks beyond seq_len are empty
+    ("nvfp4", 64, 1, 2048, 256, 32768, 31000, 0),  # 16384-token chunks (64 register keys per thread)
 ])
 def test_fused_topk_exact_on_own_logits(fmt, P, T, K, bpc, S, seq, wex):
     B = 2
