@@ -359,20 +359,25 @@ __device__ void logits_row_select(const mdc_logits_params& p, int b, int chunk, 
     const int need_row = all ? 0 : kk;
     const int need = max(0, min(need_row - eq_before, eq_mine));   // ties this block contributes
     const int base = gt_before + min(eq_before, need_row);         // entries selected in lower chunks
-    int slot[E];
-    block_emit_regs<E>(
-        need, rsel, [&](int it) { return all ? key[it] != 0u : key[it] > tau; },
-        [&](int it) { return !all && key[it] == tau; }, slot);
+    // position-ordered emit as a rolled loop over the scores (compact code: it runs once per block)
     const int64_t out0 = (static_cast<int64_t>(b) * T + t) * p.top_k;
-#pragma unroll
-    for (int it = 0; it < E; ++it) {
-      const int o = base + slot[it];
-      if (slot[it] >= 0 && o < p.top_k) {
-        const int pos = it * kBlockThreads + tid;
-        p.row_v[out0 + o] = sc_row[pos];
-        p.row_i[out0 + o] = (base_pos + pos) * p.id_mul + p.id_add;
-      }
-    }
+    Threshold<uint32_t> th;
+    th.tau = tau;
+    th.need_eq = need;
+    th.n_sel = 0;
+    block_emit_selected<uint32_t>(
+        [&](int pos, bool& valid) {
+          valid = (base_pos + pos) < limit;
+          return max(sortable_u32(sc_row[pos]), 1u);
+        },
+        n_local, th, *reinterpret_cast<SelectScratch*>(&rsel),
+        [&](int pos, int slot) {
+          const int o = base + slot;
+          if (o < p.top_k) {
+            p.row_v[out0 + o] = sc_row[pos];
+            p.row_i[out0 + o] = (base_pos + pos) * p.id_mul + p.id_add;
+          }
+        });
     if (chunk == 0 && tid == 0) p.row_c[static_cast<int64_t>(b) * T + t] = min(p.top_k, gt_all + min(eq_all, need_row));
     cluster.sync();  // counts and histograms are reused by the next query token; nobody leaves while a peer may read
   }
