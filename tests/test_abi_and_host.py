@@ -141,9 +141,9 @@ def test_layer_dag_two_ranks_gloo(tmp_path):
     assert "HOST_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
 
 
-@pytest.mark.parametrize("n_chunks,cp,splits", [(2, 1, 1), (4, 2, 2), (8, 2, 4), (16, 4, 1), (5, 8, 2)])
+@pytest.mark.parametrize("n_chunks,cp,splits", [(2, 1, 1), (4, 2, 2), (8, 2, 4), (16, 4, 1), (5, 8, 2), (20, 1, 1)])
 def test_layer_dag_variants_validate(n_chunks, cp, splits):
-    """Two-level local merge (more than 4 chunks), attention slot splits and the four LSE head
+    """Two-level local merge (more than 8 chunks), attention slot splits and the four LSE head
     groups: every variant is a valid DAG on every rank, with the arities the kernels rely on."""
     from mega_dsa_cp_b200.events import validate
     from mega_dsa_cp_b200.layer import LSE_GROUPS, arena_regions, build_layer_dag, l1_groups_for
@@ -151,7 +151,7 @@ def test_layer_dag_variants_validate(n_chunks, cp, splits):
 
     B, heads = 5, 128
     G = l1_groups_for(n_chunks)
-    assert (G == 1) == (n_chunks <= 4) and G * 4 >= n_chunks
+    assert (G == 1) == (n_chunks <= 8) and (G == 1 or G * 4 >= n_chunks)
     tasks, events, ops = build_layer_dag(B, n_chunks, cp, heads, splits, G)
     errors, table = validate(tasks, events, cp)
     assert not errors, errors[:3]
