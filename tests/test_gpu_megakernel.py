@@ -136,6 +136,16 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
         layer.step()
         torch.cuda.synchronize()
         layer.check_status()
+    # the optional task timeline: one entry per task of this rank, stamps in order
+    trace = torch.zeros(4 + 4 * 1024, dtype=torch.int64, device=DEV)
+    layer.step(trace=trace)
+    torch.cuda.synchronize()
+    layer.check_status()
+    n_tasks = len(layer.schedule.topo)
+    assert int(trace[0]) == n_tasks
+    e = trace[4:4 + 4 * n_tasks].reshape(n_tasks, 4).cpu()
+    assert bool((e[:, 1] <= e[:, 2]).all()) and bool((e[:, 2] <= e[:, 3]).all())
+    assert set(((e[:, 0] >> 24) & 0xff).tolist()) <= {1, 2, 3, 4, 5, 6}
     data, sf = orc.split_index_pages(case["fused"], "nvfp4", P)
     kd_all = orc.dequant_fp4(data, sf, "nvfp4").reshape(-1, P, 128)
     for b in range(B):
