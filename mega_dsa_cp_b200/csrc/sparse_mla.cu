@@ -118,3 +118,9 @@ extern "C" int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* strea
 int mdc_attrs_sparse_mla(cudaFuncAttributes* a) {
   return static_cast<int>(cudaFuncGetAttributes(a, mdc::mla_kernel<576, MDC_DT_BF16>));
 }
+
+#ifdef MDC_TRACE
+extern "C" int mdc_debug_mla_trace(long long* host_out) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mdc::g_mla_trace, sizeof(mdc::g_mla_trace)));
+}
+#endif

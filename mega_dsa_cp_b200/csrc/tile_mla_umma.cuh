@@ -28,6 +28,13 @@
 
 namespace mdc {
 
+#ifdef MDC_TRACE
+__device__ long long g_mla_trace[4 * 64 * 8];
+#define MLA_TRACE(role, tile, point) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 64) g_mla_trace[((role) * 64 + (tile)) * 8 + (point)] = clock64(); } while (0)
+#else
+#define MLA_TRACE(role, tile, point) do { } while (0)
+#endif
+
 constexpr int kMuHeads = 128;   // heads per block (= UMMA M)
 constexpr int kMuTile = 64;     // slots per tile
 constexpr int kMuDv = 128;      // output columns per block
@@ -72,6 +79,12 @@ __device__ inline void tmem_ld32_f(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(u[i]);
 }
 }  // namespace umma
+
+__device__ inline float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // Gather one 64-slot tile: this warp's 8 rows.  Returns the validity bits of its rows.
 template <int DQK>
@@ -192,12 +205,14 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     }
     bool ok = true;
     for (int i = 0; i < n_my; ++i) {
+      if (tid == 0) MLA_TRACE(0, i, 0);
       if (!mbar_wait(s_ready, i & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(0, i);
         ok = false;
         break;
       }
       umma::fence_after_sync();
+      if (tid == 0) MLA_TRACE(0, i, 1);
       float sv[kMuTile];
       {
         float a[32], b[32];
@@ -210,14 +225,26 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           sv[32 + j] = b[j];
         }
       }
+      if (tid == 0) MLA_TRACE(0, i, 2);
       const uint2 vb = *reinterpret_cast<const uint2*>(validb + (i % S) * 8);
-      float tmax = neg_inf;
+      // (one warp per scheduler: dependent chains are what costs here, so the maximum and the sum
+      // run on four independent accumulators and a full tile skips the masking)
+      if ((vb.x & vb.y) != 0xffffffffu) {
 #pragma unroll
-      for (int j = 0; j < kMuTile; ++j) {
-        const bool valid = ((j < 32 ? vb.x >> j : vb.y >> (j - 32)) & 1u) != 0;
-        sv[j] = valid ? sv[j] : neg_inf;
-        tmax = fmaxf(tmax, sv[j]);
+        for (int j = 0; j < kMuTile; ++j) {
+          const bool valid = ((j < 32 ? vb.x >> j : vb.y >> (j - 32)) & 1u) != 0;
+          sv[j] = valid ? sv[j] : neg_inf;
+        }
       }
+      float tm[4] = {neg_inf, neg_inf, neg_inf, neg_inf};
+#pragma unroll
+      for (int j = 0; j < kMuTile; j += 4) {
+        tm[0] = fmaxf(tm[0], sv[j]);
+        tm[1] = fmaxf(tm[1], sv[j + 1]);
+        tm[2] = fmaxf(tm[2], sv[j + 2]);
+        tm[3] = fmaxf(tm[3], sv[j + 3]);
+      }
+      const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
       // the reference maximum moves only when the tile maximum exceeds it by more than 2^8
       if (tmax > m_used && (m_used == neg_inf || (tmax - m_used) * c2 > 8.f)) {
         const float corr = (m_used == neg_inf) ? 0.f : exp2f((m_used - tmax) * c2);
@@ -240,15 +267,22 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         }
         m_used = tmax;
       }
-      float ps = 0.f;
       uint32_t pk[kMuTile / 2];
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        // p = 2^((s - m) * c2) as one fused multiply-add and one ex2.approx; a masked slot (-inf)
+        // gives 0, and with m = -inf (nothing valid so far) the whole tile is 0
+        const bool dead = m_used == neg_inf;
+        const float off = dead ? 0.f : -m_used * c2;
 #pragma unroll
-      for (int j = 0; j < kMuTile / 2; ++j) {
-        const float p0 = (m_used == neg_inf) ? 0.f : exp2f((sv[2 * j] - m_used) * c2);
-        const float p1 = (m_used == neg_inf) ? 0.f : exp2f((sv[2 * j + 1] - m_used) * c2);
-        ps += p0 + p1;
-        pk[j] = pack_bf16x2(p0, p1);
+        for (int j = 0; j < kMuTile / 2; ++j) {
+          const float p0 = dead ? 0.f : ex2_approx(fmaf(sv[2 * j], c2, off));
+          const float p1 = dead ? 0.f : ex2_approx(fmaf(sv[2 * j + 1], c2, off));
+          ps4[j & 3] += p0 + p1;
+          pk[j] = pack_bf16x2(p0, p1);
+        }
       }
+      const float ps = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l += ps;
       {
         uint32_t lo[16], hi[16];
@@ -260,10 +294,12 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         umma::tmem_st16(t_lane + kPCol, lo);
         umma::tmem_st16(t_lane + kPCol + 16, hi);
       }
+      if (tid == 0) MLA_TRACE(0, i, 3);
       umma::wait_st();
       umma::fence_before_sync();
       __syncwarp();
       mbar_arrive_if(p_ready, lane == 0);
+      if (tid == 0) MLA_TRACE(0, i, 4);
     }
     if (ok && n_my > 0 && !mbar_wait(o_final, 0, kBudget, abort_flag)) {
       if (lane == 0) give_up(1, n_my);
@@ -363,29 +399,46 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         ok = false;
       }
     }
+    // Tiles [done, i) have been issued but not yet published.  A tile is published as soon as
+    // its copies have landed -- never held back until the NEXT tile could be issued: when the
+    // stage of the next tile is still in use, this warp first drains and publishes what it has
+    // in flight (the tensor core is waiting for exactly that), then waits for the stage.
+    int done = 0;
+    auto publish = [&](int upto) {
+      fence_proxy_async_smem();  // the tensor core reads the tiles through the async proxy
+      __syncwarp();
+      for (int t = done; t < upto; ++t) mbar_arrive_if(&full[t % S], lane == 0);
+      done = upto;
+    };
     for (int i = 0; i < n_my && ok; ++i) {
       const int st = i % S;
-      if (i >= S && !mbar_wait(&free_[st], ((i / S) - 1) & 1, kBudget, abort_flag)) {
-        if (lane == 0) give_up(2, i);
-        ok = false;
-        break;
+      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 0);
+      if (i >= S) {
+        const uint32_t par = ((i / S) - 1) & 1;
+        if (!__all_sync(0xffffffffu, mbar_test(&free_[st], par))) {
+          if (done < i) {
+            cp_async_wait<0>();
+            publish(i);
+          }
+          if (!mbar_wait(&free_[st], par, kBudget, abort_flag)) {
+            if (lane == 0) give_up(2, i);
+            ok = false;
+            break;
+          }
+        }
       }
       const uint32_t bits = mla_umma_gather_rows<DQK>(p, r, (t_begin + i) * kMuTile, k_valid, win_valid,
                                                       kst + st * SM::kStageBytes, gw, lane);
       if (lane == 0) validb[st * 8 + gw] = static_cast<unsigned char>(bits);
-      if (i >= 1) {
+      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 2);
+      if (i - done >= 1) {  // at most two tiles in flight per warp
         cp_async_wait<1>();
-        fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
-        __syncwarp();
-        mbar_arrive_if(&full[(i - 1) % S], lane == 0);
+        publish(i);
       }
+      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 3);
     }
     cp_async_wait<0>();
-    if (ok && n_my > 0) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      mbar_arrive_if(&full[(n_my - 1) % S], lane == 0);
-    }
+    if (ok && n_my > 0) publish(n_my);
   } else if (warp == kMuIssueWarp) {
     // ---------------- issue warp
     constexpr uint32_t idesc_qk = umma::idesc_bf16(kMuHeads, kMuTile, false);
@@ -403,8 +456,11 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       umma::commit(&free_[i % S]);
     };
     for (int i = 0; i < n_my && ok; ++i) {
+      if (lane == 0) MLA_TRACE(1, i, 0);
       ok = mbar_wait(&full[i % S], (i / S) & 1, kBudget, abort_flag);
+      if (lane == 0) MLA_TRACE(1, i, 1);
       if (ok && i > 0) ok = mbar_wait(p_ready, (i - 1) & 1, kBudget, abort_flag);
+      if (lane == 0) MLA_TRACE(1, i, 2);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) give_up(4, i);
         ok = false;
@@ -420,6 +476,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           umma::mma_f16_ts(tmem + kSCol, tmem + 8 * k, bdesc, idesc_qk, k > 0);
         }
         umma::commit(s_ready);
+        MLA_TRACE(1, i, 3);
       }
       __syncwarp();
     }
