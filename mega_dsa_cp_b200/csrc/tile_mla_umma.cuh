@@ -86,17 +86,26 @@ __device__ inline float ex2_approx(float x) {
   return y;
 }
 
-// Gather one 64-slot tile: this warp's 8 rows.  Returns the validity bits of its rows.
+// Row pointers of this warp's 8 rows of one 64-slot tile: lane rr < 8 looks up row gw*8 + rr, so
+// the 8 page-table reads of a tile are one instruction and not a chain (nullptr = masked slot).
 template <int DQK>
-__device__ inline uint32_t mla_umma_gather_rows(const mdc_sparse_mla_params& p, int r, int slot0, int k_valid, int win_valid,
+__device__ inline const unsigned char* mla_umma_row_ptr(const mdc_sparse_mla_params& p, int r, int slot0, int k_valid,
+                                                        int win_valid, int gw, int lane) {
+  return lane < 8 ? mla_slot_ptr<DQK, 2>(p, r, slot0 + gw * 8 + lane, k_valid, win_valid) : nullptr;
+}
+
+// Gather one 64-slot tile: this warp's 8 rows, whose pointers sit in lanes 0-7 (`mine`).  Returns
+// the validity bits of its rows.
+template <int DQK>
+__device__ inline uint32_t mla_umma_gather_rows(const mdc_sparse_mla_params& p, const unsigned char* mine,
                                                 unsigned char* stage, int gw, int lane) {
   constexpr int kChunks = DQK / 8;  // 16-byte chunks per row
-  uint32_t bits = 0;
-#pragma unroll 2
+  const uint32_t bits = __ballot_sync(0xffffffffu, mine != nullptr) & 0xffu;
+  const unsigned long long mine_u = reinterpret_cast<unsigned long long>(mine);
+#pragma unroll
   for (int rr = 0; rr < 8; ++rr) {
     const int s = gw * 8 + rr;
-    const unsigned char* src = mla_slot_ptr<DQK, 2>(p, r, slot0 + s, k_valid, win_valid);
-    bits |= static_cast<uint32_t>(src != nullptr) << rr;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(__shfl_sync(0xffffffffu, mine_u, rr));
     const unsigned char* base = src ? src : static_cast<const unsigned char*>(p.kv_cmp);
 #pragma unroll
     for (int ch = lane; ch < kChunks; ch += 32) {
@@ -410,6 +419,9 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       for (int t = done; t < upto; ++t) mbar_arrive_if(&full[t % S], lane == 0);
       done = upto;
     };
+    // row pointers are looked up one tile ahead, so the page-table read is not on the path
+    const unsigned char* mine = n_my > 0 ? mla_umma_row_ptr<DQK>(p, r, t_begin * kMuTile, k_valid, win_valid, gw, lane)
+                                         : nullptr;
     for (int i = 0; i < n_my && ok; ++i) {
       const int st = i % S;
       if (gw == 0 && lane == 0) MLA_TRACE(2, i, 0);
@@ -427,8 +439,8 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           }
         }
       }
-      const uint32_t bits = mla_umma_gather_rows<DQK>(p, r, (t_begin + i) * kMuTile, k_valid, win_valid,
-                                                      kst + st * SM::kStageBytes, gw, lane);
+      const uint32_t bits = mla_umma_gather_rows<DQK>(p, mine, kst + st * SM::kStageBytes, gw, lane);
+      if (i + 1 < n_my) mine = mla_umma_row_ptr<DQK>(p, r, (t_begin + i + 1) * kMuTile, k_valid, win_valid, gw, lane);
       if (lane == 0) validb[st * 8 + gw] = static_cast<unsigned char>(bits);
       if (gw == 0 && lane == 0) MLA_TRACE(2, i, 2);
       if (i - done >= 1) {  // at most two tiles in flight per warp
