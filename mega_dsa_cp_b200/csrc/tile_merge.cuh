@@ -386,6 +386,32 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
     uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
     int32_t* ib = reinterpret_cast<int32_t*>(stage) + n_pos;
     merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
+    {
+      // Nothing to select when the lists hold no more than top_k entries between them (one rank's
+      // list passing through the cross-rank merge, short contexts): every valid position is
+      // emitted, in position order like the general path.
+      int n_valid = 0;
+      for (int l = 0; l < L; ++l) n_valid += sm.cnt[l];
+      if (n_valid <= top_k) {
+        Threshold<uint32_t> all;
+        all.tau = 0u;  // valid keys are >= 1
+        all.need_eq = 0;
+        all.n_sel = n_valid;
+        const int n = block_emit_selected<uint32_t>(
+            [&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, all, sm.sel,
+            [&](int pos, int slot) {
+              if (slot < top_k) {
+                out_v[slot] = unsortable_f32(vb[pos]);
+                out_i[slot] = ib[pos];
+              }
+            });
+        if (threadIdx.x == 0) {
+          *out_c = n;
+          if (n != n_valid && dbg) atomicAdd(dbg, 1);
+        }
+        return n;
+      }
+    }
     // the smallest register budget that holds the row: the search's cost goes with E, not with n_pos
     if (n_pos <= kBlockThreads * 8) return merge_staged_hybrid<8>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     if (n_pos <= kBlockThreads * 16) return merge_staged_hybrid<16>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);

@@ -140,6 +140,7 @@ def test_merge_golden_ordered_bitwise():
     (2, 2, 4, 512, 512, "tiny"), (2, 2, 8, 512, 512, "ties"), (2, 2, 4, 512, 512, "const"),
     (2, 2, 8, 512, 512, "neginf"), (1, 2, 256, 128, 512, "full"), (2, 2, 1, 1024, 1024, "var"),
     (2, 1, 8, 2048, 2048, "full"), (1, 1, 6, 2048, 2048, "var"),
+    (2, 1, 1, 2048, 2048, "full"), (2, 1, 4, 512, 2048, "full"), (2, 1, 4, 512, 2048, "neginf"),  # nothing to drop
 ])
 def test_merge_vs_oracle_and_deterministic(B, q, L, maxK, K, mode):
     g = torch.Generator().manual_seed(B * 131 + L)
