@@ -2,15 +2,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-N = 1 runs BASELINE config 2 (indexer logits + exact top-k 2048, B = 32 decode
-queries, context 32768, NVFP4 index cache in 64-token pages, random page
-tables).  One step = one pass of that path over the batch; the metric is decode
-tokens per second (B * q_len / step time).  Prints ONE JSON line (rank 0).
+Every N times the same workload family: one full DSA decode layer-step at
+128K context (indexer logits over the paged NVFP4 index cache, exact top-k
+2048, sparse MLA over the selection, LSE merge) as ONE persistent-kernel
+launch per rank, 8 sequences per rank, the context sharded token-interleaved
+over the N ranks (weak scaling; N = 8 is BASELINE config 4: B = 64, 16384
+tokens per rank per sequence).  One step = one layer-call of the operator;
+the metric is decode tokens per second (B * q_len / step time).  Prints ONE
+JSON line (rank 0).
 
-Timing: CUDA events on the launching stream around exactly K steps, after W
-warm-up steps, max over ranks.  The 75.5 MB index cache would fit the 126 MB
-L2, so the steps rotate over several independent copies of the cache (more
-than L2 in total): every step streams its bytes from HBM.
+Timing: CUDA events on the launching stream around exactly K steps after W
+warm-up steps, barrier + synchronize on both sides, max over ranks.  Each rank
+rotates over two independent copies of its caches (index cache 75.5 MB and
+KV pool 1.2 GB per copy), so every step streams from HBM, not from L2.
+
+At N = 1 the line also carries the roofline of the dominant kernel family
+measured alone: the indexer (BASELINE config 2: B = 32, context 32768,
+logits + exact top-k 2048 in one launch) and the tcgen05 sparse-MLA tile.
 """
 
 from __future__ import annotations
@@ -36,8 +44,9 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -91,231 +100,67 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-# ----------------------------------------------------------------------------
-# config 2 workload
-# ----------------------------------------------------------------------------
-CFG2 = dict(B=32, S=32768, page=64, top_k=2048, q_len=1, copies=4, blocks_per_chunk=128)
+class Ranks:
+    """The process group of the run, or a stand-in at N = 1 (no rendezvous needed)."""
 
+    def __init__(self):
+        import torch
 
-def cfg2_algorithmic_bytes(c, row_mode=True) -> int:
-    """Bytes one logits launch must move: 72 B per (sequence, token) of NVFP4
-    index-K, 4 B per page-table entry, 16640 B of bf16 query + weights per
-    sequence, 8 B per emitted entry (top-k per row in row mode, per chunk otherwise)."""
-    B, S, P, K = c["B"], c["S"], c["page"], c["top_k"]
-    n_lists = 1 if row_mode else (S // P) // c["blocks_per_chunk"]
-    return B * S * 72 + B * (S // P) * 4 + B * 16640 + B * n_lists * K * 8
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", self.rank))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        self.group_name = "0"
+        if self.world > 1:
+            import torch.distributed as dist
 
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+            self.group_name = dist.group.WORLD.group_name
 
-def build_cfg2_device(c, device, seed=0):
-    """Index caches (one per rotation copy), queries, weights, page tables on the GPU.
-    Values: K ~ N(0,1) quantised to NVFP4, q ~ N(0,1) in bf16, w ~ N(0, 1/64)."""
-    import torch
-    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
 
-    g = torch.Generator(device=device).manual_seed(seed)
-    B, S, P = c["B"], c["S"], c["page"]
-    pages_per_seq = S // P
-    pool = B * pages_per_seq
-    caches, tables = [], []
-    for _ in range(c["copies"]):
-        parts = []
-        for _ in range(8):  # quantise in slices to bound temporary memory
-            raw = torch.randn(pool // 8 * P, 128, generator=g, device=device)
-            parts.append(fuse_pages(raw, "nvfp4", P)[0])
-        caches.append(torch.cat(parts))
-        perm = torch.randperm(pool, generator=g, device=device).to(torch.int32)
-        tables.append(perm.reshape(B, pages_per_seq).contiguous())
-    q = torch.randn(B, 64 * c["q_len"], 128, generator=g, device=device).to(torch.bfloat16)
-    w = (torch.randn(B, 64 * c["q_len"], generator=g, device=device) / 64.0).contiguous()
-    return caches, tables, q, w
+    def reduce_max(self, values):
+        import torch
 
+        t = torch.tensor(values, device=self.dev, dtype=torch.float64)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.tolist()
 
-def run_gpu_cfg2(args):
-    import torch
-    from mega_dsa_cp_b200.tiles.logits import run_fp4_paged_mqa_logits
-    from mega_dsa_cp_b200.tiles.merge import run_merge_topk
+    def reduce_min(self, values):
+        import torch
 
-    c = CFG2
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    caches, tables, q, w = build_cfg2_device(c, dev)
-    B, K, T = c["B"], c["top_k"], c["q_len"]
-    bpc = c["blocks_per_chunk"]
-    n_chunks = (c["S"] // c["page"]) // bpc
-    cv = torch.empty(B, T, n_chunks, K, device=dev)
-    ci = torch.empty(B, T, n_chunks, K, dtype=torch.int32, device=dev)
-    cc = torch.empty(B, T, n_chunks, dtype=torch.int32, device=dev)
-    ov = torch.empty(B, T, K, device=dev)
-    oi = torch.empty(B, T, K, dtype=torch.int32, device=dev)
-    oc = torch.empty(B, T, dtype=torch.int32, device=dev)
-    status = torch.zeros(8, dtype=torch.int32, device=dev)
+        t = torch.tensor(values, device=self.dev, dtype=torch.float64)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return t.tolist()
 
-    two = args.two_kernel  # reference-shaped path: chunk candidates, then the merge kernel
+    def sum_(self, t):
+        if self.dist is not None:
+            self.dist.all_reduce(t)
+        return t
 
-    def logits_only(i, qq=q, ww=w, tables_=None):
-        r = i % c["copies"]
-        bt = tables[r] if tables_ is None else tables_[r]
-        if two:
-            run_fp4_paged_mqa_logits(caches[r], qq, None, ww, bt, None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
-                                     top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
-        else:  # one launch: the four blocks of a sequence select across their chunks as a cluster
-            run_fp4_paged_mqa_logits(caches[r], qq, None, ww, bt, None, bpc, top_k=K, fmt="nvfp4",
-                                     page_tokens=c["page"], status=status, row_topk=(ov, oi, oc))
+    def gather(self, t):
+        import torch
 
-    def step(i, qq=q, ww=w, tables_=None):
-        logits_only(i, qq, ww, tables_)
-        if two:
-            run_merge_topk(cv, ci, cc, ov, oi, oc, None, top_k=K)
+        if self.dist is None:
+            return [t]
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t.contiguous())
+        return out
 
-    for i in range(max(args.warmup, c["copies"])):
-        step(i)
-    torch.cuda.synchronize()
-    # one CUDA graph per cache copy holds the step's two launches: the timed loop replays them, so the
-    # host's launch latency (larger than the gap between the kernels) stays out of the device timeline
-    graphs = None
-    if not args.no_graph:
-        graphs = []
-        for r in range(c["copies"]):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                step(r)
-            graphs.append(g)
-        for i in range(args.warmup):
-            graphs[i % c["copies"]].replay()
-        torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(0) as clk:
-        time.sleep(0.1)
-        torch.cuda.synchronize()
-        ev0.record()
-        for i in range(args.steps):
-            if graphs is None:
-                step(args.warmup + i)
-            else:
-                graphs[(args.warmup + i) % c["copies"]].replay()
-        ev1.record()
-        torch.cuda.synchronize()
-        ms_total = ev0.elapsed_time(ev1)
-        # dominant kernel alone (same rotation), for the roofline
-        reps = max(args.steps, 20)
-        for i in range(3):
-            logits_only(i)
-        torch.cuda.synchronize()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record()
-        for i in range(reps):
-            logits_only(i)
-        k1.record()
-        torch.cuda.synchronize()
-        ms_logits = k0.elapsed_time(k1) / reps
-        time.sleep(0.1)
-    assert status[0].item() == 0, f"device failure {status.tolist()}"
-    ms_step = ms_total / args.steps
-
-    # end to end: per-step tensors start in pinned host memory (query, gate
-    # weights, page table), the selected ids come back; the index cache is
-    # resident state, like model weights, and is not re-sent.
-    # One pinned host block [q | w | page table] per cache copy goes down in one copy, one block
-    # [ids | counts] comes back: the latency of each copy, not its bytes, is what costs at this size.
-    nq, nw, nbt = q.numel() * 2, w.numel() * 4, tables[0].numel() * 4
-    hin, din, dq, dw, dbt = [], [], [], [], []
-    for r in range(c["copies"]):
-        h = torch.empty(nq + nw + nbt, dtype=torch.uint8).pin_memory()
-        h[:nq].copy_(q.cpu().view(torch.uint8).reshape(-1))
-        h[nq:nq + nw].copy_(w.cpu().view(torch.uint8).reshape(-1))
-        h[nq + nw:].copy_(tables[r].cpu().view(torch.uint8).reshape(-1))
-        d = torch.empty_like(h, device=dev)
-        hin.append(h)
-        din.append(d)
-        dq.append(d[:nq].view(torch.bfloat16).view_as(q))
-        dw.append(d[nq:nq + nw].view(torch.float32).view_as(w))
-        dbt.append(d[nq + nw:].view(torch.int32).view_as(tables[r]))
-    dout = torch.empty(B * T * K + B * T, dtype=torch.int32, device=dev)
-    e_oi, e_oc = dout[:B * T * K].view(B, T, K), dout[B * T * K:].view(B, T)
-    e_ov = torch.empty(B, T, K, device=dev)
-    hout = torch.empty(B * T * K + B * T, dtype=torch.int32).pin_memory()
-    h_cnt = hout[B * T * K:]
-
-    def e2e_body(r):
-        din[r].copy_(hin[r], non_blocking=True)
-        if two:
-            run_fp4_paged_mqa_logits(caches[r], dq[r], None, dw[r], dbt[r], None, bpc, cand_v=cv, cand_i=ci, cand_c=cc,
-                                     top_k=K, fmt="nvfp4", page_tokens=c["page"], status=status)
-            run_merge_topk(cv, ci, cc, e_ov, e_oi, e_oc, None, top_k=K)
-        else:
-            run_fp4_paged_mqa_logits(caches[r], dq[r], None, dw[r], dbt[r], None, bpc, top_k=K, fmt="nvfp4",
-                                     page_tokens=c["page"], status=status, row_topk=(e_ov, e_oi, e_oc))
-        hout.copy_(dout, non_blocking=True)
-
-    def e2e_step(i):
-        e2e_body(i % c["copies"])
-        torch.cuda.current_stream().synchronize()
-
-    for i in range(max(args.warmup, c["copies"])):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    e2e_graphs = None
-    if not args.no_graph:
-        # the whole step (H2D copy from pinned memory, the launch, D2H copy) as one graph per cache copy
-        e2e_graphs = []
-        for r in range(c["copies"]):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                e2e_body(r)
-            e2e_graphs.append(g)
-
-        def e2e_step(i):  # noqa: F811  (replaces the eager version for the timed loop)
-            e2e_graphs[i % c["copies"]].replay()
-            torch.cuda.current_stream().synchronize()
-
-        for i in range(args.warmup):
-            e2e_step(i)
-        torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(args.warmup + i)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    assert status[0].item() == 0 and int(h_cnt.min()) == K, "end-to-end step returned an incomplete selection"
-    h2d = hin[0].numel()
-    d2h = hout.numel() * 4
-
-    peak, peak_kind = measured_peaks()
-    algo = cfg2_algorithmic_bytes(c, row_mode=not two)
-    n_kernels = 2 if two else 1
-    achieved = algo / (ms_logits * 1e-3) / 1e9
-    cpu = None if args.skip_cpu else cpu_baseline_cfg2(sample_seqs=1, reps=3)
-    tokens = B * T
-    line = {
-        "metric": METRIC, "value": tokens / (ms_step * 1e-3), "unit": UNIT, "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1 x ue4m3) x bf16 -> f32", "data": "synthetic",
-        "config": {"workload": "cfg2: indexer logits + exact top-k 2048, B=32, ctx 32768, NVFP4 64-token pages, "
-                               "random page tables, bf16 q (64 heads x 128)",
-                   "l2": f"rotating {c['copies']} cache copies ({c['copies'] * 75.5:.0f} MB > 126 MB L2)",
-                   "parallelism": "cp1", "kernels_per_step": n_kernels,
-                   "launch": "eager" if graphs is None else "CUDA graph replay (one graph per cache copy)"},
-        "step_us": ms_step * 1e3,
-        "indexer_us": ms_logits * 1e3,
-        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": n_kernels * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "kernel": "logits_kernel<NVFP4,64,1>" if two else "logits_row_kernel<NVFP4,64,1>",
-                     "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES},
-        "cpu_baseline": cpu,
-        "clocks": clk.summary(),
-    }
-    if not args.skip_layer:
-        caches.clear()
-        torch.cuda.empty_cache()
-        line["decode_step_cp1"] = cp1_layer_step(min(args.steps, 20), args.warmup, dev)
-    print(json.dumps(line))
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
 
 
 # ----------------------------------------------------------------------------
-# N > 1: the full decode layer-step, context parallel over N GPUs
+# the workload: one decode layer-step at 128K context, context parallel over N ranks
 # ----------------------------------------------------------------------------
 def cp_config(n):
     """128K-token context sharded over n ranks, 8 sequences per rank (BASELINE
@@ -323,47 +168,23 @@ def cp_config(n):
     return dict(B=8 * n, S=131072, page=64, top_k=2048, H=128, d_qk=576, cp=n, copies=2, blocks_per_chunk=128)
 
 
-def cp1_layer_step(steps, warmup, dev):
-    """The full decode layer-step at CP=1 (B = 8 sequences of 128 K tokens, one megakernel launch),
-    reported beside the N=1 line so that the CP=2/4/8 runs have their single-GPU counterpart."""
-    import torch
-    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
-    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
-
-    c = cp_config(1)
-    B, P, K, H, DQK, S = c["B"], c["page"], c["top_k"], c["H"], c["d_qk"], c["S"]
-    pages = S // P
-    g = torch.Generator(device=dev).manual_seed(1000)
-    q_idx = torch.randn(B, 64, 128, generator=g, device=dev).to(torch.bfloat16)
-    w_idx = (torch.randn(B, 64, generator=g, device=dev) / 64.0).contiguous()
-    q_mla = (torch.randn(B, 1, H, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
-    seq = torch.full((B,), S, dtype=torch.int32, device=dev)
-    layers = []
-    for _ in range(c["copies"]):
-        parts = [fuse_pages(torch.randn(B * S // 8, 128, generator=g, device=dev), "nvfp4", P)[0] for _ in range(8)]
-        cache = torch.cat(parts)
-        bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages).contiguous()
-        kv = (torch.randn(B * S, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
-        layer = DsaDecodeLayer(B, cp=1, rank=0, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
-                               blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S, device=dev)
-        layer.bind(LayerInputs(cache, bt, seq, q_idx, w_idx, q_mla, kv))
-        layers.append(layer)
-    for i in range(max(warmup, len(layers))):
-        layers[i % len(layers)].step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        layers[i % len(layers)].step()
-    e1.record()
-    torch.cuda.synchronize()
-    for l in layers:
-        l.check_status()
-    ms = e0.elapsed_time(e1) / steps
-    return {"step_us": ms * 1e3, "tokens_per_s": B / (ms * 1e-3), "gpu_launches_per_step": 1,
-            "timeline": task_timeline(layers[0], dev),
-            "config": f"full DSA decode layer-step, CP=1: B={B}, ctx {S}, indexer + top-k {K} + sparse MLA "
-                      f"(128 heads, 512+64) + LSE merge, one persistent kernel"}
+def layer_algorithmic_bytes(c, attn_splits):
+    """Bytes one rank's layer-step must move, per phase (the per-unit figures: 72 B per (sequence,
+    token) of NVFP4 index-K + 4 B per page + 16640 B of query per sequence; 8 B per candidate read or
+    written; 1152 B per selected KV row + 147456 B of query per sequence; 131584 B per partial)."""
+    B, cp, K, P = c["B"], c["cp"], c["top_k"], c["page"]
+    S_loc = c["S"] // cp
+    pages = S_loc // P
+    n_chunks = -(-pages // c["blocks_per_chunk"])
+    part = 128 * 512 * 2 + 128 * 4
+    owned = -(-B // cp)
+    return {
+        "LOGITS": B * S_loc * 72 + B * pages * 4 + B * 16640 + B * n_chunks * K * 8,
+        "MERGE_L1": B * n_chunks * K * 8 + B * K * 8 * cp,
+        "MERGE_L2": B * cp * K * 8 + B * K * 12,
+        "ATTN": B * (K // cp) * 1152 + B * 128 * 576 * 2 + B * attn_splits * part,
+        "LSE_MERGE": owned * (cp * attn_splits * part + part),
+    }
 
 
 OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE", 6: "MERGE_L1A"}
@@ -371,7 +192,9 @@ OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE"
 
 def task_timeline(layer, dev):
     """One traced layer-step: per op the task count, mean wait / body time and the time its last task
-    ended (us from the first task's start), from the megakernel's optional trace buffer."""
+    ended (us from the first task's start), from the megakernel's optional trace buffer; plus the
+    LSE-merge latency per owned sequence: from the moment the first merge task of the sequence saw
+    all partials present to the moment its last head group was written."""
     import torch
 
     trace = torch.zeros(4 + 4 * 8192, dtype=torch.int64, device=dev)
@@ -381,34 +204,42 @@ def task_timeline(layer, dev):
     n = min(int(t[0]), 8192)
     e = t[4:4 + 4 * n].reshape(n, 4)
     if n == 0:
-        return {}
+        return {}, None
     t0 = int(e[:, 1].min())
+    ops = (e[:, 0] >> 24) & 0xff
     out = {}
-    for op in sorted(set(((e[:, 0] >> 24) & 0xff).tolist())):
-        m = ((e[:, 0] >> 24) & 0xff) == op
+    for op in sorted(set(ops.tolist())):
+        m = ops == op
         a, b, c = e[m, 1].double(), e[m, 2].double(), e[m, 3].double()
         out[OP_NAMES.get(op, str(op))] = {"tasks": int(m.sum()), "wait_us": round(float((b - a).mean()) / 1e3, 1),
                                           "body_us": round(float((c - b).mean()) / 1e3, 1),
+                                          "first_start_us": round(float(b.min() - t0) / 1e3, 1),
                                           "last_end_us": round(float(c.max() - t0) / 1e3, 1)}
-    return out
+    lat = None
+    m = ops == 5
+    if bool(m.any()):
+        seq = (e[m, 0] >> 12) & 0xfff
+        lats = []
+        for b in sorted(set(seq.tolist())):
+            mb = seq == b
+            lats.append(float(e[m][mb, 3].max() - e[m][mb, 2].min()) / 1e3)
+        lat = {"mean_us": round(sum(lats) / len(lats), 2), "max_us": round(max(lats), 2), "sequences": len(lats),
+               "definition": "first merge task of a sequence sees all partials arrived -> last head group written"}
+    return out, lat
 
 
-def run_gpu_cp(args):
+def build_rank(R, c, seed0=1000):
+    """This rank's caches (c['copies'] rotation copies), the replicated per-step query block and
+    one DsaDecodeLayer per copy."""
     import torch
-    import torch.distributed as dist
     from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
     from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
 
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    c = cp_config(world)
+    dev, world, rank = R.dev, R.world, R.rank
     B, P, K, H, DQK = c["B"], c["page"], c["top_k"], c["H"], c["d_qk"]
     S_loc = c["S"] // world
     pages = S_loc // P
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    g = torch.Generator(device=dev).manual_seed(seed0 + rank)
     gq = torch.Generator(device=dev).manual_seed(7)      # replicated tensors: same seed on every rank
     # the per-step tensors (indexer query, gate weights, attention query) are views of ONE device block,
     # so that the end-to-end step sends them from pinned host memory in one copy
@@ -425,15 +256,112 @@ def run_gpu_cp(args):
     for _ in range(c["copies"]):   # rotate over cache copies so every step streams from HBM
         parts = [fuse_pages(torch.randn(B * S_loc // 8, 128, generator=g, device=dev), "nvfp4", P)[0] for _ in range(8)]
         cache = torch.cat(parts)
+        del parts
         bt = torch.randperm(B * pages, generator=g, device=dev).to(torch.int32).reshape(B, pages).contiguous()
         kv = (torch.randn(B * S_loc, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
         layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
                                blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S_loc,
-                               group_name=dist.group.WORLD.group_name, device=dev)
+                               group_name=R.group_name, device=dev)
         layer.bind(LayerInputs(cache, bt, seq_loc, q_idx, w_idx, q_mla, kv))
         layers.append(layer)
         inputs.append((cache, bt, kv))
-    dist.barrier()
+    return layers, inputs, dblock, (q_idx, w_idx, q_mla)
+
+
+def parity_block(R, c, layer, inp, q):
+    """Outside the timed region: one owned sequence per rank against the CPU oracle at full size.
+    The sequence's index-K shards and the KV rows of the ids the kernel selected are collected from
+    all ranks; the owner recomputes the logits (dequantised FP4, fp32), the exact hierarchical
+    top-k and the cp-way attention + LSE merge over the kernel's own selection.  Returns the worst
+    figures over all ranks."""
+    import torch
+    from oracle import dsa_oracle as orc
+
+    world, rank, dev = R.world, R.rank, R.dev
+    cache, bt, kv = inp
+    q_idx, w_idx, q_mla = q
+    B, K, P, S, DQK = c["B"], c["top_k"], c["page"], c["S"], c["d_qk"]
+    S_loc = S // world
+    d_o = d_l = 0.0
+    overlap, count_ok, same_sel = 1.0, 1.0, 1.0
+    for b in range(min(world, B)):          # sequence b is owned by rank b % world == b
+        shards = R.gather(cache[bt[b].long()])                       # [world] x (pages, page bytes)
+        n = int(layer.sel_c[b])
+        sel = layer.sel_i[b, :n].clone()
+        ref_sel = sel.clone()
+        if R.dist is not None:
+            R.dist.broadcast(ref_sel, 0)
+        same_sel = min(same_sel, 1.0 if torch.equal(ref_sel, sel) else 0.0)
+        rows = torch.zeros(K, DQK, dtype=torch.float32, device=dev)
+        mine = (sel % world) == rank
+        rows[:n][mine] = kv[(b * S_loc + sel[mine] // world).long(), 0].float()
+        R.sum_(rows)                                                  # every id is held by exactly one rank
+        if rank != b % world:
+            continue
+        kd = torch.empty(S, 128)
+        for r, sh in enumerate(shards):
+            data, sf = orc.split_index_pages(sh.cpu(), "nvfp4", P)
+            kd[r::world] = orc.dequant_fp4(data, sf, "nvfp4").reshape(S_loc, 128)
+        qi, wi = q_idx[b].float().cpu(), w_idx[b].cpu()
+        want = orc.select_topk_ref(qi, wi, kd, S, K, cp=world)
+        got = sel.cpu()
+        overlap = min(overlap, len(set(got.tolist()) & set(want.tolist())) / max(1, want.numel()))
+        count_ok = min(count_ok, 1.0 if n == want.numel() else 0.0)
+        # attention over the kernel's own selection: row j of `rows` is the KV row of sel[j]
+        o, l = orc.attend_selected_ref(q_mla[b, 0].float().cpu(), rows[:n].cpu(), got, 1.0 / math.sqrt(DQK),
+                                       cp=world, rows_are_selected=True)
+        d_o = max(d_o, float((layer.out[b // world].float().cpu() - o).abs().max()))
+        d_l = max(d_l, float((layer.out_lse[b // world].cpu() - l).abs().max()))
+    worst = R.reduce_max([d_o, d_l])
+    best = R.reduce_min([overlap, count_ok, same_sel])
+    ok = worst[0] < 2e-2 and worst[1] < 1e-3 and best[0] >= 0.999 and best[1] == 1.0 and best[2] == 1.0
+    return {"checked_rows": min(world, B), "max_abs_o": worst[0], "max_abs_lse": worst[1], "sel_overlap": best[0],
+            "sel_count_exact": bool(best[1] == 1.0), "sel_identical_on_all_ranks": bool(best[2] == 1.0),
+            "tolerance": "o 2e-2 abs (bf16), log2-LSE 1e-3, selection overlap >= 0.999 vs oracle logits",
+            "ok": bool(ok)}
+
+
+def nccl_baseline(R, c, attn_splits, reps=20):
+    """NCCL collectives of the same payloads as the two exchange steps, timed beside the P2P path
+    (the measured baseline only; the product path never calls them): all-gather of every sequence's
+    candidate list, and the all-to-all of the bf16 partials + LSEs to their owners."""
+    import torch
+
+    if R.dist is None:
+        return None
+    B, K, cp = c["B"], c["top_k"], R.world
+    cand = torch.zeros(B * (K * 8 + 16), dtype=torch.uint8, device=R.dev)
+    cand_all = torch.zeros(cp * cand.numel(), dtype=torch.uint8, device=R.dev)
+    part = (B // cp) * attn_splits * (128 * 512 * 2 + 128 * 4)
+    send = torch.zeros(cp * part, dtype=torch.uint8, device=R.dev)
+    recv = torch.zeros_like(send)
+    out = {}
+    for name, fn in (("all_gather_candidates_us", lambda: R.dist.all_gather_into_tensor(cand_all, cand)),
+                     ("all_to_all_partials_us", lambda: R.dist.all_to_all_single(recv, send))):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        R.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = round(R.reduce_max([e0.elapsed_time(e1) / reps * 1e3])[0], 1)
+    out["bytes_per_rank"] = {"candidates": cand.numel(), "partials": send.numel()}
+    return out
+
+
+def run_layer(args):
+    import torch
+
+    R = Ranks()
+    world, rank, dev = R.world, R.rank, R.dev
+    c = cp_config(world)
+    B, H, DQK = c["B"], c["H"], c["d_qk"]
+    layers, inputs, dblock, q = build_rank(R, c)
+    R.barrier()
     torch.cuda.synchronize()
 
     def step(i):
@@ -442,163 +370,299 @@ def run_gpu_cp(args):
     for i in range(args.warmup * len(layers)):
         step(i)
     torch.cuda.synchronize()
-    dist.barrier()
+    R.barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    with ClockSampler(R.local) as clk:
         time.sleep(0.1)
-        dist.barrier()
+        R.barrier()
         torch.cuda.synchronize()
         ev0.record()
         for i in range(args.steps):
             step(i)
         ev1.record()
         torch.cuda.synchronize()
-        dist.barrier()
+        R.barrier()
         ms = ev0.elapsed_time(ev1)
         time.sleep(0.1)
     for l in layers:
         l.check_status()
-    dist.barrier()
-    timeline = task_timeline(layers[0], dev)   # every rank steps (the ranks wait on each other); rank 0 reports
+    R.barrier()
+    timeline, lse_lat = task_timeline(layers[0], dev)   # every rank steps (the ranks wait on each other); rank 0 reports
     layers[0].check_status()
-    # end to end: query tensors from pinned host memory each step, merged output rows read back
+    R.barrier()
+    parity = parity_block(R, c, layers[0], inputs[0], q)
+
+    # end to end through DsaDecodeLayer: the step's query block comes from pinned host memory, the
+    # owned output rows go back to pinned host memory, both inside the timed region
     hblock = dblock.cpu().pin_memory()
     owned = layers[0].owned_rows()
     h_out = torch.empty(len(owned), H, 512, dtype=torch.bfloat16).pin_memory()
-    d_out = torch.empty(len(owned), H, 512, dtype=torch.bfloat16, device=dev)
-    idx = torch.tensor(owned, device=dev)
 
     def e2e_step(i):
         dblock.copy_(hblock, non_blocking=True)
         l = layers[i % len(layers)]
         l.step()
-        torch.index_select(l.out, 0, idx, out=d_out)
-        h_out.copy_(d_out, non_blocking=True)
+        h_out.copy_(l.out, non_blocking=True)   # the layer keeps only its owned rows: one contiguous copy
         torch.cuda.current_stream().synchronize()
 
     for i in range(args.warmup):
         e2e_step(i)
-    dist.barrier()
+    R.barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
     torch.cuda.synchronize()
-    dist.barrier()
+    R.barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step, e2e_step_ms = t[0].item() / args.steps, t[1].item() / args.steps
+    ms_step, e2e_step_ms = [x / args.steps for x in R.reduce_max([ms, e2e_ms])]
+    nccl = nccl_baseline(R, c, layers[0].attn_splits)
+    for l in layers:
+        l.check_status()
+
+    line = None
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        algo = B * S_loc * 72 + B * pages * 4 + B * 16640 + B * (pages // c["blocks_per_chunk"]) * K * 8
-        h2d = hblock.numel()
+        peaks = measured_peaks()
+        phases = layer_algorithmic_bytes(c, layers[0].attn_splits)
+        algo = sum(phases.values())
+        gbs = algo / (ms_step * 1e-3) / 1e9
+        per_phase = {}
+        for name, nbytes in phases.items():
+            t = timeline.get(name)
+            if t:
+                span = max(1e-3, t["last_end_us"] - t["first_start_us"])
+                per_phase[name] = {"algorithmic_bytes": nbytes, "span_us": round(span, 1),
+                                   "gb_per_s": round(nbytes / span / 1e3, 1),
+                                   "frac_of_hbm": round(nbytes / span / 1e3 / peaks["hbm_gbs"], 4)}
         line = {
             "metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp4(e2m1 x ue4m3) x bf16 -> f32; bf16 MLA", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp4(e2m1 x ue4m3) x bf16 -> f32 indexer; bf16 MLA, f32 accumulate",
+            "data": "synthetic",
             "config": {"workload": f"full DSA decode layer-step, CP={world}: B={B}, ctx 131072 sharded token-interleaved "
-                                   f"({S_loc} tokens/rank/seq), indexer + top-k 2048 + sparse MLA (128 heads, 512+64) + LSE merge, "
-                                   "one persistent kernel per rank, P2P stores into symmetric memory",
-                       "l2": f"rotating {c['copies']} cache copies per rank", "parallelism": f"cp{world}"},
+                                   f"({c['S'] // world} tokens/rank/seq), indexer + top-k 2048 + sparse MLA (128 heads, "
+                                   "512+64) + LSE merge, one persistent kernel per rank, P2P stores into symmetric memory",
+                       "l2": f"rotating {c['copies']} cache copies per rank (index cache + KV pool 1.3 GB each > 126 MB L2)",
+                       "parallelism": f"cp{world}", "attn_splits": layers[0].attn_splits},
             "step_us": ms_step * 1e3,
-            "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms},
-            "gpu_launches": args.steps, "timeline_rank0": timeline,
-            "roofline": {"bound": "hbm", "achieved": algo / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": algo / (ms_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
-                         "kernel": "mega_kernel (whole step; indexer bytes only)", "algorithmic_bytes": algo, "traffic": None},
-            "cpu_baseline": None,
+            "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": hblock.numel(),
+                    "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms,
+                    "api": "DsaDecodeLayer.step() with the query block sent from pinned host memory and the owned "
+                           "output rows read back, per rank"},
+            "gpu_launches": args.steps, "kernels_per_step": 1,
+            "parity": parity,
+            "timeline_rank0": timeline, "lse_merge_latency": lse_lat,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "peak_kind": f"of {peaks['kind']}",
+                         "kernel": "mega_kernel (the whole layer-step: a chain of dependent phases)",
+                         "algorithmic_bytes": algo, "traffic": None, "phases": per_phase},
+            "nccl_baseline": nccl,
             "clocks": clk.summary(),
         }
-        print(json.dumps(line))
-    dist.destroy_process_group()
+    return R, line, layers, inputs
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one logits launch, from the
-# ncu capture summarised in profiles/logits_kernel_cfg2.md
+# ----------------------------------------------------------------------------
+# kernels measured alone (N = 1): the source of the roofline blocks
+# ----------------------------------------------------------------------------
+CFG2 = dict(B=32, S=32768, page=64, top_k=2048, q_len=1, copies=4, blocks_per_chunk=128)
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one row-mode indexer launch at BASELINE config 2,
+# from the ncu capture summarised in profiles/logits_row_kernel_cfg2.md
 NCU_TRAFFIC_BYTES = 77_734_400
+
+
+def cfg2_algorithmic_bytes(c) -> int:
+    """Bytes one row-mode indexer launch must move: 72 B per (sequence, token) of NVFP4 index-K,
+    4 B per page-table entry, 16640 B of bf16 query + weights per sequence, 8 B per emitted entry."""
+    B, S, P, K = c["B"], c["S"], c["page"], c["top_k"]
+    return B * S * 72 + B * (S // P) * 4 + B * 16640 + B * K * 8
+
+
+def indexer_alone(args, dev):
+    """BASELINE config 2 (indexer logits + exact top-k 2048, B = 32, context 32768, one row-mode
+    launch) over 4 rotating cache copies (302 MB > L2): kernel time by CUDA events, end to end
+    through the public runner with the per-step tensors sent from pinned host memory."""
+    import torch
+    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+    from mega_dsa_cp_b200.tiles.logits import run_fp4_paged_mqa_logits
+
+    c = CFG2
+    B, S, P, K, T, bpc = c["B"], c["S"], c["page"], c["top_k"], c["q_len"], c["blocks_per_chunk"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    pages_per_seq = S // P
+    pool = B * pages_per_seq
+    caches, tables = [], []
+    for _ in range(c["copies"]):
+        parts = [fuse_pages(torch.randn(pool // 8 * P, 128, generator=g, device=dev), "nvfp4", P)[0] for _ in range(8)]
+        caches.append(torch.cat(parts))
+        del parts
+        tables.append(torch.randperm(pool, generator=g, device=dev).to(torch.int32).reshape(B, pages_per_seq).contiguous())
+    q = torch.randn(B, 64 * T, 128, generator=g, device=dev).to(torch.bfloat16)
+    w = (torch.randn(B, 64 * T, generator=g, device=dev) / 64.0).contiguous()
+    ov = torch.empty(B, T, K, device=dev)
+    oi = torch.empty(B, T, K, dtype=torch.int32, device=dev)
+    oc = torch.empty(B, T, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+
+    def launch(i):
+        r = i % c["copies"]
+        run_fp4_paged_mqa_logits(caches[r], q, None, w, tables[r], None, bpc, top_k=K, fmt="nvfp4",
+                                 page_tokens=P, status=status, row_topk=(ov, oi, oc))
+
+    reps = max(args.steps, 20)
+    for i in range(max(args.warmup, c["copies"])):
+        launch(i)
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for i in range(reps):
+        launch(i)
+    k1.record()
+    torch.cuda.synchronize()
+    ms = k0.elapsed_time(k1) / reps
+    assert status[0].item() == 0 and int(oc.min()) == K, f"device failure {status.tolist()}"
+
+    # end to end: [q | w | page table] in one pinned block down, [ids | counts] in one block back
+    nq, nw, nbt = q.numel() * 2, w.numel() * 4, tables[0].numel() * 4
+    hin = []
+    for r in range(c["copies"]):
+        h = torch.empty(nq + nw + nbt, dtype=torch.uint8).pin_memory()
+        h[:nq].copy_(q.cpu().view(torch.uint8).reshape(-1))
+        h[nq:nq + nw].copy_(w.cpu().view(torch.uint8).reshape(-1))
+        h[nq + nw:].copy_(tables[r].cpu().view(torch.uint8).reshape(-1))
+        hin.append(h)
+    din = torch.empty(nq + nw + nbt, dtype=torch.uint8, device=dev)
+    dq = din[:nq].view(torch.bfloat16).view_as(q)
+    dw = din[nq:nq + nw].view(torch.float32).view_as(w)
+    dbt = din[nq + nw:].view(torch.int32).view_as(tables[0])
+    dout = torch.empty(B * T * K + B * T, dtype=torch.int32, device=dev)
+    e_oi, e_oc = dout[:B * T * K].view(B, T, K), dout[B * T * K:].view(B, T)
+    hout = torch.empty(B * T * K + B * T, dtype=torch.int32).pin_memory()
+
+    def e2e_step(i):
+        r = i % c["copies"]
+        din.copy_(hin[r], non_blocking=True)
+        run_fp4_paged_mqa_logits(caches[r], dq, None, dw, dbt, None, bpc, top_k=K, fmt="nvfp4",
+                                 page_tokens=P, status=status, row_topk=(ov, e_oi, e_oc))
+        hout.copy_(dout, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(max(args.warmup, c["copies"])):
+        e2e_step(i)
+    t0 = time.perf_counter()
+    for i in range(reps):
+        e2e_step(i)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / reps
+    assert status[0].item() == 0 and int(hout[B * T * K:].min()) == K
+    peaks = measured_peaks()
+    algo = cfg2_algorithmic_bytes(c)
+    achieved = algo / (ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "peak_kind": f"of {peaks['kind']}",
+            "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "logits_row_kernel<NVFP4,64,1>",
+            "workload": "BASELINE config 2: B=32, ctx 32768, indexer logits + exact top-k 2048, one launch",
+            "launch_us": ms * 1e3, "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES}
+    extra = {"step_us": ms * 1e3, "tokens_per_s": B * T / (ms * 1e-3), "e2e_step_us": e2e_ms * 1e3,
+             "e2e_tokens_per_s": B * T / (e2e_ms * 1e-3), "h2d_bytes_per_step": hin[0].numel(),
+             "d2h_bytes_per_step": hout.numel() * 4,
+             "l2": f"rotating {c['copies']} cache copies ({c['copies'] * 75.5:.0f} MB > 126 MB L2)"}
+    return roof, extra
+
+
+def mla_alone(args, dev):
+    """The tcgen05 sparse-MLA tile alone: B = 32 queries x 2048 selected rows, 128 heads, bf16
+    576/512, no slot splits; flops = 278528 per selected token against the bf16 burst peak."""
+    import torch
+    from mega_dsa_cp_b200.tiles.hca import run_sparse_mla
+
+    B, H, DQK, K, E = 32, 128, 576, 2048, 1 << 20     # KV pool 1.2 GB > L2
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = (torch.randn(B, 1, H, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    kv = (torch.randn(E, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    pts = [torch.randint(0, E, (B, K), generator=g, device=dev, dtype=torch.int32) for _ in range(4)]
+    kvalid = torch.full((B,), 128 + K, dtype=torch.int32, device=dev)
+    o = torch.empty(B, 1, H, 512, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(B, 1, H, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    run = lambda i: run_sparse_mla(q, None, kv, None, pts[i % 4], o, lse, kvalid, None, None, 1 / math.sqrt(DQK),
+                                   n_splits=1, status=status)
+    reps = max(args.steps, 20)
+    for i in range(4):
+        run(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        run(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    assert status[0].item() == 0
+    peaks = measured_peaks()
+    flops = B * K * 278528
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": tf / peaks["bf16_tflops"], "peak_kind": f"of {peaks['kind']} (burst)", "kernel": "mla_umma_kernel<576>",
+            "workload": "B=32 queries x 2048 selected rows, 128 heads, bf16 576/512, random gather from a 1.2 GB pool",
+            "launch_us": ms * 1e3, "algorithmic_flops": flops, "algorithmic_bytes": B * (K * 1152 + 147456 + 131072),
+            "traffic": None}
 
 
 # ----------------------------------------------------------------------------
 # CPU arm: the oracle port of the same path on the host cores
 # ----------------------------------------------------------------------------
-def cpu_cfg2_once(case, K):
+def cpu_layer_sample(world, max_steps=10, budget_s=20.0):
+    """One sequence of the CP = world layer-step (context 131072, indexer + hierarchical top-k 2048 +
+    sparse MLA + LSE merge) per step through the oracle, on all host cores."""
     import torch
     from oracle import dsa_oracle as orc
 
-    logits = orc.ref_logits(case["q_deq"], case["w"], case["fused"], case["bt"], 1, fmt="nvfp4", page_tokens=64)
-    return torch.topk(logits, K, dim=-1)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))   # torchrun pins OMP_NUM_THREADS=1
+    cc = cp_config(world)
+    S, K, H, DQK = cc["S"], cc["top_k"], cc["H"], cc["d_qk"]
+    g = torch.Generator().manual_seed(0)
+    kd = torch.randn(S, 128, generator=g)
+    data, sf = orc.quant_nvfp4(kd)
+    q_idx = torch.randn(64, 128, generator=g).bfloat16().float()
+    w_idx = torch.randn(64, generator=g) / 64.0
+    q_mla = (torch.randn(H, DQK, generator=g) * 0.5).bfloat16().float()
+    kv = (torch.randn(S, DQK, generator=g) * 0.5).bfloat16().float()
 
+    def once():   # the path reads the quantised cache: the dequantisation is part of a step
+        k = orc.dequant_fp4(data, sf, "nvfp4")
+        return orc.decode_step_ref(q_idx, w_idx, k, q_mla, kv, S, K, 1.0 / math.sqrt(DQK), cp=world)
 
-def cpu_baseline_cfg2(sample_seqs=1, reps=3):
-    import torch
-    from dsa_inputs import indexer_case
-
-    c = CFG2
-    case = indexer_case(sample_seqs, c["S"], c["page"], "nvfp4", seed=0)
-    cpu_cfg2_once(case, c["top_k"])
+    for _ in range(2):
+        once()
     t0 = time.perf_counter()
-    for _ in range(reps):
-        cpu_cfg2_once(case, c["top_k"])
-    dt = (time.perf_counter() - t0) / reps
-    return {"value": sample_seqs / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{sample_seqs} of the 32 sequences of cfg2 (ctx 32768, dequant + 64-head logits + top-k 2048) "
-                      f"per step, {reps} timed steps, torch CPU, {os.cpu_count()} host cpus"}
+    steps = 0
+    while steps < max_steps and (steps < 3 or time.perf_counter() - t0 < budget_s):
+        once()
+        steps += 1
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": 1.0 / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 of the {cc['B']} sequences of the CP={world} layer-step per step (ctx {S}: NVFP4 dequant, "
+                      f"64-head logits, hierarchical top-k {K}, sparse MLA, LSE merge), {steps} timed steps, torch CPU, "
+                      f"{os.cpu_count()} host cpus"}, dt * 1e3, steps
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the path, as restated in oracle/
-    (the reference is pure Python and is not installed on the bench box)."""
-    import torch
-
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference's CPU implementation of the path, as restated in oracle/ (the reference is pure
+    Python + a GPU JIT and is not installed on the bench box).  Rank 0 alone works."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    from dsa_inputs import indexer_case
-
     world = max(args.gpus, int(os.environ.get("WORLD_SIZE", "1")))
-    warm = max(3, min(args.warmup, 3))
-    if world > 1:
-        # the arm's workload at N > 1: the full decode layer-step at CP = N; sample = one sequence per step
-        from oracle import dsa_oracle as orc
-        cc = cp_config(world)
-        S, K, H, DQK = cc["S"], cc["top_k"], cc["H"], cc["d_qk"]
-        g = torch.Generator().manual_seed(0)
-        kd = torch.randn(S, 128, generator=g)
-        data, sf = orc.quant_nvfp4(kd)
-        kd = orc.dequant_fp4(data, sf, "nvfp4")
-        q_idx = torch.randn(64, 128, generator=g).bfloat16().float()
-        w_idx = torch.randn(64, generator=g) / 64.0
-        q_mla = (torch.randn(H, DQK, generator=g) * 0.5).bfloat16()
-        kv = (torch.randn(S, DQK, generator=g) * 0.5).bfloat16()
-        once = lambda: orc.decode_step_ref(q_idx, w_idx, kd, q_mla.float(), kv.float(), S, K, 1.0 / math.sqrt(DQK), cp=world)
-        seqs, steps = 1, min(args.steps, 5)
-        workload = (f"sample on host cores of the full DSA decode layer-step at CP={world}: 1 of the {cc['B']} sequences, "
-                    f"ctx {S}, indexer + top-k {K} + sparse MLA + LSE merge")
-        sample = f"1 of the {cc['B']} sequences per step, {steps} steps"
-    else:
-        c = CFG2
-        seqs = 2
-        case = indexer_case(seqs, c["S"], c["page"], "nvfp4", seed=0)
-        once = lambda: cpu_cfg2_once(case, c["top_k"])
-        steps = min(args.steps, 20)
-        workload = "cfg2 sample on host cores: indexer logits + top-k 2048, ctx 32768"
-        sample = f"{seqs} of the 32 sequences of cfg2 per step, {steps} steps"
-    for _ in range(warm):
-        once()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        once()
-    ms = (time.perf_counter() - t0) * 1e3 / steps
-    val = seqs / (ms * 1e-3)
-    cpu = {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
+    cpu, ms, steps = cpu_layer_sample(world, max_steps=max(3, min(args.steps, 20)), budget_s=60.0)
+    cc = cp_config(world)
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload},
+        "config": {"workload": f"sample on host cores of the full DSA decode layer-step at CP={world}: 1 of the "
+                               f"{cc['B']} sequences per step, ctx {cc['S']}, indexer + top-k {cc['top_k']} + sparse MLA "
+                               "+ LSE merge"},
         "cpu_baseline": cpu,
-        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -608,12 +672,11 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--copies", type=int, default=None, help="rotation copies of the index cache (profiling runs)")
+    ap.add_argument("--copies", type=int, default=None, help="rotation copies of the config-2 index cache (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
-    ap.add_argument("--skip-layer", action="store_true", help="N=1: omit the CP=1 full layer-step leg")
-    ap.add_argument("--two-kernel", action="store_true",
-                    help="N=1: chunk candidates + merge kernel (the reference's two launches) instead of the one-launch row mode")
-    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--skip-alone", action="store_true", help="N=1: omit the kernels-alone legs (indexer, MLA)")
+    ap.add_argument("--only", default=None, choices=["indexer", "mla"],
+                    help="run only one kernel-alone leg and print its block (profiling runs)")
     args = ap.parse_args()
     if args.copies:
         CFG2["copies"] = args.copies
@@ -621,10 +684,33 @@ def main():
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
-        run_gpu_cfg2(args)
-    else:
-        run_gpu_cp(args)
+    if args.only:
+        import torch
+
+        torch.cuda.set_device(0)
+        dev = torch.device("cuda", 0)
+        out = indexer_alone(args, dev) if args.only == "indexer" else mla_alone(args, dev)
+        print(json.dumps(out))
+        return
+    R, line, layers, inputs = run_layer(args)
+    if R.rank == 0:
+        if R.world == 1 and not args.skip_alone:
+            # free the layer-step's caches first: the kernels-alone legs bring their own
+            layers.clear()
+            inputs.clear()
+            import torch
+
+            torch.cuda.empty_cache()
+            layer_roof = line["roofline"]
+            roof, extra = indexer_alone(args, R.dev)
+            line["roofline"] = roof               # the dominant kernel, alone, on BASELINE config 2
+            line["roofline_layer_step"] = layer_roof
+            line["roofline_mla"] = mla_alone(args, R.dev)
+            line["cfg2_indexer"] = extra
+        line["cpu_baseline"] = None if args.skip_cpu else cpu_layer_sample(R.world)[0]
+        print(json.dumps(line), flush=True)
+    R.barrier()
+    R.close()
 
 
 if __name__ == "__main__":

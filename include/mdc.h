@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define MDC_ABI_VERSION 2
+#define MDC_ABI_VERSION 3
 
 /* host-side return codes */
 #define MDC_OK 0
@@ -225,9 +225,13 @@ int mdc_sparse_mla_smem_bytes(const mdc_sparse_mla_params* p);
  * at launch time (all device memory already given to a cache pool; a thread that
  * must not take the allocator's lock).  Capacity: B * q_len * n_splits * H <=
  * MDC_STATIC_WS_MAX_SLOTS, else MDC_ERR_TOO_LARGE and nothing is launched.  The
- * first call on a device looks the block's address up once: make it before any
- * stream capture begins.  One block per device: calls whose kernels may overlap
- * race on it.  Nothing has to be cleared between calls. */
+ * first call on a device is a warm-up: it loads the library's device data segment
+ * (8 MiB + 16 KiB, held until the process exits) and looks the block's address up
+ * once.  Make it at start-up: before the application commits the remaining device
+ * memory to its pool (later it could fail with MDC_ERR_CUDA / out of memory) and
+ * before any stream capture begins.  One block per device: calls whose kernels
+ * may overlap race on it.  Nothing has to be cleared between calls; a call whose
+ * status block comes back non-zero leaves o / lse undefined. */
 #define MDC_STATIC_WS_MAX_SLOTS 4096
 int mdc_sparse_mla_launch_static_ws(const mdc_sparse_mla_params* p, void* stream);
 
@@ -288,8 +292,8 @@ typedef struct {
   float* sel_v;                 /* (B, top_k) merged logits                      */
   int32_t* sel_i;               /* (B, top_k) global ids, identical on every rank */
   int32_t* sel_c;               /* (B,)                                          */
-  void* out;                    /* (B, H, 512) merged attention output (owned rows only) */
-  float* out_lse;               /* (B, H)                                        */
+  void* out;                    /* (ceil(B/cp), H, 512) merged attention output of the owned sequences: row b / cp for b % cp == rank */
+  float* out_lse;               /* (ceil(B/cp), H)                               */
   int32_t out_dtype;            /* MDC_DT_F32 | MDC_DT_BF16                      */
   /* two-level local merge: with l1_groups > 1 MERGE_L1A tasks first merge the chunk lists of one
    * group (ceil(n_chunks / l1_groups) lists each) into mid_*, and MERGE_L1 merges the groups */
@@ -326,8 +330,19 @@ typedef struct {
    * globaltimer ns at task start, after its waits, at its end (after the notifies). */
   unsigned long long* trace;
   int32_t trace_cap;           /* entries                                        */
+  /* Device-side phase counter (docs/event-system.md:32-36 of the reference: "a step counter kept on
+   * the device, +1 per replay", so that a captured CUDA graph replays without host updates).
+   * NULL: the host writes scalars[0] before every launch.  Else one u64, zero at start: every block
+   * counts in after reading scalars[0]; the last one stores scalars[0] + 1 for the next launch and
+   * clears the counter (scalars must then be writable). */
+  unsigned long long* phase_ctl;
 } mdc_mega_params;
 int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
+/* The host-side validation of a launch alone (no GPU needed): the return code mdc_megakernel_launch
+ * would give for these parameters before it touches the device.  With layer.B != 0 it covers the
+ * layer: both tiles' own checks, counts that size on-chip arrays (cp * attn_splits <= 16 LSE
+ * slices, the chunk's scores within the kernel's shared memory), strides and required pointers. */
+int mdc_megakernel_check(const mdc_mega_params* p);
 int mdc_megakernel_smem_bytes(void);
 int mdc_megakernel_threads(void);
 

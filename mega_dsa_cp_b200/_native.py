@@ -12,7 +12,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("MDC_LIB_PATH") or os.path.join(_PKG, "libmdc.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 FMT_MXFP4, FMT_NVFP4 = 0, 1
 Q_FP4, Q_BF16 = 0, 1
 DT_F32, DT_BF16, DT_E4M3 = 0, 1, 2
@@ -89,7 +89,7 @@ class MegaParams(C.Structure):
         ("scopes", p_void), ("n_events", i32), ("events", EventSetC), ("arena", PeerBufferC),
         ("wait_budget_ns", i64), ("status", p_void), ("log", p_void), ("log_cap", i32),
         ("test_off", i64), ("test_slot_bytes", i32), ("layer", LayerParams),
-        ("trace", p_void), ("trace_cap", i32),
+        ("trace", p_void), ("trace_cap", i32), ("phase_ctl", p_void),
     ]
 
 
@@ -142,7 +142,7 @@ EXPORTS = [
     "mdc_logits_fp4_launch", "mdc_logits_fp4_smem_bytes", "mdc_merge_topk_launch",
     "mdc_lse_merge_launch", "mdc_sparse_mla_launch", "mdc_sparse_mla_smem_bytes",
     "mdc_sparse_mla_launch_static_ws",
-    "mdc_megakernel_launch", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
+    "mdc_megakernel_launch", "mdc_megakernel_check", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
     "mdc_compress_step_launch", "mdc_compress_finalize_launch", "mdc_hadamard_quant_launch",
 ]
 

@@ -11,6 +11,13 @@
 //                    the budget ran out (the caller reports and winds down);
 //                    nothing in this library spins without a bound.
 //
+//
+// Payload rule.  A flag-only wait does not fence the whole block at system
+// scope (that costs ~1.7 us per wait).  Payload that a PEER GPU wrote before
+// its notify must therefore be read with the system-scope loads of common.cuh
+// (ld_sys_u4 / ld_sys_f32 / ld_acquire_sys_f4), which bypass the non-coherent
+// L1; payload written by this GPU's own blocks may be read with plain loads.
+//
 // Device counterpart of mega_dsa_cp/events/core.py:40-134 of the reference.
 #pragma once
 

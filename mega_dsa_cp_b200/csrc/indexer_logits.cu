@@ -50,7 +50,7 @@ static int launch_logits(const mdc_logits_params& p, cudaStream_t st, int smem) 
   return MDC_OK;
 }
 
-static int logits_check(const mdc_logits_params* p) {
+int logits_check(const mdc_logits_params* p) {
   if (!p) return MDC_ERR_NULL;
   if (!p->kv_pages || !p->q || !p->weights || !p->block_table) return MDC_ERR_NULL;
   if (p->fmt != MDC_FMT_MXFP4 && p->fmt != MDC_FMT_NVFP4) return MDC_ERR_BAD_FORMAT;
@@ -121,9 +121,3 @@ extern "C" int mdc_logits_fp4_launch(const mdc_logits_params* p, void* stream) {
 int mdc_attrs_logits(cudaFuncAttributes* a) {
   return static_cast<int>(cudaFuncGetAttributes(a, mdc::logits_kernel<MDC_FMT_NVFP4, 64, 1>));
 }
-
-#ifdef MDC_TRACE
-extern "C" int mdc_debug_logits_trace(unsigned long long* host_out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mdc::g_logits_trace, sizeof(mdc::g_logits_trace)));
-}
-#endif

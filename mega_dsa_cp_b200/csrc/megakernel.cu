@@ -29,6 +29,7 @@ constexpr int kMegaTileSmem = MlaUmmaSmem<576>::kTotal > MlaSmem<576>::kTotal ? 
 struct MegaShared {
   int32_t row[kStagedWords];
   int32_t fail;
+  unsigned long long phase;
 };
 
 __device__ inline int64_t phase_offset(const mdc_mega_params& p, unsigned long long phase) {
@@ -180,17 +181,21 @@ __device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, int spl
                       ((static_cast<int64_t>(b / L.cp) * L.cp + L.rank) * ns + split) * inbox_slice_bytes(L);
   unsigned char* slot = arena.peer_ptr(off, owner);
   float* lse_row = reinterpret_cast<float*>(slot + static_cast<int64_t>(L.H) * kMlaDv * 2);
-  if (L.mla.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
-    if (L.mla.d_qk == 576) mla_umma_tile<576>(L.mla, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
-    else mla_umma_tile<512>(L.mla, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
+  // The tiles seed the attention sink in split 0; across ranks exactly one partial may carry it
+  // (the owner's), or the merged denominator would count the sink cp times.
+  mdc_sparse_mla_params mp = L.mla;
+  if (L.rank != owner) mp.attn_sink = nullptr;
+  if (mp.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
+    if (mp.d_qk == 576) mla_umma_tile<576>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
+    else mla_umma_tile<512>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
     return;
   }
   if (threadIdx.x >= kBlockThreads) return;
   const int hb = hbv >> 1, dv0 = (hbv & 1) * 256;
-  if (L.mla.d_qk == 576 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
-  else if (L.mla.d_qk == 512 && L.mla.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
-  else if (L.mla.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
-  else mla_tile<512, MDC_DT_E4M3, 256>(L.mla, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  if (mp.d_qk == 576 && mp.kv_dtype == MDC_DT_BF16) mla_tile<576, MDC_DT_BF16, 256>(mp, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else if (mp.d_qk == 512 && mp.kv_dtype == MDC_DT_BF16) mla_tile<512, MDC_DT_BF16, 256>(mp, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else if (mp.d_qk == 576) mla_tile<576, MDC_DT_E4M3, 256>(mp, b, hb, split, ns, smem, slot, lse_row, dv0, true);
+  else mla_tile<512, MDC_DT_E4M3, 256>(mp, b, hb, split, ns, smem, slot, lse_row, dv0, true);
 }
 
 // owner of sequence b: cp inbox slices -> merged output
@@ -212,8 +217,8 @@ __device__ inline void op_lse_merge(const mdc_mega_params& p, int b, int hq, int
   src.lse_stride = inbox_slice_bytes(L) / 4;
   const int osz = (L.out_dtype == MDC_DT_F32) ? 4 : 2;
   lse_merge_rows<SYS>(src, L.cp * ns, L.H, kMlaDv, MDC_DT_BF16, L.out_dtype,
-                      static_cast<unsigned char*>(L.out) + static_cast<int64_t>(b) * L.H * kMlaDv * osz,
-                      L.out_lse ? L.out_lse + static_cast<int64_t>(b) * L.H : nullptr, h0, n_heads,
+                      static_cast<unsigned char*>(L.out) + static_cast<int64_t>(b / L.cp) * L.H * kMlaDv * osz,
+                      L.out_lse ? L.out_lse + static_cast<int64_t>(b / L.cp) * L.H : nullptr, h0, n_heads,
                       reinterpret_cast<float*>(smem));
 }
 
@@ -271,7 +276,22 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
   cur.scalars = reinterpret_cast<const unsigned long long*>(p.scalars);
   cur.arity = p.arity;
   cur.scopes = p.scopes;
-  cur.phase = cur.scalars[0];
+  // The phase is read once per launch.  With phase_ctl set the kernel advances it by itself: every
+  // block counts in after its read, and the last one to do so (nobody can read after it) stores
+  // phase + 1 for the next launch, so a captured graph replays without a host-side update.
+  if (tid == 0) {
+    const unsigned long long ph = ld_acquire_gpu_u64(cur.scalars);
+    sh.phase = ph;
+    if (p.phase_ctl) {
+      __threadfence();
+      if (atomicAdd(p.phase_ctl, 1ull) + 1ull == static_cast<unsigned long long>(gridDim.x)) {
+        *p.phase_ctl = 0ull;
+        *const_cast<volatile unsigned long long*>(cur.scalars) = ph + 1ull;
+      }
+    }
+  }
+  __syncthreads();
+  cur.phase = sh.phase;
   const EventSet ev{static_cast<unsigned char*>(p.events.base), p.events.offsets, p.events.my_rank, p.events.world};
   const mdc_layer_params& L = p.layer;
 
@@ -296,6 +316,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     if (p.trace && tid == 0) tr1 = global_timer_ns();
 
     // ---- the task body
+    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_MERGE_L1A;
+    if (layer_op && (L.B <= 0 || t.c0 < 0 || t.c0 >= L.B)) {  // no (validated) layer behind this queue
+      if (tid == 0) report_failure(p.status, MDC_DEV_BAD_OP, t.op, t.c0, 0, 0);
+    } else
     switch (t.op) {
       case MDC_OP_NOP:
         break;
@@ -351,10 +375,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     }
 
     // ---- notifies: everything this block wrote is released first
+    // (threads that issued bulk copies have completed them and fenced the async proxy inside the
+    // op; the barrier orders every thread's writes before thread 0's fence, which is cumulative, so
+    // ONE fence releases the whole block's payload: system scope only when a peer is notified)
     if (t.n_notifies > 0) {
-      __threadfence_system();
       __syncthreads();
       if (tid == 0) {
+        bool remote = false;
+        for (int i = 0; i < t.n_notifies; ++i) remote |= (cur.notify_word(t, i) & 0xFF) != ev.my_rank;
+        if (remote) fence_acq_rel_sys();
+        else fence_acq_rel_gpu();
         for (int i = 0; i < t.n_notifies; ++i) {
           const int w = cur.notify_word(t, i);
           const int e = w >> 8, dst = w & 0xFF;
@@ -385,12 +415,58 @@ extern "C" int mdc_megakernel_threads(void) { return mdc::kMegaThreads; }
 
 int mdc_attrs_megakernel(cudaFuncAttributes* a) { return static_cast<int>(cudaFuncGetAttributes(a, mdc::mega_kernel)); }
 
-extern "C" int mdc_megakernel_launch(const mdc_mega_params* p, void* stream) {
+namespace mdc {
+int logits_check(const mdc_logits_params* p);
+int mla_check(const mdc_sparse_mla_params* p);
+
+// Everything a layer op dereferences or sizes shared memory with, checked on the host: a bad
+// configuration comes back as an error code, it never reaches the device.  B == 0 means "no
+// layer" (test queues); the kernel then refuses layer ops.
+static int layer_check(const mdc_mega_params& p) {
+  const mdc_layer_params& L = p.layer;
+  if (L.B == 0) return MDC_OK;
+  if (L.B < 0 || L.cp < 1 || L.rank < 0 || L.rank >= L.cp || L.top_k < 1 || L.n_chunks < 1) return MDC_ERR_BAD_SHAPE;
+  if (L.cp != p.arena.world || L.rank != p.arena.my_rank || L.cp != p.events.world) return MDC_ERR_BAD_SHAPE;
+  if (!p.arena.base || !p.arena.offsets) return MDC_ERR_NULL;
+  int rc = logits_check(&L.logits);
+  if (rc != MDC_OK) return rc;
+  rc = mla_check(&L.mla);
+  if (rc != MDC_OK) return rc;
+  if (!L.logits.cand_v || L.logits.row_v || L.logits.q_len != 1 || L.mla.q_len != 1) return MDC_ERR_BAD_SHAPE;
+  if (L.logits.B != L.B || L.mla.B != L.B || L.logits.top_k != L.top_k || L.logits.n_chunks != L.n_chunks)
+    return MDC_ERR_BAD_SHAPE;
+  if (L.H != L.mla.H || L.H % 64 != 0 || L.mla.n_splits != 1) return MDC_ERR_BAD_SHAPE;
+  if ((L.top_k * 8 + 16) % 16 != 0) return MDC_ERR_BAD_ALIGN;  // candidate slices travel as 16-byte bulk copies
+  if (L.mla.pt_cols < 1 || L.kv_seq_stride < 1 || L.phases < 1 || L.phase_bytes < 0) return MDC_ERR_BAD_SHAPE;
+  if (!L.sel_v || !L.sel_i || !L.sel_c || !L.out) return MDC_ERR_NULL;
+  if (L.out_dtype != MDC_DT_F32 && L.out_dtype != MDC_DT_BF16) return MDC_ERR_BAD_FORMAT;
+  if (L.l1_groups > 1 && (!L.mid_v || !L.mid_i || !L.mid_c)) return MDC_ERR_NULL;
+  if (L.l1_groups < 0 || L.l1_groups > L.n_chunks) return MDC_ERR_BAD_SHAPE;
+  if (static_cast<long long>(L.cp) * (L.attn_splits > 1 ? L.attn_splits : 1) > kLseMaxSlices) return MDC_ERR_TOO_LARGE;
+  // the chunk's scores stay in shared memory: the tile's layout must fit the kernel's allocation
+  const int ct = L.logits.blocks_per_chunk * L.logits.page_tokens;
+  int need;
+  if (L.logits.fmt == MDC_FMT_MXFP4) need = logits_smem_layout<MDC_FMT_MXFP4, 128>(1, ct, true).total;
+  else if (L.logits.page_tokens == 64) need = logits_smem_layout<MDC_FMT_NVFP4, 64>(1, ct, true).total;
+  else need = logits_smem_layout<MDC_FMT_NVFP4, 128>(1, ct, true).total;
+  if (need > kMegaTileSmem) return MDC_ERR_TOO_LARGE;
+  return MDC_OK;
+}
+}  // namespace mdc
+
+extern "C" int mdc_megakernel_check(const mdc_mega_params* p) {
   using namespace mdc;
   if (!p || !p->queue || !p->scalars || !p->arity || !p->scopes || !p->events.base || !p->events.offsets)
     return MDC_ERR_NULL;
   if (p->n_ctas < 1 || p->row_words < 1 || p->n_events < 0) return MDC_ERR_BAD_SHAPE;
   if (p->wait_budget_ns <= 0) return MDC_ERR_BAD_SHAPE;
+  return layer_check(*p);
+}
+
+extern "C" int mdc_megakernel_launch(const mdc_mega_params* p, void* stream) {
+  using namespace mdc;
+  const int rc = mdc_megakernel_check(p);
+  if (rc != MDC_OK) return rc;
   const int smem = mdc_megakernel_smem_bytes();
   MDC_CUDA_OK(cudaFuncSetAttribute(mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   // the blocks wait on each other: all of them must be resident at once

@@ -1,7 +1,5 @@
 // Launch wrapper of the sparse-MLA tile (see tile_mla.cuh) and of the split
 // combine that follows it when the slot range is split.
-#include <cstdlib>
-
 #include "tile_mla.cuh"
 #include "tile_mla_umma.cuh"
 #include "tile_lse_merge.cuh"
@@ -42,8 +40,7 @@ static int launch_mla_umma(const mdc_sparse_mla_params& p, cudaStream_t st) {
 
 // The tensor-memory path takes bf16 operands with heads in blocks of 128 and exact (unrounded) probabilities.
 static bool mla_use_umma(const mdc_sparse_mla_params& p) {
-  static const bool legacy = std::getenv("MDC_MLA_LEGACY") != nullptr;  // A/B switch for measurements
-  return !legacy && p.kv_dtype == MDC_DT_BF16 && p.H % kMuHeads == 0 && p.fp8_p == 0;
+  return p.kv_dtype == MDC_DT_BF16 && p.H % kMuHeads == 0 && p.fp8_p == 0;
 }
 
 template <int DQK, int KVDT>
@@ -57,7 +54,7 @@ static int launch_mla(const mdc_sparse_mla_params& p, cudaStream_t st) {
   return MDC_OK;
 }
 
-static int mla_check(const mdc_sparse_mla_params* p) {
+int mla_check(const mdc_sparse_mla_params* p) {
   if (!p || !p->q || !p->kv_cmp || !p->pt_cmp || !p->k_valid || !p->o) return MDC_ERR_NULL;
   if (p->B < 1 || p->q_len < 1 || p->H < kMlaHeads || p->H % kMlaHeads) return MDC_ERR_BAD_SHAPE;
   if (p->d_v != kMlaDv || (p->d_qk != 576 && p->d_qk != 512)) return MDC_ERR_BAD_SHAPE;
@@ -84,6 +81,8 @@ static int mla_check(const mdc_sparse_mla_params* p) {
 extern "C" int mdc_sparse_mla_smem_bytes(const mdc_sparse_mla_params* p) {
   int rc = mdc::mla_check(p);
   if (rc != MDC_OK) return rc;
+  if (mdc::mla_use_umma(*p))  // the tile the launch will take (+ slack for its 1024-byte aligned base)
+    return (p->d_qk == 576 ? mdc::MlaUmmaSmem<576>::kTotal : mdc::MlaUmmaSmem<512>::kTotal) + 1024;
   return p->d_qk == 576 ? mdc::MlaSmem<576>::kTotal : mdc::MlaSmem<512>::kTotal;
 }
 
@@ -118,9 +117,3 @@ extern "C" int mdc_sparse_mla_launch(const mdc_sparse_mla_params* p, void* strea
 int mdc_attrs_sparse_mla(cudaFuncAttributes* a) {
   return static_cast<int>(cudaFuncGetAttributes(a, mdc::mla_kernel<576, MDC_DT_BF16>));
 }
-
-#ifdef MDC_TRACE
-extern "C" int mdc_debug_mla_trace(long long* host_out) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, mdc::g_mla_trace, sizeof(mdc::g_mla_trace)));
-}
-#endif

@@ -7,21 +7,31 @@
 // to the allocator, or a decode step that runs on a latency-critical thread
 // where entering the allocator (a lock, possibly a device synchronisation) is
 // not acceptable.  For them this file keeps a fixed scratch block in the
-// module's own device data segment: it exists as soon as the library is
-// loaded on a device, so the entry point below never calls an allocating
-// routine -- no cudaMalloc / cudaFree, no pool, no framework tensor.
+// module's own device data segment, so the entry point below never calls an
+// allocating routine -- no cudaMalloc / cudaFree, no pool, no framework tensor.
+// The block is part of the library image: under CUDA's default lazy module
+// loading its backing store (8 MiB + 16 KiB) is claimed when the FIRST call on
+// a device looks the symbol up, and stays claimed until the process exits.
+// Make that first call at start-up, before the application hands the rest of
+// device memory to its pool: afterwards it could fail with an out-of-memory
+// CUDA error (returned as MDC_ERR_CUDA), and later calls never touch the
+// allocator again.
 //
 // Limits and rules:
 //   * capacity: B * q_len * n_splits * H <= MDC_STATIC_WS_MAX_SLOTS (4096
 //     partial rows of 512 fp32 = 8 MiB, plus 16 KiB of LSEs); larger requests
 //     are rejected with MDC_ERR_TOO_LARGE and nothing is launched.
-//   * the first call on a device looks up the scratch address once (with that
-//     device current) and caches it; make that first call before any stream
-//     capture is begun, because the lookup is not a stream operation.
+//   * the first call on a device is a warm-up: it loads the data segment and
+//     looks up the scratch address once (with that device current), then
+//     caches it.  Make it before any stream capture is begun -- the lookup is
+//     not a stream operation -- and before memory gets tight (see above).
 //   * nothing in the scratch has to start at zero: every (row, split, head)
 //     slot that the combine kernel reads is written first by the attention
 //     kernel of the same call, including the slots of empty splits (sum 0,
 //     LSE -inf).  So the block is never cleared.
+//   * a call whose status block comes back non-zero (a device-side give-up)
+//     leaves `o` / `lse` undefined: the combine may have merged partials of an
+//     earlier call that the aborted splits did not overwrite.
 //   * there is ONE block per device: two calls whose kernels can overlap (two
 //     streams, two host threads on the same device) race on it.  Serialise
 //     them on one stream, or use mdc_sparse_mla_launch with separate

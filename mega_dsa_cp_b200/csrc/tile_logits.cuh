@@ -62,18 +62,6 @@
 
 namespace mdc {
 
-#ifdef MDC_TRACE
-// Debug builds only: SM-clock timestamps of block (0,0), [role][tile][point].
-__device__ long long g_logits_trace[4 * 256 * 8];
-#define MDC_TRACE_AT(role, tile, point)                                                        \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 256)                                    \
-      g_logits_trace[((role) * 256 + (tile)) * 8 + (point)] = clock64();                       \
-  } while (0)
-#else
-#define MDC_TRACE_AT(role, tile, point) do { } while (0)
-#endif
-
 constexpr int kIdxDim = 128;
 constexpr int kIdxHeads = 64;
 constexpr int kTileTok = 128;    // tokens per pipeline stage (= UMMA M)
@@ -487,7 +475,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       if (ready) {
         const int i0 = tile * PG::kTilePages;
         if (pp == 0) {
-          MDC_TRACE_AT(0, tile, 0);
           uint32_t bytes = 0;
 #pragma unroll
           for (int k = 0; k < PG::kTilePages; ++k) bytes += page_id[i0 + k] >= 0 ? PG::kBytes : 0;
@@ -499,7 +486,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
           bulk_g2s(ring + s * PG::kStageBytes + pp * PG::kBytes, p.kv_pages + static_cast<int64_t>(id) * PG::kBytes,
                    PG::kBytes, &raw_full[s]);
         }
-        if (pp == 0) MDC_TRACE_AT(0, tile, 1);
         tile += kRawStages;
       }
       if (__any_sync(0xffffffffu, ready)) {
@@ -522,11 +508,9 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     for (int kk = 0; kk < 8; ++kk) bdesc[kk] = umma::smem_desc_sw128(qb_u + (kk >> 2) * (N * 128) + (kk & 3) * 32);
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int a = tile % kASt, c = tile % kAccSt;
-      if (lane == 0) MDC_TRACE_AT(2, tile, 0);
       // progress counters instead of mbarriers here: an mbarrier wait costs this
       // thread ~150 cycles even when the phase is long complete
       bool ok = counter_wait(&a_cnt[a], 4u * (tile / kASt + 1), kBudget, abort_flag);
-      if (lane == 0) MDC_TRACE_AT(2, tile, 1);
       if (ok && tile >= kAccSt) ok = counter_wait(&acc_cnt[c], 4u * (tile / kAccSt), kBudget, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) give_up(1, tile);
@@ -534,10 +518,8 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       }
       umma::fence_after_sync();
       if (umma::elect_one()) {
-        MDC_TRACE_AT(2, tile, 2);
         umma::mma_f16_ts_x8(tmem + kAccBase + c * N, tmem + kABase + a * 64, bdesc, idesc);
         umma::commit(&mma_done[a]);
-        MDC_TRACE_AT(2, tile, 3);
       }
       __syncwarp();
     }
@@ -552,12 +534,10 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     bool raw_ok = false, a_ok = true;
     for (int tile = grp; tile < n_tiles; tile += DG) {
       const int s = tile % kRawStages, a = tile % kASt;
-      if (tid == 0) MDC_TRACE_AT(1, tile, 0);
       if (!raw_ok && !mbar_wait(&raw_full[s], (tile / kRawStages) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(3, tile);
         break;
       }
-      if (tid == 0) MDC_TRACE_AT(1, tile, 1);
       const unsigned char* pg = ring + s * PG::kStageBytes + pp * PG::kBytes;
       const bool ok = page_id[tile * PG::kTilePages + pp] >= 0;
       uint4 d[4];
@@ -581,11 +561,9 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         break;
       }
       umma::fence_after_sync();
-      if (tid == 0) MDC_TRACE_AT(1, tile, 2);
       // the raw stage is in registers: hand it back to the copy warp
       __syncwarp();
       mbar_arrive_if(&raw_empty[s], lane == 0);
-      if (tid == 0) MDC_TRACE_AT(1, tile, 3);
       // undo the rotation in registers (the tensor-memory store takes one column address per
       // warp, so chunk k has to sit in the same register of every lane): two select stages
       if (rot & 1) {
@@ -618,14 +596,12 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         }
         umma::tmem_st16(t_row + a * 64 + 16 * j, out);
       }
-      if (tid == 0) MDC_TRACE_AT(1, tile, 4);
       // publish the stage as soon as the stores have landed: the tensor core works on it while
       // this group decodes its next stage into another A stage
       umma::wait_st();
       umma::fence_before_sync();
       __syncwarp();
       red_release_cta_shared_inc_if(&a_cnt[a], lane == 0);
-      if (tid == 0) MDC_TRACE_AT(1, tile, 5);
       raw_ok = n_raw;
       a_ok = n_a;
     }
@@ -636,13 +612,11 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     bool done_ok = false;
     for (int tile = gg; tile < n_tiles; tile += GG) {
       const int c = tile % kAccSt;
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 0);
       if (!done_ok && !mbar_wait(&mma_done[tile % kASt], (tile / kASt) & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(5, tile);
         break;
       }
       umma::fence_after_sync();
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 1);
       const int nt = tile + GG;
       bool n_done = false;
       if (nt < n_tiles) n_done = mbar_test(&mma_done[nt % kASt], (nt / kASt) & 1);
@@ -654,11 +628,9 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         umma::tmem_ld32(t_base + c * N + t * kIdxHeads + 32, v1);
         umma::wait_ld();
         if (t == T - 1) {  // the row is in registers: the accumulator stage can be overwritten
-          if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 2);
           umma::fence_before_sync();
           __syncwarp();
           red_release_cta_shared_inc_if(&acc_cnt[c], lane == 0);
-          if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 3);
         }
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         const float4* w4 = reinterpret_cast<const float4*>(wsc + t * kIdxHeads);
@@ -687,7 +659,6 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
           }
         }
       }
-      if (q == 0 && lane == 0) MDC_TRACE_AT(3, tile, 4);
       done_ok = n_done;
     }
   }

@@ -28,13 +28,6 @@
 
 namespace mdc {
 
-#ifdef MDC_TRACE
-__device__ long long g_mla_trace[4 * 64 * 8];
-#define MLA_TRACE(role, tile, point) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 64) g_mla_trace[((role) * 64 + (tile)) * 8 + (point)] = clock64(); } while (0)
-#else
-#define MLA_TRACE(role, tile, point) do { } while (0)
-#endif
-
 constexpr int kMuHeads = 128;   // heads per block (= UMMA M)
 constexpr int kMuTile = 64;     // slots per tile
 constexpr int kMuDv = 128;      // output columns per block
@@ -214,14 +207,12 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     }
     bool ok = true;
     for (int i = 0; i < n_my; ++i) {
-      if (tid == 0) MLA_TRACE(0, i, 0);
       if (!mbar_wait(s_ready, i & 1, kBudget, abort_flag)) {
         if (lane == 0) give_up(0, i);
         ok = false;
         break;
       }
       umma::fence_after_sync();
-      if (tid == 0) MLA_TRACE(0, i, 1);
       float sv[kMuTile];
       {
         float a[32], b[32];
@@ -234,7 +225,6 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           sv[32 + j] = b[j];
         }
       }
-      if (tid == 0) MLA_TRACE(0, i, 2);
       const uint2 vb = *reinterpret_cast<const uint2*>(validb + (i % S) * 8);
       // (one warp per scheduler: dependent chains are what costs here, so the maximum and the sum
       // run on four independent accumulators and a full tile skips the masking)
@@ -303,12 +293,10 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         umma::tmem_st16(t_lane + kPCol, lo);
         umma::tmem_st16(t_lane + kPCol + 16, hi);
       }
-      if (tid == 0) MLA_TRACE(0, i, 3);
       umma::wait_st();
       umma::fence_before_sync();
       __syncwarp();
       mbar_arrive_if(p_ready, lane == 0);
-      if (tid == 0) MLA_TRACE(0, i, 4);
     }
     if (ok && n_my > 0 && !mbar_wait(o_final, 0, kBudget, abort_flag)) {
       if (lane == 0) give_up(1, n_my);
@@ -424,7 +412,6 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
                                          : nullptr;
     for (int i = 0; i < n_my && ok; ++i) {
       const int st = i % S;
-      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 0);
       if (i >= S) {
         const uint32_t par = ((i / S) - 1) & 1;
         if (!__all_sync(0xffffffffu, mbar_test(&free_[st], par))) {
@@ -442,12 +429,10 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       const uint32_t bits = mla_umma_gather_rows<DQK>(p, mine, kst + st * SM::kStageBytes, gw, lane);
       if (i + 1 < n_my) mine = mla_umma_row_ptr<DQK>(p, r, (t_begin + i + 1) * kMuTile, k_valid, win_valid, gw, lane);
       if (lane == 0) validb[st * 8 + gw] = static_cast<unsigned char>(bits);
-      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 2);
       if (i - done >= 1) {  // at most two tiles in flight per warp
         cp_async_wait<1>();
         publish(i);
       }
-      if (gw == 0 && lane == 0) MLA_TRACE(2, i, 3);
     }
     cp_async_wait<0>();
     if (ok && n_my > 0) publish(n_my);
@@ -468,11 +453,8 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       umma::commit(&free_[i % S]);
     };
     for (int i = 0; i < n_my && ok; ++i) {
-      if (lane == 0) MLA_TRACE(1, i, 0);
       ok = mbar_wait(&full[i % S], (i / S) & 1, kBudget, abort_flag);
-      if (lane == 0) MLA_TRACE(1, i, 1);
       if (ok && i > 0) ok = mbar_wait(p_ready, (i - 1) & 1, kBudget, abort_flag);
-      if (lane == 0) MLA_TRACE(1, i, 2);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) give_up(4, i);
         ok = false;
@@ -488,7 +470,6 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
           umma::mma_f16_ts(tmem + kSCol, tmem + 8 * k, bdesc, idesc_qk, k > 0);
         }
         umma::commit(s_ready);
-        MLA_TRACE(1, i, 3);
       }
       __syncwarp();
     }

@@ -133,6 +133,10 @@ class DsaDecodeLayer:
             tiles = -(-(top_k // cp + 128) // 64)
             attn_splits = max(1, min(tiles // 4, n_ctas // max(1, B * 4 * (heads // 128 or 1)), 16 // cp))
         self.attn_splits = attn_splits
+        # what the launcher's own check would refuse, refused here with a readable message
+        assert heads % 64 == 0 and top_k % 2 == 0, "heads must be a multiple of 64, top_k even"
+        assert cp * attn_splits <= 16, f"cp * attn_splits = {cp * attn_splits} exceeds the 16 slices the LSE merge takes"
+        assert 0 <= rank < cp
         self.l1_groups = l1_groups_for(self.n_chunks)
         tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups)
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
@@ -153,8 +157,9 @@ class DsaDecodeLayer:
         self.sel_c = torch.zeros(B, dtype=torch.int32, device=dev)
         self.pt_local = torch.zeros(B, K, dtype=torch.int32, device=dev)
         self.k_valid = torch.zeros(B, dtype=torch.int32, device=dev)
-        self.out = torch.zeros(B, heads, D_V, dtype=out_dtype, device=dev)
-        self.out_lse = torch.zeros(B, heads, device=dev)
+        n_owned = -(-B // cp)   # the merged rows of the sequences this rank owns (b % cp == rank), at row b // cp
+        self.out = torch.zeros(n_owned, heads, D_V, dtype=out_dtype, device=dev)
+        self.out_lse = torch.zeros(n_owned, heads, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32, device=dev)
         self.phase = 0
         self._params = None
@@ -194,14 +199,16 @@ class DsaDecodeLayer:
         self._params, self._inputs = L, x
 
     def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None) -> None:
-        """Launches one layer-step (asynchronous).  Every rank must call it with the same phase."""
+        """Launches one layer-step (asynchronous): exactly one kernel launch, nothing else.  The
+        phase lives on the device and the kernel advances it, so a step can be captured in a CUDA
+        graph and replayed.  Every rank must run the same number of steps."""
         assert self._params is not None, "bind() inputs first"
-        self.dsched.scalars[0:1].fill_(self.phase)
         launch_megakernel(self.dsched, self.events, self.arena, self.status, layer=self._params,
-                          wait_budget_ns=wait_budget_ns, stream=stream, trace=trace)
-        self.phase += 1
+                          wait_budget_ns=wait_budget_ns, stream=stream, trace=trace, device_phase=True)
+        self.phase += 1   # host mirror, for reporting only
 
     def owned_rows(self):
+        """Sequences whose merged output this rank holds; sequence b is row b // cp of `out`."""
         return [b for b in range(self.B) if b % self.cp == self.rank]
 
     def check_status(self) -> None:

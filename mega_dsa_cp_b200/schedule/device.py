@@ -27,6 +27,7 @@ class DeviceSchedule:
     arity: torch.Tensor     # int32 (n_events,)
     scopes: torch.Tensor    # int32 (n_events,)
     scalars: torch.Tensor   # int64: [0] phase, [1:] dynamic extents
+    phase_ctl: torch.Tensor  # int64 (1,): arrival counter of the device-side phase bump
     n_ctas: int
     row_words: int
     n_events: int
@@ -40,6 +41,7 @@ def upload_schedule(schedule: Schedule, device="cuda", n_scalars: int = 8) -> De
         queue=torch.tensor(flat, dtype=torch.int32, device=device).view(n_ctas, row),
         arity=i32(schedule.arity), scopes=i32(schedule.scopes),
         scalars=torch.zeros(n_scalars, dtype=torch.int64, device=device),
+        phase_ctl=torch.zeros(1, dtype=torch.int64, device=device),
         n_ctas=n_ctas, row_words=row, n_events=schedule.n_events,
     )
 
@@ -47,9 +49,12 @@ def upload_schedule(schedule: Schedule, device="cuda", n_scalars: int = 8) -> De
 def launch_megakernel(ds: DeviceSchedule, events: EventBuffer, arena: SymmetricArena | None, status: torch.Tensor,
                       layer: N.LayerParams | None = None, log: torch.Tensor | None = None,
                       wait_budget_ns: int = 2_000_000_000, test_off: int = 0, test_slot_bytes: int = 0,
-                      stream=None, trace: torch.Tensor | None = None) -> None:
+                      stream=None, trace: torch.Tensor | None = None, device_phase: bool = False) -> None:
     """One launch of the persistent kernel on this rank (asynchronous).  `trace`: optional int64
-    tensor of 4 + 4 * entries words that receives the task timeline (word 0 = entry count)."""
+    tensor of 4 + 4 * entries words that receives the task timeline (word 0 = entry count).
+    `device_phase`: the kernel itself advances scalars[0] after every block has read it (the
+    reference's device-side step counter, docs/event-system.md:32-36), so the same launch can be
+    replayed, also from a captured CUDA graph, with no host write in between."""
     p = N.MegaParams()
     p.queue, p.row_words, p.n_ctas = N.ptr(ds.queue), ds.row_words, ds.n_ctas
     p.scalars, p.arity, p.scopes, p.n_events = N.ptr(ds.scalars), N.ptr(ds.arity), N.ptr(ds.scopes), ds.n_events
@@ -68,4 +73,5 @@ def launch_megakernel(ds: DeviceSchedule, events: EventBuffer, arena: SymmetricA
         p.layer = layer
     p.trace = N.ptr(trace)
     p.trace_cap = 0 if trace is None else (trace.numel() - 4) // 4
+    p.phase_ctl = N.ptr(ds.phase_ctl) if device_phase else None
     N.call("mdc_megakernel_launch", p, stream)

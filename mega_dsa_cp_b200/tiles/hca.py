@@ -14,25 +14,25 @@ from .. import _native as N
 
 H = 128
 D = 512
-_SM_COUNT = 148
-_ws_cache: dict = {}
+STATIC_WS_MAX_SLOTS = 4096   # MDC_STATIC_WS_MAX_SLOTS of include/mdc.h
 
 
-def _workspace(device, rows: int, splits: int, heads: int):
-    key = (device, rows, splits, heads)
-    if key not in _ws_cache:
-        _ws_cache[key] = (
-            torch.empty(rows, splits, heads, D, dtype=torch.float32, device=device),
-            torch.empty(rows, splits, heads, dtype=torch.float32, device=device),
-        )
-    return _ws_cache[key]
+def sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
 
 
-def pick_splits(rows: int, heads: int, slots: int) -> int:
+def pick_splits(rows: int, heads: int, slots: int, sms: int) -> int:
     """KV splits so that rows * heads/64 * splits blocks roughly fill the SMs."""
     blocks = rows * (heads // 64)
     tiles = max(1, (slots + 63) // 64)
-    return int(max(1, min(16, tiles, _SM_COUNT // max(1, blocks))))
+    return int(max(1, min(16, tiles, sms // max(1, blocks))))
+
+
+def split_workspace(rows: int, n_splits: int, heads: int, device):
+    """The fp32 workspace a split launch needs: (rows, n_splits, heads, 512) partial outputs and
+    (rows, n_splits, heads) log2-LSEs.  The caller allocates it once and passes it to every call."""
+    return (torch.empty(rows, n_splits, heads, D, dtype=torch.float32, device=device),
+            torch.empty(rows, n_splits, heads, dtype=torch.float32, device=device))
 
 
 def run_sparse_mla(
@@ -52,7 +52,12 @@ def run_sparse_mla(
     fp8_p: bool = False,
     status: torch.Tensor | None = None,
     stream=None,
+    workspace: tuple | None = None,   # split_workspace(...) owned by the caller
 ) -> None:
+    """Nothing is allocated here.  A split launch writes its partials into `workspace` when the
+    caller passes one, else into the library's fixed device block (mdc_sparse_mla_launch_static_ws:
+    rows * n_splits * heads <= 4096, one call at a time per device); the split count is lowered
+    to what that block holds."""
     B, T, heads, d_qk = q.shape
     rows = B * T
     kv_dt = N.DT_E4M3 if q.dtype == torch.float8_e4m3fn else N.DT_BF16
@@ -60,13 +65,20 @@ def run_sparse_mla(
     o2 = o.view(rows, heads, o.shape[-1]) if o.dim() == 4 else o
     assert o2.stride(2) == 1 and o2.stride(1) == o2.shape[2]
     if n_splits is None:
-        n_splits = pick_splits(rows, heads, pt_cmp.shape[1] * kv_cmp.shape[1] + 128)
+        n_splits = pick_splits(rows, heads, pt_cmp.shape[1] * kv_cmp.shape[1] + 128, sm_count(q.device))
     contiguous_out = o2.stride(0) == heads * o2.shape[2] and (lse is None or lse.is_contiguous())
     if not contiguous_out:
         n_splits = 1
     ws_o = ws_l = None
-    if n_splits > 1:
-        ws_o, ws_l = _workspace(q.device, rows, n_splits, heads)
+    entry = "mdc_sparse_mla_launch"
+    if n_splits > 1 and workspace is not None:
+        ws_o, ws_l = workspace
+        assert ws_o.dtype == torch.float32 and ws_o.numel() >= rows * n_splits * heads * D
+        assert ws_l.dtype == torch.float32 and ws_l.numel() >= rows * n_splits * heads
+    elif n_splits > 1:
+        n_splits = max(1, min(n_splits, STATIC_WS_MAX_SLOTS // (rows * heads)))
+        if n_splits > 1:
+            entry = "mdc_sparse_mla_launch_static_ws"
     p = N.SparseMlaParams(
         q=N.ptr(q), kv_win=N.ptr(kv_win), kv_cmp=N.ptr(kv_cmp), pt_win=N.ptr(pt_win), pt_cmp=N.ptr(pt_cmp),
         k_valid=N.ptr(k_valid), win_valid=N.ptr(win_valid), attn_sink=N.ptr(attn_sink),
@@ -79,7 +91,7 @@ def run_sparse_mla(
         n_splits=n_splits, fp8_p=int(fp8_p), softmax_scale=softmax_scale, output_scale=output_scale,
         status=N.ptr(status),
     )
-    N.call("mdc_sparse_mla_launch", p, stream)
+    N.call(entry, p, stream)
 
 
 def run_hca_fp8(

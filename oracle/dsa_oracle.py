@@ -534,14 +534,11 @@ def shard_tokens(x: torch.Tensor, cp: int, rank: int) -> torch.Tensor:
     return x[rank::cp]
 
 
-def decode_step_ref(q_idx, w_idx, k_idx_deq, q_mla, kv_mla, seq_len: int, top_k: int,
-                    softmax_scale: float, cp: int = 1, d_v: int = 512):
-    """One sequence, one query token.  q_idx (64,128), w_idx (64,), k_idx_deq
-    (S,128) dequantised index keys, q_mla (H,Dqk), kv_mla (S,Dqk).
-    Returns (selected global ids (sorted ascending), o (H,d_v), lse (H,)) where the
-    selection is the exact global top-k of the logits under (v desc, id asc),
-    computed hierarchically (per-rank top-k then merge) and the attention is
-    computed per rank over its share of the selection and merged by LSE."""
+def select_topk_ref(q_idx, w_idx, k_idx_deq, seq_len: int, top_k: int, cp: int = 1):
+    """Selection of one sequence, one query token: the exact global top-k of the indexer logits
+    under (v desc, id asc), computed hierarchically (per-rank top-k of the token-interleaved
+    shards, then the merge), in the merge's emit order.  q_idx (64,128), w_idx (64,), k_idx_deq
+    (S,128) dequantised index keys."""
     S = seq_len
     logits = ((q_idx @ k_idx_deq[:S].T).clamp(min=0) * w_idx[:, None]).sum(dim=0)
     cand_v, cand_i = [], []
@@ -558,13 +555,39 @@ def decode_step_ref(q_idx, w_idx, k_idx_deq, q_mla, kv_mla, seq_len: int, top_k:
         n = cand_v[r].numel()
         cv[0, 0, r, :n], ci[0, 0, r, :n], cc[0, 0, r] = cand_v[r], cand_i[r], n
     _, sel_i, sel_c = merge_topk_ref(cv, ci, cc, top_k)
-    sel = sel_i[0, 0, :int(sel_c[0, 0])].long()
+    return sel_i[0, 0, :int(sel_c[0, 0])].long()
+
+
+def decode_step_ref(q_idx, w_idx, k_idx_deq, q_mla, kv_mla, seq_len: int, top_k: int,
+                    softmax_scale: float, cp: int = 1, d_v: int = 512):
+    """One sequence, one query token.  q_idx (64,128), w_idx (64,), k_idx_deq
+    (S,128) dequantised index keys, q_mla (H,Dqk), kv_mla (S,Dqk).
+    Returns (selected global ids (sorted ascending), o (H,d_v), lse (H,)) where the
+    selection is select_topk_ref's and the attention is computed per rank over its
+    share of the selection and merged by LSE."""
+    sel = select_topk_ref(q_idx, w_idx, k_idx_deq, seq_len, top_k, cp)
+    o, l = attend_selected_ref(q_mla, kv_mla, sel, softmax_scale, cp=cp, d_v=d_v)
+    return torch.sort(sel).values, o, l
+
+
+def attend_selected_ref(q_mla, kv_mla, sel, softmax_scale: float, cp: int = 1, d_v: int = 512,
+                        rows_are_selected: bool = False):
+    """Sparse attention of one query token over the GIVEN global token ids `sel`
+    (any order), computed the context-parallel way: rank r attends over the ids
+    with id % cp == r in the order given, the cp partials are merged by LSE.
+    q_mla (H,Dqk); kv_mla (S,Dqk) indexed by id, or with rows_are_selected one row
+    per entry of sel (row j = the KV row of sel[j]).  Returns (o (H,d_v), log2-LSE
+    (H,)).  Lets a test hold a kernel's attention to the oracle on the kernel's
+    own selection."""
+    sel = sel.long()
     H = q_mla.shape[0]
     acc_o = torch.zeros(1, 1, cp, H, d_v)
     acc_l = torch.full((1, 1, cp, H), -math.inf)
     sink = torch.full((H,), -math.inf)
+    where = torch.arange(sel.numel())
     for r in range(cp):
-        mine = sel[sel % cp == r]
+        m = sel % cp == r
+        mine = where[m] if rows_are_selected else sel[m]
         n = mine.numel()
         pt = torch.zeros(1, max(n, 1), dtype=torch.int32)
         pt[0, :n] = mine.to(torch.int32)
@@ -573,4 +596,4 @@ def decode_step_ref(q_idx, w_idx, k_idx_deq, q_mla, kv_mla, seq_len: int, top_k:
                        softmax_scale, d_v=d_v)
         acc_o[0, 0, r], acc_l[0, 0, r] = o[0, 0], l[0, 0]
     o, l = lse_merge_ref(acc_o, acc_l, cp)
-    return torch.sort(sel).values, o[0, 0], l[0, 0]
+    return o[0, 0], l[0, 0]

@@ -56,6 +56,70 @@ def test_launchers_reject_bad_arguments_without_a_gpu():
     assert lib.mdc_megakernel_threads() in (448, 480) and lib.mdc_megakernel_smem_bytes() > 200 * 1024
 
 
+def _valid_mega_params(N, cp=1, attn_splits=1, bpc=128, heads=128, top_k=2048, layer=True):
+    """Parameters mdc_megakernel_check accepts (fake 4096-aligned addresses: nothing is dereferenced)."""
+    A = 1 << 20
+    p = N.MegaParams()
+    p.queue = p.scalars = p.arity = p.scopes = A
+    p.row_words, p.n_ctas, p.n_events, p.wait_budget_ns = 8, 4, 1, 1000
+    p.events = N.EventSetC(A, A, 0, cp)
+    p.arena = N.PeerBufferC(A, A, 0, cp, 0)
+    if not layer:
+        return p
+    B = 4
+    lp = N.LogitsParams(kv_pages=A, num_pages=64, page_tokens=64, fmt=N.FMT_NVFP4, q_fmt=N.Q_BF16, q=A, weights=A,
+                        block_table=A, max_pages=256, cand_v=A, cand_i=A, cand_c=A, top_k=top_k, B=B, q_len=1,
+                        heads=64, blocks_per_chunk=bpc, n_chunks=2, id_mul=cp, id_add=0)
+    mp = N.SparseMlaParams(q=A, kv_cmp=A, pt_cmp=A, k_valid=A, o=A, lse=A, o_stride=heads * 512, lse_stride=heads,
+                           B=B, q_len=1, H=heads, d_qk=576, d_v=512, pages_cmp=1000, page_cmp=1, pt_cols=top_k,
+                           kv_dtype=N.DT_BF16, out_dtype=N.DT_BF16, n_splits=1, softmax_scale=0.04, output_scale=1.0)
+    L = N.LayerParams()
+    L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = cp, 0, B, top_k, heads, 2
+    L.kv_seq_stride, L.attn_splits, L.logits, L.mla = 16384, attn_splits, lp, mp
+    L.phase_bytes, L.phases = 1 << 20, 2
+    L.sel_v = L.sel_i = L.sel_c = L.out = L.out_lse = A
+    L.out_dtype, L.l1_groups = N.DT_BF16, 1
+    p.layer = L
+    return p
+
+
+def test_megakernel_check_rejects_bad_layer_configurations():
+    """Configurations that would overrun on-chip arrays or dereference missing buffers come back as
+    error codes from the host-side check (no GPU involved)."""
+    from mega_dsa_cp_b200 import _native as N
+
+    chk = lambda p: N.lib().mdc_megakernel_check(C.byref(p))
+    assert chk(_valid_mega_params(N)) == 0
+    assert chk(_valid_mega_params(N, layer=False)) == 0               # test queues carry no layer
+    assert chk(_valid_mega_params(N, cp=8, attn_splits=2)) == 0       # 16 LSE slices: the limit
+    assert chk(_valid_mega_params(N, cp=8, attn_splits=4)) == -6      # 32 slices overrun the merge's arrays
+    assert chk(_valid_mega_params(N, bpc=1024)) == -6                 # 65536 scores per chunk: past the kernel's shared memory
+    assert chk(_valid_mega_params(N, heads=96)) == -1                 # heads not a multiple of 64
+    assert chk(_valid_mega_params(N, top_k=2047)) in (-1, -2)         # candidate slice not a multiple of 16 bytes
+    p = _valid_mega_params(N)
+    p.layer.sel_i = None
+    assert chk(p) == -4
+    p = _valid_mega_params(N)
+    p.layer.l1_groups = 2                                             # two-level merge without its scratch
+    assert chk(p) == -4
+    p = _valid_mega_params(N)
+    p.layer.logits.kv_pages = None                                    # the indexer tile's own check
+    assert chk(p) == -4
+    p = _valid_mega_params(N)
+    p.layer.mla.d_qk = 500                                            # the attention tile's own check
+    assert chk(p) == -1
+    p = _valid_mega_params(N)
+    p.layer.rank = 3                                                  # rank outside cp
+    assert chk(p) == -1
+    p = _valid_mega_params(N)
+    p.arena = N.PeerBufferC(None, None, 0, 1, 0)                      # a layer needs the arena
+    assert chk(p) == -4
+    # and the Python layer object refuses the same things before it builds anything
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer
+    with pytest.raises(AssertionError):
+        DsaDecodeLayer(4, cp=8, rank=0, attn_splits=4, device="cpu", n_ctas=8)
+
+
 def test_missing_library_fails_loudly(tmp_path):
     code = ("import os, sys; sys.path.insert(0, %r); os.environ['MDC_LIB_PATH'] = %r\n"
             "from mega_dsa_cp_b200 import _native\n"

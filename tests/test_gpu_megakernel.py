@@ -150,12 +150,15 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
     kd_all = orc.dequant_fp4(data, sf, "nvfp4").reshape(-1, P, 128)
     for b in range(B):
         kd = kd_all[case["bt"][b].long()].reshape(S, 128)
-        sel, o, l = orc.decode_step_ref(case["q_deq"][b], case["w"][b], kd, q_mla[b, 0].float(),
+        sel, _, _ = orc.decode_step_ref(case["q_deq"][b], case["w"][b], kd, q_mla[b, 0].float(),
                                         kv[b * S:(b + 1) * S, 0].float(), int(seq[b]), K, 1 / math.sqrt(DQK))
         n = int(layer.sel_c[b])
         got = torch.sort(layer.sel_i[b, :n].cpu()).values
         overlap = len(set(got.tolist()) & set(sel.tolist())) / max(1, sel.numel())
         assert n == sel.numel() and overlap >= 0.999, (n, sel.numel(), overlap)
-        if overlap == 1.0:
-            assert (layer.out[b].cpu() - o).abs().max() < 2e-2
-            assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
+        # attention + LSE merge are always held to the oracle, on the ids the kernel selected
+        # (a near-tie at the selection boundary may swap an id; the attention must still be right)
+        o, l = orc.attend_selected_ref(q_mla[b, 0].float(), kv[b * S:(b + 1) * S, 0].float(),
+                                       layer.sel_i[b, :n].cpu(), 1 / math.sqrt(DQK))
+        assert (layer.out[b].cpu() - o).abs().max() < 2e-2
+        assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3

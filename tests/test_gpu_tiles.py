@@ -338,3 +338,53 @@ def test_row_topk_equals_fused_plus_merge(fmt, P, T, K, bpc, S, seq, wex):
             n = int(oc[b, t])
             assert torch.equal(ri[b, t, :n], oi[b, t, :n]), (b, t)
             assert torch.equal(rv[b, t, :n].view(torch.int32), ov[b, t, :n].view(torch.int32)), (b, t)
+
+
+def test_row_topk_config2_full_size_exact_on_own_logits():
+    """BASELINE config 2 at full size (B = 32 sequences of 32768 tokens, NVFP4 pages of 64,
+    top-k 2048, one row-mode launch): on sampled sequences the ids and values are, bit for bit
+    and in order, the top-k of the kernel's own logits under (value desc, position asc); every
+    sequence returns exactly k entries, all distinct and in range.  Inputs are generated on the
+    device (seeded) to keep the test short."""
+    from mega_dsa_cp_b200.tiles.fp4 import fuse_pages
+    from mega_dsa_cp_b200.tiles.logits import run_fp4_paged_mqa_logits
+
+    B, S, P, K, bpc = 32, 32768, 64, 2048, 128
+    g = torch.Generator(device=DEV).manual_seed(11)
+    pages = S // P
+    pool = B * pages
+    cache = torch.cat([fuse_pages(torch.randn(pool // 8 * P, 128, generator=g, device=DEV), "nvfp4", P)[0]
+                       for _ in range(8)])
+    bt = torch.randperm(pool, generator=g, device=DEV).to(torch.int32).reshape(B, pages).contiguous()
+    q = torch.randn(B, 64, 128, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(B, 64, generator=g, device=DEV) / 64.0).contiguous()
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    logits = torch.full((B, S), float("nan"), device=DEV)
+    run_fp4_paged_mqa_logits(cache, q, None, w, bt, logits, bpc, fmt="nvfp4", page_tokens=P, status=status)
+    rv = torch.full((B, 1, K), float("nan"), device=DEV)
+    ri = torch.full((B, 1, K), -1, dtype=torch.int32, device=DEV)
+    rc = torch.zeros(B, 1, dtype=torch.int32, device=DEV)
+    run_fp4_paged_mqa_logits(cache, q, None, w, bt, None, bpc, top_k=K, fmt="nvfp4", page_tokens=P, status=status,
+                             row_topk=(rv, ri, rc))
+    torch.cuda.synchronize()
+    assert status[0].item() == 0, status.tolist()
+    assert not torch.isnan(logits).any()
+    assert bool((rc == K).all())
+    srt = torch.sort(ri[:, 0], dim=-1).values
+    assert bool((srt[:, 1:] > srt[:, :-1]).all()) and int(srt.min()) >= 0 and int(srt.max()) < S
+    # every selected value is the logit at its id, and nothing outside the selection beats the smallest selected value
+    assert torch.equal(torch.gather(logits, 1, ri[:, 0].long()).view(torch.int32), rv[:, 0].view(torch.int32))
+    masked = logits.clone()
+    masked.scatter_(1, ri[:, 0].long(), float("-inf"))
+    assert bool((masked.max(dim=1).values <= rv[:, 0].min(dim=1).values).all())
+    lg, ri_c, rv_c = logits.cpu(), ri.cpu(), rv.cpu()
+    for b in (0, 7, 13, 22, 31):
+        ev, ei = orc.local_topk_ref(lg[b], 0, S, S, K, 1, 0)
+        assert torch.equal(ri_c[b, 0], ei), b
+        assert torch.equal(rv_c[b, 0].view(torch.int32), ev.view(torch.int32)), b
+    # one sampled sequence against the oracle's logits (dequantised FP4, fp32): 1e-3 relative
+    b = 13
+    data, sf = orc.split_index_pages(cache[bt[b].long()].cpu(), "nvfp4", P)
+    kd = orc.dequant_fp4(data, sf, "nvfp4").reshape(S, 128)
+    ref = ((q[b].float().cpu() @ kd.T).clamp(min=0) * w[b].cpu()[:, None]).sum(dim=0)
+    assert torch.allclose(lg[b], ref, rtol=1e-3, atol=1e-4), (lg[b] - ref).abs().max()
