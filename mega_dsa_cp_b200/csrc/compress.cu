@@ -169,13 +169,17 @@ __global__ void __launch_bounds__(kBlockThreads) online_step_kernel(const __grid
 }
 
 // ---------------------------------------------------------------- finalize helpers
-__device__ inline float block_sum(float v, float* red) {
+// Block-wide sum in double precision.  The squares of fp32 values are exact in fp64 and their
+// fp64 sum is accurate far below one fp32 ulp, so the fp32 result does not depend on the order of
+// the reduction: a CPU restatement that accumulates in fp64 gets the same bits.
+__device__ inline double block_sum_f64(double v, double* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  v = warp_sum(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   __syncthreads();
   if (lane == 0) red[warp] = v;
   __syncthreads();
-  float t = 0.f;
+  double t = 0.0;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) t += red[w];
   return t;
@@ -207,15 +211,20 @@ __device__ inline float merge_channel(const float* stats, int cp, int n_floats, 
 // RMS norm + rope(last 64 channels at position pos) of an hd-wide vector held
 // one or two channels per thread; result in y_smem[hd]
 __device__ inline void norm_rope(float v0, float v1, int hd, const float* norm_w, float eps, const float* freqs, int pos,
-                                 float* y_smem, float* red) {
+                                 float* y_smem, double* red) {
+  // Every step rounds exactly like the fp32 tensor arithmetic of the reference chain
+  // (compress_ref.py:77-95): mean of squares (accumulated in fp64, see block_sum_f64), + eps,
+  // 1 / sqrt with IEEE division and square root, x * factor * weight as two multiplications,
+  // and the rotation as two rounded products and one rounded sum (no fused multiply-add).
   const int tid = threadIdx.x;
   const bool two = hd > kBlockThreads;
-  float ssq = 0.f;
-  if (tid < hd) ssq = v0 * v0 + (two ? v1 * v1 : 0.f);
-  const float factor = rsqrtf(block_sum(ssq, red) / static_cast<float>(hd) + eps);
+  double ssq = 0.0;
+  if (tid < hd) ssq = static_cast<double>(v0) * v0 + (two ? static_cast<double>(v1) * v1 : 0.0);
+  const float mean = static_cast<float>(block_sum_f64(ssq, red) / static_cast<double>(hd));
+  const float factor = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
   if (tid < hd) {
-    y_smem[tid] = v0 * factor * norm_w[tid];
-    if (two) y_smem[tid + kBlockThreads] = v1 * factor * norm_w[tid + kBlockThreads];
+    y_smem[tid] = __fmul_rn(__fmul_rn(v0, factor), norm_w[tid]);
+    if (two) y_smem[tid + kBlockThreads] = __fmul_rn(__fmul_rn(v1, factor), norm_w[tid + kBlockThreads]);
   }
   __syncthreads();
   float r[2];
@@ -226,7 +235,8 @@ __device__ inline void norm_rope(float v0, float v1, int hd, const float* norm_w
       const int i2 = ch - (hd - kRope);
       const float c = freqs[static_cast<int64_t>(pos) * kRope + (i2 & ~1)];
       const float sn = freqs[static_cast<int64_t>(pos) * kRope + (i2 | 1)];
-      r[k] = y_smem[ch] * c + y_smem[ch ^ 1] * ((ch & 1) ? sn : -sn);
+      // even channel: re * c - im * s ; odd channel: re * s + im * c
+      r[k] = __fadd_rn(__fmul_rn(y_smem[ch], c), __fmul_rn(y_smem[ch ^ 1], (ch & 1) ? sn : -sn));
     }
   }
   __syncthreads();
@@ -324,8 +334,8 @@ __device__ inline bool wait_stats(const mdc_compress_params& p, int b, int* flag
 namespace mdc {
 
 struct FinalizeSmem {
+  double red[kWarps];
   float y[kHdAttn];
-  float red[kWarps];
   int flag;
 };
 

@@ -396,8 +396,14 @@ def hadamard128_staged(x: torch.Tensor) -> torch.Tensor:
 
 
 def rms_norm(x, weight, eps):
-    """mega_dsa_cp/tiles/compress_ref.py:77-80."""
-    return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps) * weight
+    """mega_dsa_cp/tiles/compress_ref.py:77-80.  The mean of squares is accumulated in float64 and
+    rounded to float32 once: within one ulp of the reference's float32 reduction, but independent
+    of the order of the additions, which is what lets a CUDA kernel (tree reduction) and this
+    restatement (vector reduction) agree bit for bit.  1 / sqrt is the IEEE division and square
+    root; x * factor * weight are two float32 multiplications."""
+    ms = x.double().pow(2).mean(dim=-1, keepdim=True).to(torch.float32)
+    factor = 1.0 / torch.sqrt(ms + torch.tensor(eps, dtype=torch.float32))
+    return x * factor * weight
 
 
 def rope_tail(x: torch.Tensor, freqs: torch.Tensor, pos: int) -> torch.Tensor:

@@ -162,3 +162,39 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
                                        layer.sel_i[b, :n].cpu(), 1 / math.sqrt(DQK))
         assert (layer.out[b].cpu() - o).abs().max() < 2e-2
         assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
+
+
+def test_layer_steps_replay_from_a_cuda_graph():
+    """The phase counter lives on the device and the kernel advances it, so a model step -- here 61
+    layer-calls, the reference's count (docs/overview.md:10) -- captured once as a CUDA graph replays
+    with no host update in between; every replay gives the eager result."""
+    from dsa_inputs import indexer_case
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+
+    B, S, K, bpc, P, H, DQK = 2, 4096, 512, 16, 64, 128, 576
+    case = indexer_case(B, S, P, "nvfp4", seed=6)
+    g = torch.Generator().manual_seed(9)
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
+    seq = torch.tensor([S, S - 300], dtype=torch.int32)
+    layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=32)
+    d = lambda t: t.to(DEV)
+    layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
+    layer.step()
+    torch.cuda.synchronize()
+    layer.check_status()
+    want_o, want_l, want_i = layer.out.clone(), layer.out_lse.clone(), layer.sel_i.clone()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(61):
+                layer.step(stream=stream)
+    for _ in range(2):
+        layer.out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        layer.check_status()
+        assert torch.equal(layer.out, want_o) and torch.equal(layer.out_lse, want_l) and torch.equal(layer.sel_i, want_i)
+    assert int(layer.dsched.scalars[0]) == 1 + 2 * 61   # one eager step + two replays of 61
