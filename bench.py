@@ -521,6 +521,20 @@ def indexer_alone(args, dev):
     torch.cuda.synchronize()
     ms = k0.elapsed_time(k1) / reps
     assert status[0].item() == 0 and int(oc.min()) == K, f"device failure {status.tolist()}"
+    # the same pipeline without the selection (logits written out, 4.2 MB more): what the select adds
+    logits = torch.empty(B * T, S, device=dev)
+    plain = lambda i: run_fp4_paged_mqa_logits(caches[i % c["copies"]], q, None, w, tables[i % c["copies"]], logits, bpc,
+                                               fmt="nvfp4", page_tokens=P, status=status)
+    for i in range(c["copies"]):
+        plain(i)
+    torch.cuda.synchronize()
+    k0.record()
+    for i in range(reps):
+        plain(i)
+    k1.record()
+    torch.cuda.synchronize()
+    ms_plain = k0.elapsed_time(k1) / reps
+    del logits
 
     # end to end: [q | w | page table] in one pinned block down, [ids | counts] in one block back
     nq, nw, nbt = q.numel() * 2, w.numel() * 4, tables[0].numel() * 4
@@ -562,7 +576,7 @@ def indexer_alone(args, dev):
             "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "logits_row_kernel<NVFP4,64,1>",
             "workload": "BASELINE config 2: B=32, ctx 32768, indexer logits + exact top-k 2048, one launch",
             "launch_us": ms * 1e3, "algorithmic_bytes": algo, "traffic": NCU_TRAFFIC_BYTES}
-    extra = {"step_us": ms * 1e3, "tokens_per_s": B * T / (ms * 1e-3), "e2e_step_us": e2e_ms * 1e3,
+    extra = {"step_us": ms * 1e3, "logits_without_select_us": ms_plain * 1e3, "tokens_per_s": B * T / (ms * 1e-3), "e2e_step_us": e2e_ms * 1e3,
              "e2e_tokens_per_s": B * T / (e2e_ms * 1e-3), "h2d_bytes_per_step": hin[0].numel(),
              "d2h_bytes_per_step": hout.numel() * 4,
              "l2": f"rotating {c['copies']} cache copies ({c['copies'] * 75.5:.0f} MB > 126 MB L2)"}

@@ -153,6 +153,23 @@ __device__ inline void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes
       "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// L2 cache policy for data that is read exactly once (a streamed cache): its lines are the first
+// to be evicted, so the stream does not push out what the other tasks of a persistent kernel re-use
+// every step -- their code above all: instructions live in the same L2, and a task whose code has
+// been evicted pays a DRAM round trip per instruction-cache miss.
+__device__ inline uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+// bulk_g2s with an L2 cache policy
+__device__ inline void bulk_g2s_hint(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 // 1-D bulk copy shared -> global (local or peer memory), bulk-group completion.
 __device__ inline void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),

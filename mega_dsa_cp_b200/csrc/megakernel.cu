@@ -40,16 +40,25 @@ __device__ inline int inbox_slice_bytes(const mdc_layer_params& L) { return L.H 
 
 // Ordered compaction by the 256 workers: keeps ids[i] (i < n) with
 // ids[i] % cp == rank and writes row_base + ids[i] / cp to out in input order.  Returns the count.
+// A warp fetches its whole segment in batches of eight independent loads per lane (the ids were just
+// written to global memory: one dependent load per step of the scan would cost an L2 round trip each).
 __device__ inline int compact_local_ids(const int32_t* ids, int n, int cp, int rank, int row_base, int32_t* out,
                                         int out_cap, SelectScratch& sc) {
+  constexpr int U = 8;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seg = ceil_div(ceil_div(n, kWarps), 32) * 32;
   const int lo = warp * seg, hi = min(n, lo + seg);
+  const uint32_t lt = (1u << lane) - 1u;
   int cnt = 0;
-  for (int base = lo; base < hi; base += 32) {
-    const int i = base + lane;
-    const bool keep = i < hi && (ids[i] % cp) == rank;
-    cnt += __popc(__ballot_sync(0xffffffffu, keep));
+  for (int base = lo; base < hi; base += 32 * U) {
+    int32_t id[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + 32 * u + lane;
+      id[u] = i < hi ? ids[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) cnt += __popc(__ballot_sync(0xffffffffu, id[u] >= 0 && (id[u] % cp) == rank));
   }
   sync_workers();
   if (lane == 0) sc.wgt[warp] = cnt;
@@ -60,15 +69,21 @@ __device__ inline int compact_local_ids(const int32_t* ids, int n, int cp, int r
     if (w < warp) before += sc.wgt[w];
     total += sc.wgt[w];
   }
-  const uint32_t lt = (1u << lane) - 1u;
-  for (int base = lo; base < hi; base += 32) {
-    const int i = base + lane;
-    const int id = i < hi ? ids[i] : 0;
-    const bool keep = i < hi && (id % cp) == rank;
-    const uint32_t m = __ballot_sync(0xffffffffu, keep);
-    const int slot = before + __popc(m & lt);
-    if (keep && slot < out_cap) out[slot] = row_base + id / cp;
-    before += __popc(m);
+  for (int base = lo; base < hi; base += 32 * U) {
+    int32_t id[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + 32 * u + lane;
+      id[u] = i < hi ? ids[i] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool keep = id[u] >= 0 && (id[u] % cp) == rank;
+      const uint32_t m = __ballot_sync(0xffffffffu, keep);
+      const int slot = before + __popc(m & lt);
+      if (keep && slot < out_cap) out[slot] = row_base + id[u] / cp;
+      before += __popc(m);
+    }
   }
   sync_workers();
   return min(total, out_cap);

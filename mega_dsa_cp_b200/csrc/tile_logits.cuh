@@ -191,34 +191,19 @@ __device__ inline void logits_stage_query(const mdc_logits_params& p, int b, uns
   }
 }
 
-// Exact top-k of one chunk's scores (shared memory): the search runs on register keys; the
-// scores become sortable keys in place (0 = not a candidate) and the position-ordered emit is a
-// rolled loop over them.  Straight-line code that a block executes once per task is bound by
-// instruction fetch, so only the hot search is unrolled.  Ties at the threshold go to the
-// smaller position.  Returns the number of entries emitted.
-template <int E, typename Emit>
+// Exact top-k of one chunk's scores (shared memory).  The scores become sortable keys in place
+// (0 = not a candidate); search and position-ordered emit are rolled loops over them: code that a
+// block executes once per task is bound by instruction fetch, so it is kept small.  Ties at the
+// threshold go to the smaller position.  Returns the number of entries emitted.
+template <typename Emit>
 __device__ inline int fused_chunk_select(const float* sc_row, uint32_t* keys, int n_local, int base_pos, int limit, int top_k,
-                                         RegSelectScratch<kFusedRegE>& rsel, SelectScratch& sel, Emit emit) {
-  const int tid = threadIdx.x;
-  Threshold<uint32_t> th;
-  {
-    uint32_t key[E];
-#pragma unroll
-    for (int it = 0; it < E; ++it) {
-      const int pos = it * kBlockThreads + tid;
-      key[it] = (pos < n_local && (base_pos + pos) < limit) ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
-    }
-    sync_workers();
-#pragma unroll
-    for (int it = 0; it < E; ++it) {
-      const int pos = it * kBlockThreads + tid;
-      if (pos < n_local) keys[pos] = key[it];
-    }
-    th = block_select_regs<E>(key, top_k, rsel);
-  }
+                                         SelectScratch& sel, Emit emit) {
   sync_workers();
-  return block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = keys[pos] != 0u; return keys[pos]; }, n_local,
-                                       th, sel, emit);
+  for (int pos = threadIdx.x; pos < n_local; pos += kBlockThreads)
+    keys[pos] = (base_pos + pos) < limit ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+  sync_workers();
+  const Threshold<uint32_t> th = block_select_bits_smem(keys, n_local, top_k, sel);
+  return block_emit_keys(keys, n_local, th, sel, emit);
 }
 
 // Exact top-k of a whole request row across the blocks of a thread-block
@@ -467,6 +452,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     // the address arithmetic of all pages.
     const int s = lane / PG::kTilePages, pp = lane % PG::kTilePages;
     int tile = (s < kRawStages) ? s : n_tiles;
+    const uint64_t stream_policy = l2_policy_evict_first();  // the index cache is read once per step
     long long t_last = clock64();
     while (__any_sync(0xffffffffu, tile < n_tiles) && !*abort_flag) {
       bool ready = false;
@@ -483,8 +469,8 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
         }
         const int32_t id = page_id[i0 + pp];
         if (id >= 0) {
-          bulk_g2s(ring + s * PG::kStageBytes + pp * PG::kBytes, p.kv_pages + static_cast<int64_t>(id) * PG::kBytes,
-                   PG::kBytes, &raw_full[s]);
+          bulk_g2s_hint(ring + s * PG::kStageBytes + pp * PG::kBytes, p.kv_pages + static_cast<int64_t>(id) * PG::kBytes,
+                        PG::kBytes, &raw_full[s], stream_policy);
         }
         tile += kRawStages;
       }
@@ -687,35 +673,13 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
     const int base_pos = blk0 * PAGE;
     for (int t = 0; t < T; ++t) {
       const float* sc_row = scores + t * chunk_tokens;
-      auto src = [&](int pos, bool& valid) -> uint32_t {
-        valid = (base_pos + pos) < limit;
-        return sortable_u32(sc_row[pos]);
-      };
       const int64_t slot0 = ((static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk) * p.top_k;
-      int n;
-      // the smallest register budget that holds the chunk (the search's cost goes with E)
-      RegSelectScratch<kFusedRegE>& rsel = *reinterpret_cast<RegSelectScratch<kFusedRegE>*>(smem + L.sel);
       uint32_t* keys = reinterpret_cast<uint32_t*>(scores + t * chunk_tokens);
-      auto emit = [&](int pos, int slot) {
+      const int n = fused_chunk_select(sc_row, keys, n_local, base_pos, limit, p.top_k, sel, [&](int pos, int slot) {
         const uint32_t kv = keys[pos];
         p.cand_v[slot0 + slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
         p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
-      };
-      if (n_local <= kBlockThreads * 8) {
-        n = fused_chunk_select<8>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
-      } else if (n_local <= kBlockThreads * 16) {
-        n = fused_chunk_select<16>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
-      } else if (n_local <= kBlockThreads * 32) {
-        n = fused_chunk_select<32>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
-      } else if (n_local <= kBlockThreads * 64) {
-        n = fused_chunk_select<64>(sc_row, keys, n_local, base_pos, limit, p.top_k, rsel, sel, emit);
-      } else {
-        Threshold<uint32_t> th = block_select_threshold<uint32_t>(src, n_local, p.top_k, sel);
-        n = block_emit_selected<uint32_t>(src, n_local, th, sel, [&](int pos, int slot) {
-          p.cand_v[slot0 + slot] = sc_row[pos];
-          p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
-        });
-      }
+      });
       if (tid == 0) p.cand_c[(static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk] = n;
     }
   }

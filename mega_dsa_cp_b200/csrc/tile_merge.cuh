@@ -307,8 +307,7 @@ __device__ inline int merge_staged_hybrid(int n_pos, int top_k, float* out_v, in
   int n;
   sync_workers();
   if (th.need_eq == 0x7fffffff || n_eq == th.need_eq) {
-    n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, th,
-                                      sm.sel, put);
+    n = block_emit_keys(vb, n_pos, th, sm.sel, put);
   } else {
     const uint32_t tau = th.tau;
     auto key2 = [&](int pos) -> uint32_t {
@@ -355,8 +354,7 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
   };
   if (th.need_eq == 0x7fffffff || n_eq == th.need_eq) {
     // everything valid, or every entry tied at the threshold is taken (distinct logits: the usual case)
-    n = block_emit_selected<uint32_t>([&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, th,
-                                      sm.sel, put);
+    n = block_emit_keys(vb, n_pos, th, sm.sel, put);
   } else {
     const uint32_t tau = th.tau;
     auto key2 = [&](int pos) -> uint32_t {
@@ -397,8 +395,9 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
         all.tau = 0u;  // valid keys are >= 1
         all.need_eq = 0;
         all.n_sel = n_valid;
-        const int n = block_emit_selected<uint32_t>(
-            [&](int pos, bool& valid) { valid = vb[pos] != 0u; return vb[pos]; }, n_pos, all, sm.sel,
+        all.need_eq = 0x7fffffff;
+        const int n = block_emit_keys(
+            vb, n_pos, all, sm.sel,
             [&](int pos, int slot) {
               if (slot < top_k) {
                 out_v[slot] = unsortable_f32(vb[pos]);
@@ -412,13 +411,6 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
         return n;
       }
     }
-    // the smallest register budget that holds the row: the search's cost goes with E, not with n_pos
-    if (n_pos <= kBlockThreads * 8) return merge_staged_hybrid<8>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    if (n_pos <= kBlockThreads * 16) return merge_staged_hybrid<16>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    if (n_pos <= kBlockThreads * kMergeRegE)
-      return merge_staged_hybrid<kMergeRegE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
-    if (n_pos <= kBlockThreads * kMergeBigE)
-      return merge_staged_hybrid<kMergeBigE>(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, ib);
     return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; });
   }
   if (stage && n_pos * 4 <= stage_bytes && maxK >= 1) {

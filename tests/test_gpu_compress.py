@@ -110,7 +110,7 @@ def test_window_machine_roll(cp):
                 pi = orc.csa_entry_ref(rec_i[b], ape_i, n, 128)
                 _post_checks(sts[owner], b, slot, pa, pi, 4 * n, norm_a, norm_i, freqs, 0.02, (cp, s, b), tally)
             assert sts[owner].k_valid.tolist() == [slot + 1] * B
-    assert tally["nibbles"] == 6 * B * 256 and tally["e4m3_off_by_one"] <= tally["e4m3"] // 100, tally
+    assert tally["nibbles"] == 6 * B * 128 and tally["e4m3_off_by_one"] <= tally["e4m3"] // 100, tally
 
 
 @pytest.mark.parametrize("cp,ratio", [(1, 64), (4, 64), (2, 128)])
