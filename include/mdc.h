@@ -258,6 +258,69 @@ typedef struct {
   int64_t mc_base;        /* NVLS multicast address or 0 */
 } mdc_peer_buffer;
 
+/* ------------------------------------------------------------------------
+ * KV compressor: softmax-gated pooling of token records into compressed
+ * entries, context-parallel (per-rank partial statistics -> pushed to the
+ * entry's owner rank -> owner merges, normalises, rotates, quantises and
+ * writes its pools).  Replaces the four kernels and launchers of
+ * mega_dsa_cp/tiles/compress.py:120-250 (csa step), :284-523 (csa finalize),
+ * :564-640 (c128 step), :669-792 (c128 finalize) and the micro kernel :828-889.
+ *
+ * ratio == 4 : overlapping 8-slot window machine, two streams (attention 512
+ *              channels, indexer 128 channels), records (B, 4*hd) =
+ *              [kv_overlap | kv_normal | score_overlap | score_normal]; rings
+ *              (B, ring_slots, 4*hd), slot of local record l = l % ring_slots.
+ * ratio == 64 / 128 : online machine, one stream of 512 channels, records
+ *              (B, 2*512) = [kv | score], running state (B, 3, 512) = [m | l | kv].
+ * A step covers global positions seq_len[b] .. seq_len[b] + q_len - 1; this
+ * rank owns the position p with p % cp == rank (q_len <= cp).  Entry n is
+ * owned by rank n % cp and stored at its local slot n / cp.
+ * Statistics region: (B, cp, stats_bytes) at arena offset stats_off with
+ * stats_bytes = 7696 (ratio 4) or 6160 (online); event cell ev_base_id + b is
+ * bumped once per rank per step on every rank (arity cp).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, cp, rank, q_len, ratio;
+  int32_t phase;               /* finalize: waits for cell value cp * (phase + 1)        */
+  const int32_t* seq_len;      /* (B,) global length before the step                     */
+  float* ring_attn;            /* ratio 4: (B, 8, 4*512) ring of this rank's records     */
+  float* ring_idx;             /* ratio 4: (B, 8, 4*128)                                 */
+  const float* new_attn;       /* ratio 4: (B, 4*512); online: (B, 2*512)                */
+  const float* new_idx;        /* ratio 4: (B, 4*128)                                    */
+  const float* ape_attn;       /* ratio 4: (8, 512) slot bias; online: (ratio, 512)      */
+  const float* ape_idx;        /* ratio 4: (8, 128)                                      */
+  float* state;                /* online: (B, 3, 512)                                    */
+  mdc_peer_buffer arena;
+  int64_t stats_off;
+  mdc_event_set events;
+  int32_t ev_base_id;
+  int32_t do_push;             /* 0 skips the payload push (bisecting aid)               */
+  int64_t wait_budget_ns;
+  const float* norm_w_attn;    /* (512,)                                                 */
+  const float* norm_w_idx;     /* (128,)                                                 */
+  const float* freqs;          /* (freq_rows, 64) rope table [cos0, sin0, cos1, ...]     */
+  int32_t freq_rows;
+  float norm_eps;
+  float inv_fp8_scale;
+  int32_t attn_pool_dtype;     /* MDC_DT_E4M3 | MDC_DT_BF16                              */
+  void* attn_pool;             /* (B, max_entries, 512)                                  */
+  uint8_t* idx_pool;           /* ratio 4: (B, max_entries / idx_page_tokens, page bytes) */
+  int32_t idx_fmt;             /* MDC_FMT_*                                              */
+  int32_t idx_page_tokens;
+  int32_t max_entries;
+  int32_t ring_slots;          /* ratio 4: slots of ring_attn / ring_idx per sequence, >= ceil(8 / cp); 0 = 8.  The reference's ring holds 4 (cp = 2, compress.py:43) */
+  int32_t* k_valid;            /* (B,) entries held by this rank                         */
+  float* dbg_attn;             /* (B, max_entries, 512) merged fp32 before the norm, or NULL */
+  float* dbg_idx;              /* (B, max_entries, 128) or NULL                          */
+  int32_t* status;
+} mdc_compress_params;
+int mdc_compress_step_launch(const mdc_compress_params* p, void* stream);
+int mdc_compress_finalize_launch(const mdc_compress_params* p, void* stream);
+/* staged 128-point Hadamard + MXFP4 quantisation of n rows: x (n, 128) fp32 ->
+ * out (n, 68) = 64 B packed codes + 4 B UE8M0 (compress.py:828-889) */
+int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* stream);
+
+
 /* task op codes understood by mdc_megakernel_launch */
 #define MDC_OP_NOP 0
 #define MDC_OP_LOGITS 1     /* c0 = b, c1 = chunk                                  */
@@ -266,6 +329,8 @@ typedef struct {
 #define MDC_OP_ATTN 4       /* c0 = b, c1 = head/column block (see megakernel.cu), c2 = slot split: partial -> owner inbox */
 #define MDC_OP_MERGE_L1A 6  /* c0 = b, c1 = group: chunk lists of the group -> mid list              */
 #define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
+#define MDC_OP_CMP_STEP 7   /* c0 = b: compressor step of layer.cmp (record append, statistics push to the entry owner)  */
+#define MDC_OP_CMP_FIN 8    /* c0 = b: entry owner merges the cp statistics and writes its pools                       */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
 #define MDC_OP_PUSH 18      /* c1 = dst rank, c2 = slot: bulk push a pattern (test op) */
@@ -301,6 +366,12 @@ typedef struct {
   float* mid_v;                 /* (B, l1_groups, top_k)                         */
   int32_t* mid_i;               /* (B, l1_groups, top_k)                         */
   int32_t* mid_c;               /* (B, l1_groups)                                */
+  /* KV compressor of the layer as CMP_STEP / CMP_FIN tasks (docs/phase1.4-comm-tasks.md:37-38,52,67 of the
+   * reference: ops of the layer DAG, event cmp_stats_arrived[b] with arity cp, arena region cmp_stats).
+   * cmp.B == 0: the layer has no compressor tasks.  The tasks' wait / notify edges replace the event
+   * fields of cmp (events, ev_base_id, phase, wait_budget_ns are not used); cmp.stats_off is the offset
+   * of the statistics region inside ONE phase of the arena (the kernel adds the phase rotation). */
+  mdc_compress_params cmp;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of
@@ -345,67 +416,6 @@ int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
 int mdc_megakernel_check(const mdc_mega_params* p);
 int mdc_megakernel_smem_bytes(void);
 int mdc_megakernel_threads(void);
-
-/* ------------------------------------------------------------------------
- * KV compressor: softmax-gated pooling of token records into compressed
- * entries, context-parallel (per-rank partial statistics -> pushed to the
- * entry's owner rank -> owner merges, normalises, rotates, quantises and
- * writes its pools).  Replaces the four kernels and launchers of
- * mega_dsa_cp/tiles/compress.py:120-250 (csa step), :284-523 (csa finalize),
- * :564-640 (c128 step), :669-792 (c128 finalize) and the micro kernel :828-889.
- *
- * ratio == 4 : overlapping 8-slot window machine, two streams (attention 512
- *              channels, indexer 128 channels), records (B, 4*hd) =
- *              [kv_overlap | kv_normal | score_overlap | score_normal].
- * ratio == 64 / 128 : online machine, one stream of 512 channels, records
- *              (B, 2*512) = [kv | score], running state (B, 3, 512) = [m | l | kv].
- * A step covers global positions seq_len[b] .. seq_len[b] + q_len - 1; this
- * rank owns the position p with p % cp == rank (q_len <= cp).  Entry n is
- * owned by rank n % cp and stored at its local slot n / cp.
- * Statistics region: (B, cp, stats_bytes) at arena offset stats_off with
- * stats_bytes = 7696 (ratio 4) or 6160 (online); event cell ev_base_id + b is
- * bumped once per rank per step on every rank (arity cp).
- * ------------------------------------------------------------------------ */
-typedef struct {
-  int32_t B, cp, rank, q_len, ratio;
-  int32_t phase;               /* finalize: waits for cell value cp * (phase + 1)        */
-  const int32_t* seq_len;      /* (B,) global length before the step                     */
-  float* ring_attn;            /* ratio 4: (B, 8, 4*512) ring of this rank's records     */
-  float* ring_idx;             /* ratio 4: (B, 8, 4*128)                                 */
-  const float* new_attn;       /* ratio 4: (B, 4*512); online: (B, 2*512)                */
-  const float* new_idx;        /* ratio 4: (B, 4*128)                                    */
-  const float* ape_attn;       /* ratio 4: (8, 512) slot bias; online: (ratio, 512)      */
-  const float* ape_idx;        /* ratio 4: (8, 128)                                      */
-  float* state;                /* online: (B, 3, 512)                                    */
-  mdc_peer_buffer arena;
-  int64_t stats_off;
-  mdc_event_set events;
-  int32_t ev_base_id;
-  int32_t do_push;             /* 0 skips the payload push (bisecting aid)               */
-  int64_t wait_budget_ns;
-  const float* norm_w_attn;    /* (512,)                                                 */
-  const float* norm_w_idx;     /* (128,)                                                 */
-  const float* freqs;          /* (freq_rows, 64) rope table [cos0, sin0, cos1, ...]     */
-  int32_t freq_rows;
-  float norm_eps;
-  float inv_fp8_scale;
-  int32_t attn_pool_dtype;     /* MDC_DT_E4M3 | MDC_DT_BF16                              */
-  void* attn_pool;             /* (B, max_entries, 512)                                  */
-  uint8_t* idx_pool;           /* ratio 4: (B, max_entries / idx_page_tokens, page bytes) */
-  int32_t idx_fmt;             /* MDC_FMT_*                                              */
-  int32_t idx_page_tokens;
-  int32_t max_entries;
-  int32_t reserved0;
-  int32_t* k_valid;            /* (B,) entries held by this rank                         */
-  float* dbg_attn;             /* (B, max_entries, 512) merged fp32 before the norm, or NULL */
-  float* dbg_idx;              /* (B, max_entries, 128) or NULL                          */
-  int32_t* status;
-} mdc_compress_params;
-int mdc_compress_step_launch(const mdc_compress_params* p, void* stream);
-int mdc_compress_finalize_launch(const mdc_compress_params* p, void* stream);
-/* staged 128-point Hadamard + MXFP4 quantisation of n rows: x (n, 128) fp32 ->
- * out (n, 68) = 64 B packed codes + 4 B UE8M0 (compress.py:828-889) */
-int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* stream);
 
 #ifdef __cplusplus
 }

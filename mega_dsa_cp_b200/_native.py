@@ -72,6 +72,20 @@ class PeerBufferC(C.Structure):
     _fields_ = [("base", p_void), ("offsets", p_void), ("my_rank", i32), ("world", i32), ("mc_base", i64)]
 
 
+class CompressParams(C.Structure):
+    _fields_ = [
+        ("B", i32), ("cp", i32), ("rank", i32), ("q_len", i32), ("ratio", i32), ("phase", i32),
+        ("seq_len", p_void), ("ring_attn", p_void), ("ring_idx", p_void), ("new_attn", p_void), ("new_idx", p_void),
+        ("ape_attn", p_void), ("ape_idx", p_void), ("state", p_void),
+        ("arena", PeerBufferC), ("stats_off", i64), ("events", EventSetC), ("ev_base_id", i32), ("do_push", i32),
+        ("wait_budget_ns", i64), ("norm_w_attn", p_void), ("norm_w_idx", p_void), ("freqs", p_void),
+        ("freq_rows", i32), ("norm_eps", f32), ("inv_fp8_scale", f32), ("attn_pool_dtype", i32),
+        ("attn_pool", p_void), ("idx_pool", p_void), ("idx_fmt", i32), ("idx_page_tokens", i32),
+        ("max_entries", i32), ("ring_slots", i32), ("k_valid", p_void), ("dbg_attn", p_void), ("dbg_idx", p_void),
+        ("status", p_void),
+    ]
+
+
 class LayerParams(C.Structure):
     _fields_ = [
         ("cp", i32), ("rank", i32), ("B", i32), ("top_k", i32), ("H", i32), ("n_chunks", i32),
@@ -80,6 +94,7 @@ class LayerParams(C.Structure):
         ("cand_off", i64), ("inbox_off", i64), ("phase_bytes", i64), ("phases", i32),
         ("sel_v", p_void), ("sel_i", p_void), ("sel_c", p_void), ("out", p_void), ("out_lse", p_void),
         ("out_dtype", i32), ("l1_groups", i32), ("mid_v", p_void), ("mid_i", p_void), ("mid_c", p_void),
+        ("cmp", CompressParams),
     ]
 
 
@@ -93,21 +108,8 @@ class MegaParams(C.Structure):
     ]
 
 
-class CompressParams(C.Structure):
-    _fields_ = [
-        ("B", i32), ("cp", i32), ("rank", i32), ("q_len", i32), ("ratio", i32), ("phase", i32),
-        ("seq_len", p_void), ("ring_attn", p_void), ("ring_idx", p_void), ("new_attn", p_void), ("new_idx", p_void),
-        ("ape_attn", p_void), ("ape_idx", p_void), ("state", p_void),
-        ("arena", PeerBufferC), ("stats_off", i64), ("events", EventSetC), ("ev_base_id", i32), ("do_push", i32),
-        ("wait_budget_ns", i64), ("norm_w_attn", p_void), ("norm_w_idx", p_void), ("freqs", p_void),
-        ("freq_rows", i32), ("norm_eps", f32), ("inv_fp8_scale", f32), ("attn_pool_dtype", i32),
-        ("attn_pool", p_void), ("idx_pool", p_void), ("idx_fmt", i32), ("idx_page_tokens", i32),
-        ("max_entries", i32), ("reserved0", i32), ("k_valid", p_void), ("dbg_attn", p_void), ("dbg_idx", p_void),
-        ("status", p_void),
-    ]
-
-
 OP_NOP, OP_LOGITS, OP_MERGE_L1, OP_MERGE_L2, OP_ATTN, OP_LSE_MERGE, OP_MERGE_L1A = 0, 1, 2, 3, 4, 5, 6
+OP_CMP_STEP, OP_CMP_FIN = 7, 8
 OP_SLEEP, OP_LOG, OP_PUSH, OP_VERIFY = 16, 17, 18, 19
 DEV_WAIT_TIMEOUT, DEV_COPY_TIMEOUT, DEV_BAD_INDEX, DEV_BAD_OP = 1, 2, 3, 4
 

@@ -13,6 +13,7 @@
 #include "comm.cuh"
 #include "events.cuh"
 #include "sched.cuh"
+#include "tile_compress.cuh"
 #include "tile_logits.cuh"
 #include "tile_lse_merge.cuh"
 #include "tile_merge.cuh"
@@ -237,6 +238,25 @@ __device__ inline void op_lse_merge(const mdc_mega_params& p, int b, int hq, int
                       reinterpret_cast<float*>(smem));
 }
 
+// KV compressor of sequence b (layer.cmp): the step appends this rank's new record and, on a closing
+// step, pushes this rank's statistics to the entry's owner; the finalize runs on the owner after all
+// cp statistics have arrived (the task's wait edge) and writes the pools.  Off the critical path:
+// the new entry becomes visible to the next step.
+__device__ inline void op_cmp(const mdc_mega_params& p, int b, bool finalize, unsigned long long phase, unsigned char* smem) {
+  mdc_compress_params c = p.layer.cmp;
+  c.arena = p.arena;
+  c.stats_off += phase_offset(p, phase);
+  c.status = p.status;
+  if (b < 0 || b >= c.B) return;
+  if (c.ratio == 4) {
+    if (finalize) csa_finalize_tile<false>(c, b, *reinterpret_cast<FinalizeSmem*>(smem));
+    else csa_step_tile<false>(c, b, reinterpret_cast<float*>(smem));
+  } else {
+    if (finalize) online_finalize_tile<false>(c, b, *reinterpret_cast<FinalizeSmem*>(smem));
+    else online_step_tile<false>(c, b, reinterpret_cast<float*>(smem));
+  }
+}
+
 // ------------------------------------------------------------------ test ops
 __device__ inline uint32_t test_pattern(int src_rank, int slot, unsigned long long phase, int i) {
   return 0x9e3779b9u * static_cast<uint32_t>(i + 1) + static_cast<uint32_t>(src_rank) * 0x01000193u +
@@ -331,7 +351,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     if (p.trace && tid == 0) tr1 = global_timer_ns();
 
     // ---- the task body
-    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_MERGE_L1A;
+    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_CMP_FIN;
     if (layer_op && (L.B <= 0 || t.c0 < 0 || t.c0 >= L.B)) {  // no (validated) layer behind this queue
       if (tid == 0) report_failure(p.status, MDC_DEV_BAD_OP, t.op, t.c0, 0, 0);
     } else
@@ -363,6 +383,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
           if (L.cp > 1) op_lse_merge<true>(p, t.c0, t.c1, t.c2, cur.phase, smem);
           else op_lse_merge<false>(p, t.c0, t.c1, t.c2, cur.phase, smem);
         }
+        break;
+      case MDC_OP_CMP_STEP:
+      case MDC_OP_CMP_FIN:
+        if (worker) op_cmp(p, t.c0, t.op == MDC_OP_CMP_FIN, cur.phase, smem);
         break;
       case MDC_OP_SLEEP:
         if (tid == 0) {
@@ -433,6 +457,7 @@ int mdc_attrs_megakernel(cudaFuncAttributes* a) { return static_cast<int>(cudaFu
 namespace mdc {
 int logits_check(const mdc_logits_params* p);
 int mla_check(const mdc_sparse_mla_params* p);
+int compress_check(const mdc_compress_params* p, bool finalize);
 
 // Everything a layer op dereferences or sizes shared memory with, checked on the host: a bad
 // configuration comes back as an error code, it never reaches the device.  B == 0 means "no
@@ -465,6 +490,17 @@ static int layer_check(const mdc_mega_params& p) {
   else if (L.logits.page_tokens == 64) need = logits_smem_layout<MDC_FMT_NVFP4, 64>(1, ct, true).total;
   else need = logits_smem_layout<MDC_FMT_NVFP4, 128>(1, ct, true).total;
   if (need > kMegaTileSmem) return MDC_ERR_TOO_LARGE;
+  if (L.cmp.B != 0) {  // compressor tasks: the tiles' own checks, with the fields the kernel fills in
+    mdc_compress_params c = L.cmp;
+    c.arena = p.arena;
+    c.events = p.events;
+    c.wait_budget_ns = p.wait_budget_ns;
+    if (c.B != L.B || c.cp != L.cp || c.rank != L.rank) return MDC_ERR_BAD_SHAPE;
+    rc = compress_check(&c, false);
+    if (rc != MDC_OK) return rc;
+    rc = compress_check(&c, true);
+    if (rc != MDC_OK) return rc;
+  }
   return MDC_OK;
 }
 }  // namespace mdc

@@ -44,8 +44,12 @@ def l1_groups_for(n_chunks: int) -> int:
     return 1 if n_chunks <= 8 else -(-n_chunks // 4)
 
 
-def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1):
-    """Tasks / events of one layer-step for ALL ranks, plus op codes by task name."""
+def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1,
+                    compressor: bool = False):
+    """Tasks / events of one layer-step for ALL ranks, plus op codes by task name.  With `compressor`
+    every rank also runs CMP_STEP(b) (record append + statistics push, notifies cmp_stats[b] on all
+    ranks) and CMP_FIN(b) (entry owner, waits for the cp statistics); they are listed last, so the
+    queues hold them behind the attention path (docs/phase1.4-comm-tasks.md:37-38,52 of the reference)."""
     cross = SCOPE_SYS if cp > 1 else SCOPE_LOCAL
     events, tasks, ops = [], [], {}
     for b in range(B):
@@ -89,13 +93,27 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                     name = f"lse_merge[{r},{b},{hq}]"
                     tasks.append(TaskSpec(name, r, (WaitEdge(f"part[{b}]"),), (), (b, hq, LSE_GROUPS)))
                     ops[name] = N.OP_LSE_MERGE
+    if compressor:
+        events += [EventSpec(f"cmp_stats[{b}]", cross) for b in range(B)]
+        for r in range(cp):
+            for b in range(B):
+                name = f"cmp_step[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"cmp_stats[{b}]", d) for d in range(cp)), (b, 0, 0)))
+                ops[name] = N.OP_CMP_STEP
+            for b in range(B):
+                name = f"cmp_fin[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (WaitEdge(f"cmp_stats[{b}]"),), (), (b, 0, 0)))
+                ops[name] = N.OP_CMP_FIN
     return tasks, events, ops
 
 
-def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1):
+def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1, cmp_stats_bytes: int = 0):
     cand = B * cp * (top_k * 8 + 16)
     inbox = -(-B // cp) * cp * attn_splits * (heads * D_V * 2 + heads * 4)
-    return {"cand": cand, "inbox": inbox}
+    regions = {"cand": cand, "inbox": inbox}
+    if cmp_stats_bytes:
+        regions["cmp_stats"] = B * cp * cmp_stats_bytes
+    return regions
 
 
 @dataclass
@@ -116,7 +134,9 @@ class DsaDecodeLayer:
                  fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
-                 attn_splits: int | None = None):
+                 attn_splits: int | None = None, compressor=None):
+        """compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
+        runs its step / finalize as tasks (bind_compressor() supplies the per-step tensors)."""
         self.B, self.cp, self.rank, self.K, self.H, self.d_qk = B, cp, rank, top_k, heads, d_qk
         self.fmt, self.P, self.max_pages, self.bpc = fmt, page_tokens, max_pages, blocks_per_chunk
         self.n_chunks = -(-max_pages // blocks_per_chunk)
@@ -138,11 +158,18 @@ class DsaDecodeLayer:
         assert cp * attn_splits <= 16, f"cp * attn_splits = {cp * attn_splits} exceeds the 16 slices the LSE merge takes"
         assert 0 <= rank < cp
         self.l1_groups = l1_groups_for(self.n_chunks)
-        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups)
+        self.compressor = compressor
+        if compressor is not None:
+            assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
+        tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups,
+                                             compressor=compressor is not None)
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
         self.dsched = upload_schedule(self.schedule, self.device)
         self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
-        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits), phases, rank, cp, group_name, self.device)
+        from .tiles.compress import stats_bytes
+        cmp_bytes = stats_bytes(compressor.ratio) if compressor is not None else 0
+        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes), phases, rank, cp, group_name,
+                                 self.device)
         dev = self.device
         C, K = self.n_chunks, top_k
         self.cand_v = torch.empty(B, 1, C, K, device=dev)
@@ -197,6 +224,24 @@ class DsaDecodeLayer:
         L.out, L.out_lse = N.ptr(self.out), N.ptr(self.out_lse)
         L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
         self._params, self._inputs = L, x
+
+    def bind_compressor(self, seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, norm_eps: float,
+                        freqs, fp8_scale: float = 1.0) -> None:
+        """Fixes the compressor's per-step tensors (the caller refreshes their contents before each
+        step): seq_len (B,) int32 GLOBAL lengths before the step, the new records of this rank, the slot
+        biases, norm weights and rope table.  Call after bind()."""
+        from .tiles.compress import fill_finalize_params
+        assert self._params is not None and self.compressor is not None
+        st = self.compressor
+        c = N.CompressParams()
+        c.B, c.cp, c.rank, c.q_len, c.ratio = st.B, st.cp, st.rank, st.q_len, st.ratio
+        c.seq_len = N.ptr(seq_len)
+        c.ring_attn, c.ring_idx, c.state = N.ptr(st.ring_attn), N.ptr(st.ring_idx), N.ptr(st.state)
+        c.new_attn, c.new_idx, c.ape_attn, c.ape_idx = N.ptr(new_attn), N.ptr(new_idx), N.ptr(ape_attn), N.ptr(ape_idx)
+        c.stats_off, c.do_push = self.arena.regions["cmp_stats"], 1
+        fill_finalize_params(c, st, norm_w_attn, norm_w_idx, norm_eps, freqs, fp8_scale)
+        self._params.cmp = c
+        self._cmp_keep = (seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, freqs)
 
     def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None) -> None:
         """Launches one layer-step (asynchronous): exactly one kernel launch, nothing else.  The

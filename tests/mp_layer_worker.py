@@ -76,6 +76,47 @@ def main():
     ok &= bool(torch.equal(ref_sel, layer.sel_i))
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    # ---- the compressor as tasks of the same persistent kernel, across the real ranks: 13 steps of the
+    # ratio-4 window machine (3 closing groups), each entry checked on its owner (n % world)
+    from test_gpu_compress import _post_checks
+    from mega_dsa_cp_b200.tiles.compress import CompressorState
+    st = CompressorState(B, world, rank, 4, 128, device=dev)
+    clayer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
+                            kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
+                            group_name=dist.group.WORLD.group_name, device=dev, compressor=st)
+    clayer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx), d(w_idx), d(q_mla), d(kv_loc)))
+    steps = 13
+    rec_a = torch.stack([torch.stack([orc.synth_record(b, p, 512, True) for p in range(steps)]) for b in range(B)])
+    rec_i = torch.stack([torch.stack([orc.synth_record(b, p, 128, True) for p in range(steps)]) for b in range(B)])
+    ape_a, ape_i = orc.synth_bias(512, 8), orc.synth_bias(128, 8)
+    gn = torch.Generator().manual_seed(2)
+    norm_a, norm_i = torch.rand(512, generator=gn) + 0.5, torch.rand(128, generator=gn) + 0.5
+    freqs = orc.make_freqs(256)
+    glen = torch.zeros(B, dtype=torch.int32, device=dev)
+    new_a, new_i = torch.zeros(B, 4 * 512, device=dev), torch.zeros(B, 4 * 128, device=dev)
+    clayer.bind_compressor(glen, new_a, new_i, d(ape_a), d(ape_i), d(norm_a), d(norm_i), 1e-6, d(freqs), fp8_scale=0.02)
+    tally = {"e4m3": 0, "e4m3_off_by_one": 0, "nibbles": 0}
+    dist.barrier()
+    try:
+        for sidx in range(steps):
+            glen.fill_(sidx)
+            new_a.copy_(rec_a[:, sidx])     # the rank that owns position sidx (sidx % world) appends it
+            new_i.copy_(rec_i[:, sidx])
+            clayer.step(wait_budget_ns=5_000_000_000)
+            torch.cuda.synchronize()
+            clayer.check_status()
+            dist.barrier()
+            if (sidx + 1) % 4 == 0:
+                n = sidx // 4
+                if n % world == rank:
+                    for b in range(B):
+                        pa = orc.csa_entry_ref(rec_a[b], ape_a, n, 512)
+                        pi = orc.csa_entry_ref(rec_i[b], ape_i, n, 128)
+                        _post_checks(st, b, n // world, pa, pi, 4 * n, norm_a, norm_i, freqs, 0.02, (world, sidx, b), tally)
+                    ok &= st.k_valid.tolist() == [n // world + 1] * B
+    except AssertionError as e:   # report through the common flag so every rank leaves together
+        print(f"[rank {rank}] compressor check failed: {e}", flush=True)
+        ok = False
     worst = torch.tensor([worst_o, worst_l], device=dev)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     if rank == 0:

@@ -198,3 +198,72 @@ def test_layer_steps_replay_from_a_cuda_graph():
         layer.check_status()
         assert torch.equal(layer.out, want_o) and torch.equal(layer.out_lse, want_l) and torch.equal(layer.sel_i, want_i)
     assert int(layer.dsched.scalars[0]) == 1 + 2 * 61   # one eager step + two replays of 61
+
+
+@pytest.mark.parametrize("ratio", [4, 64])
+def test_layer_step_runs_the_compressor_as_tasks(ratio):
+    """CMP_STEP / CMP_FIN inside the persistent kernel (cp = 1): the layer-step rolls the compressor
+    over closing groups; entries against single-machine pooling and the oracle's post chain (bit for
+    bit for the MXFP4 codes), the attention path's result unchanged."""
+    from dsa_inputs import indexer_case
+    from test_gpu_compress import _post_checks
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from mega_dsa_cp_b200.tiles.compress import CompressorState
+    from oracle import dsa_oracle as orc
+
+    B, S, K, bpc, P, H, DQK = 2, 4096, 512, 16, 64, 128, 576
+    steps = 13 if ratio == 4 else 2 * ratio + 3
+    case = indexer_case(B, S, P, "nvfp4", seed=7)
+    g = torch.Generator().manual_seed(10)
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
+    seq = torch.tensor([S, S - 300], dtype=torch.int32)
+    st = CompressorState(B, 1, 0, ratio, 128 if ratio == 4 else 16,
+                         attn_dtype=torch.float8_e4m3fn if ratio == 4 else torch.bfloat16)
+    layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=32, compressor=st)
+    d = lambda t: t.to(DEV)
+    layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
+    hd_rec = 4 * 512 if ratio == 4 else 2 * 512
+    rec_a = torch.stack([torch.stack([orc.synth_record(b, p, 512, ratio == 4, seed=3) for p in range(steps)]) for b in range(B)])
+    rec_i = torch.stack([torch.stack([orc.synth_record(b, p, 128, True) for p in range(steps)]) for b in range(B)])
+    ape_a = orc.synth_bias(512, 8 if ratio == 4 else ratio)
+    ape_i = orc.synth_bias(128, 8)
+    gn = torch.Generator().manual_seed(2)
+    norm_a, norm_i = torch.rand(512, generator=gn) + 0.5, torch.rand(128, generator=gn) + 0.5
+    freqs = orc.make_freqs(4 * max(ratio, 64))
+    glen = torch.zeros(B, dtype=torch.int32, device=DEV)
+    new_a = torch.zeros(B, hd_rec, device=DEV)
+    new_i = torch.zeros(B, 4 * 128, device=DEV)
+    layer.bind_compressor(glen, new_a, new_i if ratio == 4 else None, d(ape_a), d(ape_i) if ratio == 4 else None,
+                          d(norm_a), d(norm_i) if ratio == 4 else None, 1e-6, d(freqs), fp8_scale=0.02 if ratio == 4 else 1.0)
+    tally = {"e4m3": 0, "e4m3_off_by_one": 0, "nibbles": 0}
+    closed = 0
+    first_out = None
+    for s in range(steps):
+        glen.fill_(s)
+        new_a.copy_(rec_a[:, s])
+        if ratio == 4:
+            new_i.copy_(rec_i[:, s])
+        layer.step()
+        torch.cuda.synchronize()
+        layer.check_status()
+        if first_out is None:
+            first_out = layer.out.clone()
+        if (s + 1) % ratio == 0:
+            n = s // ratio
+            closed += 1
+            for b in range(B):
+                if ratio == 4:
+                    pa = orc.csa_entry_ref(rec_a[b], ape_a, n, 512)
+                    pi = orc.csa_entry_ref(rec_i[b], ape_i, n, 128)
+                    _post_checks(st, b, n, pa, pi, 4 * n, norm_a, norm_i, freqs, 0.02, (ratio, s, b), tally)
+                else:
+                    want = orc.online_entry_ref(rec_a[b], ape_a, n, 512, ratio)
+                    got = st.dbg_attn[b, n].cpu()
+                    assert torch.allclose(got, want, rtol=2e-4, atol=2e-5), (s, b, (got - want).abs().max())
+                    ent = orc.post_attn_bf16(got, norm_a, 1e-6, freqs, n * ratio).float()
+                    assert torch.equal(st.attn_pool[b, n].cpu().float(), ent)
+            assert st.k_valid.tolist() == [n + 1] * B
+    assert closed >= 2
+    assert torch.equal(layer.out, first_out)   # the attention path does not depend on the compressor tasks
