@@ -241,16 +241,11 @@ def build_rank(R, c, seed0=1000):
     pages = S_loc // P
     g = torch.Generator(device=dev).manual_seed(seed0 + rank)
     gq = torch.Generator(device=dev).manual_seed(7)      # replicated tensors: same seed on every rank
-    # the per-step tensors (indexer query, gate weights, attention query) are views of ONE device block,
-    # so that the end-to-end step sends them from pinned host memory in one copy
-    nq, nw, nm = B * 64 * 128 * 2, B * 64 * 4, B * H * DQK * 2
-    dblock = torch.empty(nq + nw + nm, dtype=torch.uint8, device=dev)
-    q_idx = dblock[:nq].view(torch.bfloat16).view(B, 64, 128)
-    w_idx = dblock[nq:nq + nw].view(torch.float32).view(B, 64)
-    q_mla = dblock[nq + nw:].view(torch.bfloat16).view(B, 1, H, DQK)
-    q_idx.copy_(torch.randn(B, 64, 128, generator=gq, device=dev))
-    w_idx.copy_(torch.randn(B, 64, generator=gq, device=dev) / 64.0)
-    q_mla.copy_(torch.randn(B, 1, H, DQK, generator=gq, device=dev) * 0.5)
+    # the per-step query tensors (same values on every rank: the oracle check needs them); a rank feeds the
+    # layer only the sequences it owns, the QPATH task of the step distributes them over NVLink
+    q_idx = torch.randn(B, 64, 128, generator=gq, device=dev).to(torch.bfloat16)
+    w_idx = (torch.randn(B, 64, generator=gq, device=dev) / 64.0).contiguous()
+    q_mla = (torch.randn(B, 1, H, DQK, generator=gq, device=dev) * 0.5).to(torch.bfloat16)
     seq_loc = torch.full((B,), S_loc, dtype=torch.int32, device=dev)
     layers, inputs = [], []
     for _ in range(c["copies"]):   # rotate over cache copies so every step streams from HBM
@@ -261,11 +256,11 @@ def build_rank(R, c, seed0=1000):
         kv = (torch.randn(B * S_loc, 1, DQK, generator=g, device=dev) * 0.5).to(torch.bfloat16)
         layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
                                blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S_loc,
-                               group_name=R.group_name, device=dev)
-        layer.bind(LayerInputs(cache, bt, seq_loc, q_idx, w_idx, q_mla, kv))
+                               group_name=R.group_name, device=dev, distribute_q=True)
+        layer.bind(LayerInputs(cache, bt, seq_loc, q_idx[rank::world], w_idx[rank::world], q_mla[rank::world], kv))
         layers.append(layer)
         inputs.append((cache, bt, kv))
-    return layers, inputs, dblock, (q_idx, w_idx, q_mla)
+    return layers, inputs, (q_idx, w_idx, q_mla)
 
 
 def parity_block(R, c, layer, inp, q):
@@ -360,7 +355,7 @@ def run_layer(args):
     world, rank, dev = R.world, R.rank, R.dev
     c = cp_config(world)
     B, H, DQK = c["B"], c["H"], c["d_qk"]
-    layers, inputs, dblock, q = build_rank(R, c)
+    layers, inputs, q = build_rank(R, c)
     R.barrier()
     torch.cuda.synchronize()
 
@@ -394,13 +389,13 @@ def run_layer(args):
 
     # end to end through DsaDecodeLayer: the step's query block comes from pinned host memory, the
     # owned output rows go back to pinned host memory, both inside the timed region
-    hblock = dblock.cpu().pin_memory()
+    hblock = layers[0].q_stage.cpu().pin_memory()     # [q_idx | w | q_mla] of the sequences this rank owns
     owned = layers[0].owned_rows()
     h_out = torch.empty(len(owned), H, 512, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(i):
-        dblock.copy_(hblock, non_blocking=True)
         l = layers[i % len(layers)]
+        l.q_stage.copy_(hblock, non_blocking=True)
         l.step()
         h_out.copy_(l.out, non_blocking=True)   # the layer keeps only its owned rows: one contiguous copy
         torch.cuda.current_stream().synchronize()
@@ -440,14 +435,14 @@ def run_layer(args):
             "data": "synthetic",
             "config": {"workload": f"full DSA decode layer-step, CP={world}: B={B}, ctx 131072 sharded token-interleaved "
                                    f"({c['S'] // world} tokens/rank/seq), indexer + top-k 2048 + sparse MLA (128 heads, "
-                                   "512+64) + LSE merge, one persistent kernel per rank, P2P stores into symmetric memory",
+                                   "512+64) + LSE merge, one persistent kernel per rank, P2P stores into symmetric memory (query blocks, candidates, partials)",
                        "l2": f"rotating {c['copies']} cache copies per rank (index cache + KV pool 1.3 GB each > 126 MB L2)",
                        "parallelism": f"cp{world}", "attn_splits": layers[0].attn_splits},
             "step_us": ms_step * 1e3,
             "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": hblock.numel(),
                     "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms,
-                    "api": "DsaDecodeLayer.step() with the query block sent from pinned host memory and the owned "
-                           "output rows read back, per rank"},
+                    "api": "DsaDecodeLayer.step(): each rank sends the query block of the sequences it owns from pinned host "
+                           "memory (the step's QPATH tasks spread it over NVLink) and reads its owned output rows back"},
             "gpu_launches": args.steps, "kernels_per_step": 1,
             "parity": parity,
             "timeline_rank0": timeline, "lse_merge_latency": lse_lat,
@@ -631,7 +626,10 @@ def cpu_layer_sample(world, max_steps=10, budget_s=20.0):
     import torch
     from oracle import dsa_oracle as orc
 
-    torch.set_num_threads(max(1, os.cpu_count() or 1))   # torchrun pins OMP_NUM_THREADS=1
+    # torchrun pins OMP_NUM_THREADS=1; inside an N-rank GPU run the other ranks' host threads sit in a barrier
+    # and keep a core each, so they are left out (a thread that has to share its core stalls the whole team)
+    busy = int(os.environ.get("WORLD_SIZE", "1")) - 1 if os.environ.get("RANK") is not None else 0
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) - busy))
     cc = cp_config(world)
     S, K, H, DQK = cc["S"], cc["top_k"], cc["H"], cc["d_qk"]
     g = torch.Generator().manual_seed(0)

@@ -331,6 +331,7 @@ int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* str
 #define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
 #define MDC_OP_CMP_STEP 7   /* c0 = b: compressor step of layer.cmp (record append, statistics push to the entry owner)  */
 #define MDC_OP_CMP_FIN 8    /* c0 = b: entry owner merges the cp statistics and writes its pools                       */
+#define MDC_OP_QPATH 9      /* c0 = b (owned): this step's query block of sequence b -> every rank's arena (q_ready[b]) */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
 #define MDC_OP_PUSH 18      /* c1 = dst rank, c2 = slot: bulk push a pattern (test op) */
@@ -372,6 +373,16 @@ typedef struct {
    * fields of cmp (events, ev_base_id, phase, wait_budget_ns are not used); cmp.stats_off is the offset
    * of the statistics region inside ONE phase of the arena (the kernel adds the phase rotation). */
   mdc_compress_params cmp;
+  /* Query path (the reference's QPATH_STUB task and q_ready event, docs/phase1.4-comm-tasks.md:37,48,117:
+   * "the host supplies q").  q_stage == NULL: logits.q / logits.weights / mla.q are read as given
+   * (replicated on every rank by the caller).  Else the owner of sequence b (b % cp) holds that
+   * sequence's per-step block in q_stage, laid out over its owned sequences j = b / cp as
+   *   [ (n_owned, 64, 128) bf16 indexer q | (n_owned, 64) f32 gate weights | (n_owned, H, d_qk) bf16 attention q ],
+   * and QPATH(b) stores it into the q region of EVERY rank's arena (offset q_off inside a phase, same
+   * three arrays over all B sequences); the indexer and attention tiles then read q from the arena.
+   * Each rank receives 1/cp of the bytes from its host instead of all of them. */
+  const void* q_stage;
+  int64_t q_off;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

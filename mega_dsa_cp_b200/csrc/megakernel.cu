@@ -91,9 +91,63 @@ __device__ inline int compact_local_ids(const int32_t* ids, int n, int cp, int r
 }
 
 // ------------------------------------------------------------------ layer ops
+// Byte sizes of one sequence's query arrays and the q region's sub-offsets (arrays over all B sequences).
+__device__ __host__ inline int64_t q_idx_bytes() { return 64 * 128 * 2; }
+__device__ __host__ inline int64_t q_w_bytes() { return 64 * 4; }
+__device__ __host__ inline int64_t q_mla_bytes(const mdc_layer_params& L) { return static_cast<int64_t>(L.H) * L.mla.d_qk * 2; }
+
+// Owner of sequence b: its query block from the staging buffer -> the q region of every rank's arena.
+// 16-byte loads from local memory, 16-byte posted stores to each destination (own arena included).
+__device__ inline void op_qpath(const mdc_mega_params& p, int b, unsigned long long phase) {
+  const mdc_layer_params& L = p.layer;
+  if (!L.q_stage || b % L.cp != L.rank) return;
+  const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
+                         p.arena.mc_base};
+  const int n_owned = ceil_div(L.B - L.rank, L.cp), j = b / L.cp;
+  const unsigned char* st = static_cast<const unsigned char*>(L.q_stage);
+  const int64_t src_off[3] = {j * q_idx_bytes(), n_owned * q_idx_bytes() + j * q_w_bytes(),
+                              n_owned * (q_idx_bytes() + q_w_bytes()) + j * q_mla_bytes(L)};
+  const int64_t base = phase_offset(p, phase) + L.q_off;
+  const int64_t dst_off[3] = {base + b * q_idx_bytes(), base + L.B * q_idx_bytes() + b * q_w_bytes(),
+                              base + L.B * (q_idx_bytes() + q_w_bytes()) + b * q_mla_bytes(L)};
+  const int64_t len[3] = {q_idx_bytes(), q_w_bytes(), q_mla_bytes(L)};
+#pragma unroll 1
+  for (int a = 0; a < 3; ++a) {
+    const uint4* src = reinterpret_cast<const uint4*>(st + src_off[a]);
+    const int n16 = static_cast<int>(len[a] / 16);
+#pragma unroll 1
+    for (int i0 = threadIdx.x; i0 < n16; i0 += 4 * kBlockThreads) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = i0 + u * kBlockThreads < n16 ? __ldg(src + i0 + u * kBlockThreads) : make_uint4(0, 0, 0, 0);
+      for (int dst = 0; dst < L.cp; ++dst) {
+        uint4* d = reinterpret_cast<uint4*>(arena.peer_ptr(dst_off[a], dst));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i0 + u * kBlockThreads < n16) d[i0 + u * kBlockThreads] = v[u];
+      }
+    }
+  }
+}
+
+// the tiles' parameters with the query pointers redirected to this phase's q region of the own arena
+__device__ inline void redirect_q(const mdc_mega_params& p, unsigned long long phase, mdc_logits_params* lp,
+                                  mdc_sparse_mla_params* mp) {
+  const mdc_layer_params& L = p.layer;
+  if (!L.q_stage) return;
+  const unsigned char* base = static_cast<const unsigned char*>(p.arena.base) + phase_offset(p, phase) + L.q_off;
+  if (lp) {
+    lp->q = base;
+    lp->weights = reinterpret_cast<const float*>(base + L.B * q_idx_bytes());
+  }
+  if (mp) mp->q = base + L.B * (q_idx_bytes() + q_w_bytes());
+}
+
 template <int FMT, int PAGE>
-__device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned char* smem) {
-  logits_tile<FMT, PAGE, 1, 2, 1>(p.layer.logits, b, chunk, smem);
+__device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned long long phase, unsigned char* smem) {
+  mdc_logits_params lp = p.layer.logits;
+  redirect_q(p, phase, &lp, nullptr);
+  logits_tile<FMT, PAGE, 1, 2, 1>(lp, b, chunk, smem);
 }
 
 // first level of a two-level local merge: the chunk lists of group g of sequence b -> one list
@@ -201,6 +255,7 @@ __device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, int spl
   // (the owner's), or the merged denominator would count the sink cp times.
   mdc_sparse_mla_params mp = L.mla;
   if (L.rank != owner) mp.attn_sink = nullptr;
+  redirect_q(p, phase, nullptr, &mp);
   if (mp.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
     if (mp.d_qk == 576) mla_umma_tile<576>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
     else mla_umma_tile<512>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
@@ -351,7 +406,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     if (p.trace && tid == 0) tr1 = global_timer_ns();
 
     // ---- the task body
-    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_CMP_FIN;
+    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_QPATH;
     if (layer_op && (L.B <= 0 || t.c0 < 0 || t.c0 >= L.B)) {  // no (validated) layer behind this queue
       if (tid == 0) report_failure(p.status, MDC_DEV_BAD_OP, t.op, t.c0, 0, 0);
     } else
@@ -359,9 +414,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
       case MDC_OP_NOP:
         break;
       case MDC_OP_LOGITS:
-        if (L.logits.fmt == MDC_FMT_MXFP4) op_logits<MDC_FMT_MXFP4, 128>(p, t.c0, t.c1, smem);
-        else if (L.logits.page_tokens == 64) op_logits<MDC_FMT_NVFP4, 64>(p, t.c0, t.c1, smem);
-        else op_logits<MDC_FMT_NVFP4, 128>(p, t.c0, t.c1, smem);
+        if (L.logits.fmt == MDC_FMT_MXFP4) op_logits<MDC_FMT_MXFP4, 128>(p, t.c0, t.c1, cur.phase, smem);
+        else if (L.logits.page_tokens == 64) op_logits<MDC_FMT_NVFP4, 64>(p, t.c0, t.c1, cur.phase, smem);
+        else op_logits<MDC_FMT_NVFP4, 128>(p, t.c0, t.c1, cur.phase, smem);
+        break;
+      case MDC_OP_QPATH:
+        if (worker) op_qpath(p, t.c0, cur.phase);
         break;
       case MDC_OP_MERGE_L1:
         if (worker) op_merge_l1(p, t.c0, cur.phase, smem);
@@ -490,6 +548,8 @@ static int layer_check(const mdc_mega_params& p) {
   else if (L.logits.page_tokens == 64) need = logits_smem_layout<MDC_FMT_NVFP4, 64>(1, ct, true).total;
   else need = logits_smem_layout<MDC_FMT_NVFP4, 128>(1, ct, true).total;
   if (need > kMegaTileSmem) return MDC_ERR_TOO_LARGE;
+  if (L.q_stage && ((reinterpret_cast<uintptr_t>(L.q_stage) | static_cast<uintptr_t>(L.q_off)) & 15)) return MDC_ERR_BAD_ALIGN;
+  if (L.q_stage && (L.logits.q_fmt != MDC_Q_BF16 || L.mla.kv_dtype != MDC_DT_BF16)) return MDC_ERR_BAD_FORMAT;
   if (L.cmp.B != 0) {  // compressor tasks: the tiles' own checks, with the fields the kernel fills in
     mdc_compress_params c = L.cmp;
     c.arena = p.arena;

@@ -45,7 +45,7 @@ def l1_groups_for(n_chunks: int) -> int:
 
 
 def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1,
-                    compressor: bool = False):
+                    compressor: bool = False, qpath: bool = False):
     """Tasks / events of one layer-step for ALL ranks, plus op codes by task name.  With `compressor`
     every rank also runs CMP_STEP(b) (record append + statistics push, notifies cmp_stats[b] on all
     ranks) and CMP_FIN(b) (entry owner, waits for the cp statistics); they are listed last, so the
@@ -59,12 +59,20 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                    EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
     n_attn = 2 * (heads // 64)
     per = -(-n_chunks // l1_groups)
+    if qpath:   # QPATH(b) on the owner of b: the step's query block -> every rank's arena, then q_ready[b]
+        events += [EventSpec(f"q_ready[{b}]", cross) for b in range(B)]
     for r in range(cp):
+        if qpath:
+            for b in range(r, B, cp):
+                name = f"qpath[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"q_ready[{b}]", d) for d in range(cp)), (b, 0, 0)))
+                ops[name] = N.OP_QPATH
         for b in range(B):
             for c in range(n_chunks):
                 name = f"logits[{r},{b},{c}]"
                 ev = f"l1a[{b},{c // per}]" if l1_groups > 1 else f"l1[{b}]"
-                tasks.append(TaskSpec(name, r, (), (NotifyEdge(ev, r),), (b, c, 0)))
+                waits = (WaitEdge(f"q_ready[{b}]"),) if qpath else ()
+                tasks.append(TaskSpec(name, r, waits, (NotifyEdge(ev, r),), (b, c, 0)))
                 ops[name] = N.OP_LOGITS
         if l1_groups > 1:
             for b in range(B):
@@ -107,10 +115,18 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
     return tasks, events, ops
 
 
-def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1, cmp_stats_bytes: int = 0):
+def q_block_bytes(heads: int = 128, d_qk: int = 576) -> int:
+    """One sequence's per-step query block: bf16 indexer q (64 x 128), fp32 gate weights (64), bf16 attention q."""
+    return 64 * 128 * 2 + 64 * 4 + heads * d_qk * 2
+
+
+def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1, cmp_stats_bytes: int = 0,
+                  q_bytes: int = 0):
     cand = B * cp * (top_k * 8 + 16)
     inbox = -(-B // cp) * cp * attn_splits * (heads * D_V * 2 + heads * 4)
     regions = {"cand": cand, "inbox": inbox}
+    if q_bytes:
+        regions["q"] = B * q_bytes
     if cmp_stats_bytes:
         regions["cmp_stats"] = B * cp * cmp_stats_bytes
     return regions
@@ -121,7 +137,8 @@ class LayerInputs:
     kv_pages: torch.Tensor      # (num_pages, page_bytes) uint8 index-K cache of this rank
     block_table: torch.Tensor   # (B, max_pages) int32
     seq_lens: torch.Tensor      # (B,) int32 rank-local token counts
-    q_idx: torch.Tensor         # (B, 64, 128) bf16 indexer query (replicated on all ranks)
+    q_idx: torch.Tensor         # (B, 64, 128) bf16 indexer query (replicated on all ranks); with distribute_q the
+                                # three query tensors hold the OWNED sequences only (b = rank, rank + cp, ...) or are None
     w_idx: torch.Tensor         # (B, 64) fp32 head-gate weights
     q_mla: torch.Tensor         # (B, 1, H, d_qk) bf16 attention query (replicated)
     kv_mla: torch.Tensor        # (B * kv_seq_stride, 1, d_qk) bf16 local KV rows
@@ -134,8 +151,10 @@ class DsaDecodeLayer:
                  fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
-                 attn_splits: int | None = None, compressor=None):
-        """compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
+                 attn_splits: int | None = None, compressor=None, distribute_q: bool = False):
+        """distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
+        then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
+        compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
         runs its step / finalize as tasks (bind_compressor() supplies the per-step tensors)."""
         self.B, self.cp, self.rank, self.K, self.H, self.d_qk = B, cp, rank, top_k, heads, d_qk
         self.fmt, self.P, self.max_pages, self.bpc = fmt, page_tokens, max_pages, blocks_per_chunk
@@ -162,14 +181,27 @@ class DsaDecodeLayer:
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
         tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups,
-                                             compressor=compressor is not None)
+                                             compressor=compressor is not None, qpath=distribute_q)
+        self.distribute_q = distribute_q
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
         self.dsched = upload_schedule(self.schedule, self.device)
         self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
         from .tiles.compress import stats_bytes
         cmp_bytes = stats_bytes(compressor.ratio) if compressor is not None else 0
-        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes), phases, rank, cp, group_name,
-                                 self.device)
+        self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes,
+                                               q_block_bytes(heads, d_qk) if distribute_q else 0),
+                                 phases, rank, cp, group_name, self.device)
+        self.n_owned = len(range(rank, B, cp))
+        # distribute_q: the owned sequences' query blocks, one contiguous block [q_idx | w | q_mla] that a
+        # caller fills from the host in one copy (views below); sequence b = j * cp + rank is entry j
+        self.q_stage = None
+        if distribute_q:
+            n = self.n_owned
+            nq, nw, nm = n * 64 * 128 * 2, n * 64 * 4, n * heads * d_qk * 2
+            self.q_stage = torch.zeros(nq + nw + nm, dtype=torch.uint8, device=self.device)
+            self.q_idx_owned = self.q_stage[:nq].view(torch.bfloat16).view(n, 64, 128)
+            self.w_idx_owned = self.q_stage[nq:nq + nw].view(torch.float32).view(n, 64)
+            self.q_mla_owned = self.q_stage[nq + nw:].view(torch.bfloat16).view(n, 1, heads, d_qk)
         dev = self.device
         C, K = self.n_chunks, top_k
         self.cand_v = torch.empty(B, 1, C, K, device=dev)
@@ -195,17 +227,28 @@ class DsaDecodeLayer:
     def bind(self, x: LayerInputs) -> None:
         """Fixes the input tensors (their addresses are baked into the launch parameters)."""
         B, K = self.B, self.K
-        assert x.q_idx.dtype == torch.bfloat16 and x.q_mla.dtype == torch.bfloat16
+        if self.distribute_q:
+            # q comes through the arena: x.q_idx / x.w_idx / x.q_mla, when given, are the OWNED sequences'
+            # tensors and are copied into the staging block once here (refresh q_stage before later steps)
+            if x.q_idx is not None:
+                self.q_idx_owned.copy_(x.q_idx)
+                self.w_idx_owned.copy_(x.w_idx)
+                self.q_mla_owned.copy_(x.q_mla)
+            qbase = self.arena.tensor.data_ptr() + self.arena.regions["q"]
+            q_ptr, w_ptr, qm_ptr = qbase, qbase + B * 64 * 128 * 2, qbase + B * (64 * 128 * 2 + 64 * 4)
+        else:
+            assert x.q_idx.dtype == torch.bfloat16 and x.q_mla.dtype == torch.bfloat16
+            q_ptr, w_ptr, qm_ptr = N.ptr(x.q_idx), N.ptr(x.w_idx), N.ptr(x.q_mla)
         lp = N.LogitsParams(
             kv_pages=N.ptr(x.kv_pages), num_pages=x.kv_pages.shape[0], page_tokens=self.P,
             fmt=N.FMT_MXFP4 if self.fmt == "mxfp4" else N.FMT_NVFP4, q_fmt=N.Q_BF16,
-            q=N.ptr(x.q_idx), q_sf=None, weights=N.ptr(x.w_idx), block_table=N.ptr(x.block_table),
+            q=q_ptr, q_sf=None, weights=w_ptr, block_table=N.ptr(x.block_table),
             max_pages=self.max_pages, seq_lens=N.ptr(x.seq_lens), logits=None, logits_stride=0,
             cand_v=N.ptr(self.cand_v), cand_i=N.ptr(self.cand_i), cand_c=N.ptr(self.cand_c), top_k=K,
             B=B, q_len=1, heads=64, blocks_per_chunk=self.bpc, n_chunks=self.n_chunks, window_exclude=0,
             id_mul=self.cp, id_add=self.rank, status=N.ptr(self.status))
         mp = N.SparseMlaParams(
-            q=N.ptr(x.q_mla), kv_win=None, kv_cmp=N.ptr(x.kv_mla), pt_win=None, pt_cmp=N.ptr(self.pt_local),
+            q=qm_ptr, kv_win=None, kv_cmp=N.ptr(x.kv_mla), pt_win=None, pt_cmp=N.ptr(self.pt_local),
             k_valid=N.ptr(self.k_valid), win_valid=None, attn_sink=None, o=N.ptr(self.out), lse=N.ptr(self.out_lse),
             o_stride=self.H * D_V, lse_stride=self.H, ws_o=None, ws_lse=None,
             B=B, q_len=1, H=self.H, d_qk=self.d_qk, d_v=D_V, pages_win=0, pages_cmp=x.kv_mla.shape[0], page_cmp=1,
@@ -223,6 +266,8 @@ class DsaDecodeLayer:
         L.sel_v, L.sel_i, L.sel_c = N.ptr(self.sel_v), N.ptr(self.sel_i), N.ptr(self.sel_c)
         L.out, L.out_lse = N.ptr(self.out), N.ptr(self.out_lse)
         L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
+        if self.distribute_q:
+            L.q_stage, L.q_off = N.ptr(self.q_stage), self.arena.regions["q"]
         self._params, self._inputs = L, x
 
     def bind_compressor(self, seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, norm_eps: float,

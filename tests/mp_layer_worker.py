@@ -39,10 +39,12 @@ def main():
     kv_loc = kv[:, rank::world].reshape(B * S_loc, 1, DQK).contiguous()
     dev = torch.device("cuda", torch.cuda.current_device())
     d = lambda t: t.to(dev)
+    # the query block of a sequence comes from its owner only (QPATH task: P2P stores into every rank's arena)
     layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
                            kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
-                           group_name=dist.group.WORLD.group_name, device=dev)
-    layer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx), d(w_idx), d(q_mla), d(kv_loc)))
+                           group_name=dist.group.WORLD.group_name, device=dev, distribute_q=True)
+    layer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx[rank::world]), d(w_idx[rank::world]),
+                           d(q_mla[rank::world]), d(kv_loc)))
     dist.barrier()
     for _ in range(3):
         layer.step(wait_budget_ns=5_000_000_000)

@@ -116,8 +116,8 @@ def test_bulk_push_and_verify_world1():
     assert arena.tensor.view(torch.int32).abs().sum().item() != 0
 
 
-@pytest.mark.parametrize("B,S,K,bpc", [(2, 4096, 512, 16), (3, 8192, 2048, 32)])
-def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
+@pytest.mark.parametrize("B,S,K,bpc,qpath", [(2, 4096, 512, 16, False), (3, 8192, 2048, 32, False), (3, 8192, 2048, 32, True)])
+def test_decode_layer_cp1_matches_oracle(B, S, K, bpc, qpath):
     from dsa_inputs import indexer_case
     from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
     from oracle import dsa_oracle as orc
@@ -129,7 +129,7 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
     kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
     seq = torch.tensor([S - 100 * b for b in range(B)], dtype=torch.int32)
     layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
-                           out_dtype=torch.float32, n_ctas=64)
+                           out_dtype=torch.float32, n_ctas=64, distribute_q=qpath)   # qpath: q through the QPATH task
     d = lambda t: t.to(DEV)
     layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
     for phase in range(2):   # the second launch replays with the phase bumped
@@ -145,7 +145,7 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc):
     assert int(trace[0]) == n_tasks
     e = trace[4:4 + 4 * n_tasks].reshape(n_tasks, 4).cpu()
     assert bool((e[:, 1] <= e[:, 2]).all()) and bool((e[:, 2] <= e[:, 3]).all())
-    assert set(((e[:, 0] >> 24) & 0xff).tolist()) <= {1, 2, 3, 4, 5, 6}
+    assert set(((e[:, 0] >> 24) & 0xff).tolist()) <= {1, 2, 3, 4, 5, 6, 9}
     data, sf = orc.split_index_pages(case["fused"], "nvfp4", P)
     kd_all = orc.dequant_fp4(data, sf, "nvfp4").reshape(-1, P, 128)
     for b in range(B):
