@@ -332,6 +332,7 @@ int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* str
 #define MDC_OP_CMP_STEP 7   /* c0 = b: compressor step of layer.cmp (record append, statistics push to the entry owner)  */
 #define MDC_OP_CMP_FIN 8    /* c0 = b: entry owner merges the cp statistics and writes its pools                       */
 #define MDC_OP_QPATH 9      /* c0 = b (owned): this step's query block of sequence b -> every rank's arena (q_ready[b]) */
+#define MDC_OP_KVWRITE 10   /* c0 = b: the step's new token of sequence b -> index-K page and KV row of its owner (kv_written[b]) */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
 #define MDC_OP_PUSH 18      /* c1 = dst rank, c2 = slot: bulk push a pattern (test op) */
@@ -383,6 +384,19 @@ typedef struct {
    * Each rank receives 1/cp of the bytes from its host instead of all of them. */
   const void* q_stage;
   int64_t q_off;
+  /* New-token write (the reference's KVWRITE task and kv_written event, docs/phase1.4-comm-tasks.md:37,49,
+   * 114-116: "host-supplied new token KV / index records are written into the pools, the valid counters
+   * updated").  kvw_glen == NULL: no KVWRITE tasks.  Else every rank runs KVWRITE(b): with t = kvw_glen[b]
+   * (global length before the step, the same on every rank), the rank with t % cp == rank quantises
+   * kvw_k_idx[b] to the cache format and writes it into slot t / cp of its index-K cache (page
+   * block_table[b][slot / page_tokens], which must be allocated), copies kvw_kv[b] to KV pool row
+   * b * kv_seq_stride + slot, and sets logits.seq_lens[b] = slot + 1 (seq_lens is written here).  The
+   * indexer tasks of b wait for kv_written[b]: the new token takes part in this step's selection.
+   * kvw_advance != 0: the task then adds 1 to kvw_glen[b], so a replayed launch writes the next token. */
+  const float* kvw_k_idx;       /* (B, 128) fp32, replicated on every rank       */
+  const void* kvw_kv;           /* (B, d_qk) elements of mla.kv_dtype, replicated */
+  int32_t* kvw_glen;            /* (B,)                                          */
+  int32_t kvw_advance;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

@@ -95,6 +95,7 @@ class LayerParams(C.Structure):
         ("sel_v", p_void), ("sel_i", p_void), ("sel_c", p_void), ("out", p_void), ("out_lse", p_void),
         ("out_dtype", i32), ("l1_groups", i32), ("mid_v", p_void), ("mid_i", p_void), ("mid_c", p_void),
         ("cmp", CompressParams), ("q_stage", p_void), ("q_off", i64),
+        ("kvw_k_idx", p_void), ("kvw_kv", p_void), ("kvw_glen", p_void), ("kvw_advance", i32),
     ]
 
 
@@ -109,7 +110,7 @@ class MegaParams(C.Structure):
 
 
 OP_NOP, OP_LOGITS, OP_MERGE_L1, OP_MERGE_L2, OP_ATTN, OP_LSE_MERGE, OP_MERGE_L1A = 0, 1, 2, 3, 4, 5, 6
-OP_CMP_STEP, OP_CMP_FIN, OP_QPATH = 7, 8, 9
+OP_CMP_STEP, OP_CMP_FIN, OP_QPATH, OP_KVWRITE = 7, 8, 9, 10
 OP_SLEEP, OP_LOG, OP_PUSH, OP_VERIFY = 16, 17, 18, 19
 DEV_WAIT_TIMEOUT, DEV_COPY_TIMEOUT, DEV_BAD_INDEX, DEV_BAD_OP = 1, 2, 3, 4
 

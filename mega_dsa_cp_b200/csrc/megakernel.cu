@@ -130,6 +130,42 @@ __device__ inline void op_qpath(const mdc_mega_params& p, int b, unsigned long l
   }
 }
 
+// The step's new token of sequence b: on the rank that owns its position, the index-K record is
+// quantised into the paged cache, the KV row is copied into the pool and the rank-local length grows
+// by one; every rank then (optionally) advances its copy of the global length.
+__device__ inline void op_kvwrite(const mdc_mega_params& p, int b) {
+  const mdc_layer_params& L = p.layer;
+  if (!L.kvw_glen) return;
+  const mdc_logits_params& lp = L.logits;
+  const int tid = threadIdx.x;
+  const int t = L.kvw_glen[b];
+  if (t >= 0 && t % L.cp == L.rank) {
+    const int slot = t / L.cp, P = lp.page_tokens;
+    const int blk = slot / P, tok = slot % P;
+    const int32_t page = blk < lp.max_pages ? lp.block_table[static_cast<int64_t>(b) * lp.max_pages + blk] : -1;
+    if (page < 0 || page >= lp.num_pages || slot >= L.kv_seq_stride) {
+      if (tid == 0) report_failure(p.status, MDC_DEV_BAD_INDEX, page, slot, 0, 0);
+    } else {
+      if (tid < 32) {  // one warp: 128 fp32 -> 64 code bytes + block scales of the cache format
+        const float4 v = reinterpret_cast<const float4*>(L.kvw_k_idx + static_cast<int64_t>(b) * 128)[tid];
+        const float x[4] = {v.x, v.y, v.z, v.w};
+        const int sf_per_tok = lp.fmt == MDC_FMT_MXFP4 ? 4 : 8;
+        uint8_t* pg = const_cast<uint8_t*>(lp.kv_pages) + static_cast<int64_t>(page) * (P * 64 + P * sf_per_tok);
+        uint8_t* sf = lp.fmt == MDC_FMT_MXFP4 ? pg + P * 64 + (tok % 32) * 16 + (tok / 32) * 4 : pg + P * 64 + tok * 8;
+        fp4_quant_warp(x, pg + tok * 64, sf, lp.fmt);
+      }
+      const int row_bytes = L.mla.d_qk * (L.mla.kv_dtype == MDC_DT_E4M3 ? 1 : 2);
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(L.kvw_kv) + static_cast<int64_t>(b) * row_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(const_cast<void*>(L.mla.kv_cmp)) +
+                                            (static_cast<int64_t>(b) * L.kv_seq_stride + slot) * row_bytes);
+      for (int i = tid; i < row_bytes / 16; i += kBlockThreads) dst[i] = src[i];
+      if (tid == 0) const_cast<int32_t*>(lp.seq_lens)[b] = slot + 1;
+    }
+  }
+  sync_workers();
+  if (tid == 0 && L.kvw_advance) L.kvw_glen[b] = t + 1;
+}
+
 // the tiles' parameters with the query pointers redirected to this phase's q region of the own arena
 __device__ inline void redirect_q(const mdc_mega_params& p, unsigned long long phase, mdc_logits_params* lp,
                                   mdc_sparse_mla_params* mp) {
@@ -406,7 +442,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     if (p.trace && tid == 0) tr1 = global_timer_ns();
 
     // ---- the task body
-    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_QPATH;
+    const bool layer_op = t.op >= MDC_OP_LOGITS && t.op <= MDC_OP_KVWRITE;
     if (layer_op && (L.B <= 0 || t.c0 < 0 || t.c0 >= L.B)) {  // no (validated) layer behind this queue
       if (tid == 0) report_failure(p.status, MDC_DEV_BAD_OP, t.op, t.c0, 0, 0);
     } else
@@ -420,6 +456,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         break;
       case MDC_OP_QPATH:
         if (worker) op_qpath(p, t.c0, cur.phase);
+        break;
+      case MDC_OP_KVWRITE:
+        if (worker) op_kvwrite(p, t.c0);
         break;
       case MDC_OP_MERGE_L1:
         if (worker) op_merge_l1(p, t.c0, cur.phase, smem);
@@ -550,6 +589,11 @@ static int layer_check(const mdc_mega_params& p) {
   if (need > kMegaTileSmem) return MDC_ERR_TOO_LARGE;
   if (L.q_stage && ((reinterpret_cast<uintptr_t>(L.q_stage) | static_cast<uintptr_t>(L.q_off)) & 15)) return MDC_ERR_BAD_ALIGN;
   if (L.q_stage && (L.logits.q_fmt != MDC_Q_BF16 || L.mla.kv_dtype != MDC_DT_BF16)) return MDC_ERR_BAD_FORMAT;
+  if (L.kvw_glen) {
+    if (!L.kvw_k_idx || !L.kvw_kv || !L.logits.seq_lens) return MDC_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(L.kvw_k_idx) | reinterpret_cast<uintptr_t>(L.kvw_kv)) & 15) return MDC_ERR_BAD_ALIGN;
+    if (L.mla.page_cmp != 1) return MDC_ERR_BAD_SHAPE;   // the new row goes to pool row b * kv_seq_stride + slot
+  }
   if (L.cmp.B != 0) {  // compressor tasks: the tiles' own checks, with the fields the kernel fills in
     mdc_compress_params c = L.cmp;
     c.arena = p.arena;

@@ -276,10 +276,10 @@ __device__ inline void store_attn_entry(const mdc_compress_params& p, int b, int
   }
 }
 
+__device__ inline void fp4_quant_warp(const float (&x)[4], uint8_t* data, uint8_t* sf, int fmt);
+
 // warp 0: staged 128-point Hadamard of y[0..127] (4 consecutive elements per
-// lane: strides 1, 2 in-thread, then lane masks 1..16), scaled, rounded through
-// bf16, then block-scaled FP4.  Writes 64 code bytes at `data` and the scales at
-// `sf` (MXFP4: one byte per 8 lanes at sf[lane/8]; NVFP4: per 4 lanes at sf[lane/4]).
+// lane: strides 1, 2 in-thread, then lane masks 1..16), scaled, then block-scaled FP4 (fp4_quant_warp).
 __device__ inline void hadamard_quant_warp(const float* y, uint8_t* data, uint8_t* sf, int fmt) {
   const int lane = threadIdx.x & 31;
   const float x0 = y[4 * lane], x1 = y[4 * lane + 1], x2 = y[4 * lane + 2], x3 = y[4 * lane + 3];
@@ -294,10 +294,22 @@ __device__ inline void hadamard_quant_warp(const float* y, uint8_t* data, uint8_
       d[i] = hi ? o - d[i] : d[i] + o;
     }
   }
+  float q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = d[i] * kHadamardScale;
+  fp4_quant_warp(q, data, sf, fmt);
+}
+
+// One warp quantises a 128-wide vector (lane l holds elements 4l .. 4l+3) to block-scaled FP4: values
+// rounded through bf16, scale from the block maximum / 6 (MXFP4: UE8M0 ceil per 32 elements; NVFP4:
+// UE4M3 round-to-nearest per 16), E2M1 codes with ties to the even code.  Writes 64 code bytes at `data`
+// and the scales at `sf` (MXFP4: one byte per 8 lanes at sf[lane/8]; NVFP4: per 4 lanes at sf[lane/4]).
+__device__ inline void fp4_quant_warp(const float (&x)[4], uint8_t* data, uint8_t* sf, int fmt) {
+  const int lane = threadIdx.x & 31;
   float q[4], amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    q[i] = __bfloat162float(__float2bfloat16_rn(d[i] * kHadamardScale));
+    q[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
     amax = fmaxf(amax, fabsf(q[i]));
   }
   const int group_lanes = (fmt == MDC_FMT_MXFP4) ? 8 : 4;

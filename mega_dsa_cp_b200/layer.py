@@ -45,7 +45,7 @@ def l1_groups_for(n_chunks: int) -> int:
 
 
 def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1,
-                    compressor: bool = False, qpath: bool = False):
+                    compressor: bool = False, qpath: bool = False, kvwrite: bool = False):
     """Tasks / events of one layer-step for ALL ranks, plus op codes by task name.  With `compressor`
     every rank also runs CMP_STEP(b) (record append + statistics push, notifies cmp_stats[b] on all
     ranks) and CMP_FIN(b) (entry owner, waits for the cp statistics); they are listed last, so the
@@ -61,7 +61,14 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
     per = -(-n_chunks // l1_groups)
     if qpath:   # QPATH(b) on the owner of b: the step's query block -> every rank's arena, then q_ready[b]
         events += [EventSpec(f"q_ready[{b}]", cross) for b in range(B)]
+    if kvwrite:  # KVWRITE(b) on every rank (the owner of the new position acts); the indexer of b waits for it
+        events += [EventSpec(f"kv_written[{b}]", SCOPE_LOCAL) for b in range(B)]
     for r in range(cp):
+        if kvwrite:
+            for b in range(B):
+                name = f"kvwrite[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (), (NotifyEdge(f"kv_written[{b}]", r),), (b, 0, 0)))
+                ops[name] = N.OP_KVWRITE
         if qpath:
             for b in range(r, B, cp):
                 name = f"qpath[{r},{b}]"
@@ -71,7 +78,7 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
             for c in range(n_chunks):
                 name = f"logits[{r},{b},{c}]"
                 ev = f"l1a[{b},{c // per}]" if l1_groups > 1 else f"l1[{b}]"
-                waits = (WaitEdge(f"q_ready[{b}]"),) if qpath else ()
+                waits = ((WaitEdge(f"q_ready[{b}]"),) if qpath else ()) + ((WaitEdge(f"kv_written[{b}]"),) if kvwrite else ())
                 tasks.append(TaskSpec(name, r, waits, (NotifyEdge(ev, r),), (b, c, 0)))
                 ops[name] = N.OP_LOGITS
         if l1_groups > 1:
@@ -151,7 +158,7 @@ class DsaDecodeLayer:
                  fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
-                 attn_splits: int | None = None, compressor=None, distribute_q: bool = False):
+                 attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False):
         """distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
         then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
         compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
@@ -181,7 +188,8 @@ class DsaDecodeLayer:
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
         tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups,
-                                             compressor=compressor is not None, qpath=distribute_q)
+                                             compressor=compressor is not None, qpath=distribute_q, kvwrite=kvwrite)
+        self.kvwrite = kvwrite
         self.distribute_q = distribute_q
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
         self.dsched = upload_schedule(self.schedule, self.device)
@@ -287,6 +295,18 @@ class DsaDecodeLayer:
         fill_finalize_params(c, st, norm_w_attn, norm_w_idx, norm_eps, freqs, fp8_scale)
         self._params.cmp = c
         self._cmp_keep = (seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, freqs)
+
+    def bind_kvwrite(self, k_idx_new, kv_new, global_len, advance: bool = True) -> None:
+        """Fixes the new-token inputs of the KVWRITE tasks (layer built with kvwrite=True; call after
+        bind()): k_idx_new (B, 128) fp32 and kv_new (B, d_qk) bf16, replicated on every rank and refreshed
+        by the caller before each step; global_len (B,) int32 = sequence lengths before the step.  With
+        `advance` the kernel adds 1 to global_len itself.  The bound block table must already hold a page
+        for the new slot; seq_lens and the caches are written by the step."""
+        assert self._params is not None and self.kvwrite
+        assert k_idx_new.dtype == torch.float32 and global_len.dtype == torch.int32
+        L = self._params
+        L.kvw_k_idx, L.kvw_kv, L.kvw_glen, L.kvw_advance = N.ptr(k_idx_new), N.ptr(kv_new), N.ptr(global_len), int(advance)
+        self._kvw_keep = (k_idx_new, kv_new, global_len)
 
     def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None) -> None:
         """Launches one layer-step (asynchronous): exactly one kernel launch, nothing else.  The

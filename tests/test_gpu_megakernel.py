@@ -267,3 +267,64 @@ def test_layer_step_runs_the_compressor_as_tasks(ratio):
             assert st.k_valid.tolist() == [n + 1] * B
     assert closed >= 2
     assert torch.equal(layer.out, first_out)   # the attention path does not depend on the compressor tasks
+
+
+def test_layer_step_writes_the_new_token_before_it_scores():
+    """KVWRITE tasks (cp = 1): each step quantises the host-supplied index-K record of the new token into
+    the paged NVFP4 cache (bit-exact against the oracle's quantiser), copies its KV row, grows the
+    length, and the same step's selection and attention already see the token (oracle on the updated
+    caches).  The global length advances on the device, so the steps need no host update of it."""
+    from dsa_inputs import indexer_case
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from oracle import dsa_oracle as orc
+
+    B, S, K, bpc, P, H, DQK = 2, 4096, 512, 16, 64, 128, 576
+    case = indexer_case(B, S, P, "nvfp4", seed=12, shuffle=True)
+    g = torch.Generator().manual_seed(13)
+    q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
+    start = [1000, 63]                       # the second sequence crosses a page boundary on its second step
+    seq = torch.tensor(start, dtype=torch.int32)
+    layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=32, kvwrite=True)
+    d = lambda t: t.to(DEV)
+    cache, kv_d, seq_d = d(case["fused"]), d(kv), d(seq)
+    layer.bind(LayerInputs(cache, d(case["bt"]), seq_d, d(case["q"]), d(case["w"]), d(q_mla), kv_d))
+    k_new = torch.zeros(B, 128, device=DEV)
+    kv_new = torch.zeros(B, DQK, dtype=torch.bfloat16, device=DEV)
+    glen = seq_d.clone()
+    layer.bind_kvwrite(k_new, kv_new, glen, advance=True)
+    steps = 3
+    k_all = torch.randn(steps, B, 128, generator=g) * 1.7
+    kv_all = (torch.randn(steps, B, DQK, generator=g) * 0.5).bfloat16()
+    for s in range(steps):
+        k_new.copy_(k_all[s])
+        kv_new.copy_(kv_all[s])
+        layer.step()
+        torch.cuda.synchronize()
+        layer.check_status()
+    assert seq_d.tolist() == [x + steps for x in start] and glen.tolist() == [x + steps for x in start]
+    pages = cache.cpu()
+    for b in range(B):
+        for s in range(steps):
+            slot = start[b] + s
+            pg = pages[int(case["bt"][b, slot // P])]
+            codes, sf = orc.quant_nvfp4(k_all[s, b][None])
+            assert torch.equal(pg[(slot % P) * 64:(slot % P + 1) * 64], codes[0]), (b, s)
+            assert torch.equal(pg[P * 64 + (slot % P) * 8:P * 64 + (slot % P + 1) * 8], sf[0]), (b, s)
+            assert torch.equal(kv_d[b * S + slot, 0].cpu(), kv_all[s, b])
+    # the last step's result against the oracle on the updated caches
+    data, sf = orc.split_index_pages(pages, "nvfp4", P)
+    kd_all = orc.dequant_fp4(data, sf, "nvfp4").reshape(-1, P, 128)
+    kv_h = kv_d.cpu()
+    for b in range(B):
+        n_tok = start[b] + steps
+        kd = kd_all[case["bt"][b].long()].reshape(S, 128)
+        want = orc.select_topk_ref(case["q_deq"][b], case["w"][b], kd, n_tok, K)
+        n = int(layer.sel_c[b])
+        got = layer.sel_i[b, :n].cpu()
+        assert n == want.numel() and len(set(got.tolist()) & set(want.tolist())) >= n - 1
+        assert int(got.max()) <= n_tok - 1 and (n_tok - 1) in set(got.tolist()) or n_tok > K   # short rows select every token, the new one included
+        o, l = orc.attend_selected_ref(q_mla[b, 0].float(), kv_h[b * S:(b + 1) * S, 0].float(), got, 1 / math.sqrt(DQK))
+        assert (layer.out[b].cpu() - o).abs().max() < 2e-2
+        assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
