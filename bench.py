@@ -411,6 +411,16 @@ def run_layer(args):
     e2e_ms = (time.perf_counter() - t0) * 1e3
     ms_step, e2e_step_ms = [x / args.steps for x in R.reduce_max([ms, e2e_ms])]
     nccl = nccl_baseline(R, c, layers[0].attn_splits)
+    # notify -> wait one-way latency of the event layer (ping-pong, round trip / 2): block to block on this GPU,
+    # and rank 0 <-> rank 1 over NVLink; the reference publishes 1.1 us / 2.85 us on B200 (docs/event-system.md:5)
+    from mega_dsa_cp_b200.events.latency import cross_gpu_notify_latency, local_notify_latency
+    latency = {"published_reference_ns": {"local": 1100, "cross_gpu": 2850}}
+    if R.dist is not None:
+        cross = cross_gpu_notify_latency(rank, world, R.group_name, dev)
+        if rank == 0:
+            latency["cross_gpu"] = cross
+    if rank == 0:
+        latency["local"] = local_notify_latency(dev)
     for l in layers:
         l.check_status()
 
@@ -450,7 +460,7 @@ def run_layer(args):
                          "frac": gbs / peaks["hbm_gbs"], "peak_kind": f"of {peaks['kind']}",
                          "kernel": "mega_kernel (the whole layer-step: a chain of dependent phases)",
                          "algorithmic_bytes": algo, "traffic": None, "phases": per_phase},
-            "nccl_baseline": nccl,
+            "nccl_baseline": nccl, "notify_latency": latency,
             "clocks": clk.summary(),
         }
     return R, line, layers, inputs

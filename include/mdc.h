@@ -321,6 +321,22 @@ int mdc_compress_finalize_launch(const mdc_compress_params* p, void* stream);
 int mdc_hadamard_quant_launch(const float* x, uint8_t* out, int32_t n, void* stream);
 
 
+/* Latency probe of the event layer: a ping-pong over two event cells, timed on the pinging side with
+ * %globaltimer (replaces pingpong_kernel / waitoverhead_kernel of tests/bench_notify_latency.py:49-143).
+ * role 0 pings (notify ev_ping at `peer`, wait for the own ev_pong), role 1 pongs; launched on two GPUs,
+ * one block each.  role 2 runs both roles as two blocks of ONE launch on one GPU (peer = own rank).
+ * Cells are monotonic: `base` = value of both cells before the launch.  out_ns (pinging side):
+ * rounds round-trip times in ns, then one more entry = mean cost of a wait that is already satisfied. */
+typedef struct {
+  mdc_event_set events;
+  int32_t role, peer, ev_ping, ev_pong, rounds;
+  uint64_t base;
+  int64_t wait_budget_ns;
+  unsigned long long* out_ns;  /* rounds + 1 entries, or NULL (pong side) */
+  int32_t* status;
+} mdc_pingpong_params;
+int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
+
 /* task op codes understood by mdc_megakernel_launch */
 #define MDC_OP_NOP 0
 #define MDC_OP_LOGITS 1     /* c0 = b, c1 = chunk                                  */

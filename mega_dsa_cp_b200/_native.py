@@ -109,6 +109,11 @@ class MegaParams(C.Structure):
     ]
 
 
+class PingpongParams(C.Structure):
+    _fields_ = [("events", EventSetC), ("role", i32), ("peer", i32), ("ev_ping", i32), ("ev_pong", i32), ("rounds", i32),
+                ("base", C.c_uint64), ("wait_budget_ns", i64), ("out_ns", p_void), ("status", p_void)]
+
+
 OP_NOP, OP_LOGITS, OP_MERGE_L1, OP_MERGE_L2, OP_ATTN, OP_LSE_MERGE, OP_MERGE_L1A = 0, 1, 2, 3, 4, 5, 6
 OP_CMP_STEP, OP_CMP_FIN, OP_QPATH, OP_KVWRITE = 7, 8, 9, 10
 OP_SLEEP, OP_LOG, OP_PUSH, OP_VERIFY = 16, 17, 18, 19
@@ -147,6 +152,7 @@ EXPORTS = [
     "mdc_sparse_mla_launch_static_ws",
     "mdc_megakernel_launch", "mdc_megakernel_check", "mdc_megakernel_smem_bytes", "mdc_megakernel_threads",
     "mdc_compress_step_launch", "mdc_compress_finalize_launch", "mdc_hadamard_quant_launch",
+    "mdc_test_pingpong_launch",
 ]
 
 

@@ -328,3 +328,14 @@ def test_layer_step_writes_the_new_token_before_it_scores():
         o, l = orc.attend_selected_ref(q_mla[b, 0].float(), kv_h[b * S:(b + 1) * S, 0].float(), got, 1 / math.sqrt(DQK))
         assert (layer.out[b].cpu() - o).abs().max() < 2e-2
         assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
+
+
+def test_local_notify_latency_probe():
+    """Block-to-block notify -> wait on one GPU (two blocks of one launch): the probe completes every
+    round inside its budget and reports a one-way latency of a plausible size (the reference publishes
+    1.1 us on B200, docs/event-system.md:5)."""
+    from mega_dsa_cp_b200.events.latency import local_notify_latency
+
+    r = local_notify_latency(DEV, rounds=500)
+    assert r["rounds"] == 450 and 100 < r["one_way_ns_median"] < 20000, r
+    print("local notify->wait one-way ns:", r)

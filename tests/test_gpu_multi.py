@@ -12,12 +12,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(world):
+def _run(world, worker="mp_layer_worker.py", token="MP_LAYER_OK", port=29500):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "mp_layer_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(port + world), os.path.join(ROOT, "tests", worker)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0 and "MP_LAYER_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
+    assert r.returncode == 0 and token in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
+    print([l for l in r.stdout.splitlines() if token in l][-1])
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -25,3 +26,12 @@ def test_decode_layer_across_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_events_comm_scheduler_across_gpus(world):
+    """Ping-pong / fan-in / fan-out hand-offs with a bulk-pushed payload checked behind flag-only waits,
+    25 phases of a cross-rank task DAG, and the cross-GPU notify latency probe."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, "mp_events_worker.py", "MP_EVENTS_OK", port=29600)
