@@ -347,7 +347,7 @@ int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
 #define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
 #define MDC_OP_CMP_STEP 7   /* c0 = b: compressor step of layer.cmp (record append, statistics push to the entry owner)  */
 #define MDC_OP_CMP_FIN 8    /* c0 = b: entry owner merges the cp statistics and writes its pools                       */
-#define MDC_OP_QPATH 9      /* c0 = b (owned): this step's query block of sequence b -> every rank's arena (q_ready[b]) */
+#define MDC_OP_QPATH 9      /* c0 = b (owned), c1 = part (0 indexer q + weights, 1 attention q, 2 both): this step's query block of sequence b -> every rank's arena */
 #define MDC_OP_KVWRITE 10   /* c0 = b: the step's new token of sequence b -> index-K page and KV row of its owner (kv_written[b]) */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */
@@ -413,6 +413,14 @@ typedef struct {
   const void* kvw_kv;           /* (B, d_qk) elements of mla.kv_dtype, replicated */
   int32_t* kvw_glen;            /* (B,)                                          */
   int32_t kvw_advance;
+  /* Row-threshold candidate filter (no counterpart in the reference, whose chunk tasks emit exact chunk
+   * top-k lists).  thr_hist != NULL: the LOGITS tasks of a sequence sum a 2048-bin histogram of their
+   * scores in thr_hist, wait for each other (bounded), and emit only the scores in the bins that can
+   * still hold the row's top_k: about top_k candidates per sequence instead of top_k per chunk, one
+   * MERGE_L1 behind them (l1_groups = 1).  thr_hist: (2, B, 2048) u32, zero before the first step (the
+   * kernel keeps the two halves zeroed in turn); thr_done: (B,) u32, zero before the first step. */
+  uint32_t* thr_hist;
+  uint32_t* thr_done;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

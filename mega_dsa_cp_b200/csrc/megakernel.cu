@@ -27,6 +27,11 @@ static_assert(kMegaThreads == kMuThreads, "the attention tile and the logits til
 constexpr int kStagedWords = 128;  // queue rows up to this length are staged in shared memory
 constexpr int kMegaTileSmem = MlaUmmaSmem<576>::kTotal > MlaSmem<576>::kTotal ? MlaUmmaSmem<576>::kTotal : MlaSmem<576>::kTotal;  // the largest tile
 
+// The merge ops keep their scratch (MergeSmem) at the base of the tile's shared memory and stage the
+// lists behind it.
+constexpr int kMergeHdr = (static_cast<int>(sizeof(MergeSmem)) + 1023) / 1024 * 1024;
+static_assert(kMergeHdr + 16384 * 8 <= kMegaTileSmem, "a row of 16384 staged candidates must fit behind the merge scratch");
+
 struct MegaShared {
   int32_t row[kStagedWords];
   int32_t fail;
@@ -98,7 +103,9 @@ __device__ __host__ inline int64_t q_mla_bytes(const mdc_layer_params& L) { retu
 
 // Owner of sequence b: its query block from the staging buffer -> the q region of every rank's arena.
 // 16-byte loads from local memory, 16-byte posted stores to each destination (own arena included).
-__device__ inline void op_qpath(const mdc_mega_params& p, int b, unsigned long long phase) {
+// part 0: the indexer's share (q_idx, weights: 16.6 KB, what the LOGITS tasks wait for), part 1: the
+// attention query (147 KB, needed only once the selection is done), part 2: both.
+__device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, unsigned long long phase) {
   const mdc_layer_params& L = p.layer;
   if (!L.q_stage || b % L.cp != L.rank) return;
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
@@ -112,7 +119,7 @@ __device__ inline void op_qpath(const mdc_mega_params& p, int b, unsigned long l
                               base + L.B * (q_idx_bytes() + q_w_bytes()) + b * q_mla_bytes(L)};
   const int64_t len[3] = {q_idx_bytes(), q_w_bytes(), q_mla_bytes(L)};
 #pragma unroll 1
-  for (int a = 0; a < 3; ++a) {
+  for (int a = (part == 1 ? 2 : 0); a < (part == 0 ? 2 : 3); ++a) {
     const uint4* src = reinterpret_cast<const uint4*>(st + src_off[a]);
     const int n16 = static_cast<int>(len[a] / 16);
 #pragma unroll 1
@@ -181,8 +188,20 @@ __device__ inline void redirect_q(const mdc_mega_params& p, unsigned long long p
 
 template <int FMT, int PAGE>
 __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned long long phase, unsigned char* smem) {
-  mdc_logits_params lp = p.layer.logits;
+  const mdc_layer_params& L = p.layer;
+  mdc_logits_params lp = L.logits;
   redirect_q(p, phase, &lp, nullptr);
+  if (L.thr_hist && L.thr_done) {
+    const int64_t half = static_cast<int64_t>(L.B) * kThrBins;
+    RowThreshold rt;
+    rt.hist = L.thr_hist + (phase & 1ull) * half;
+    rt.hist_next = L.thr_hist + ((phase + 1ull) & 1ull) * half;
+    rt.done = L.thr_done;
+    rt.target = static_cast<uint32_t>(static_cast<unsigned long long>(L.n_chunks) * (phase + 1ull));
+    rt.budget_ns = p.wait_budget_ns;
+    logits_tile<FMT, PAGE, 1, 2, 1>(lp, b, chunk, smem, &rt);
+    return;
+  }
   logits_tile<FMT, PAGE, 1, 2, 1>(lp, b, chunk, smem);
 }
 
@@ -200,8 +219,8 @@ __device__ inline void op_merge_l1a(const mdc_mega_params& p, int b, int g, unsi
   ls.stride = K;
   ls.c_stride = 1;
   const int64_t o = static_cast<int64_t>(b) * G + g;
-  merge_lists_auto<false>(ls, n, K, K, L.mid_v + o * K, L.mid_i + o * K, L.mid_c + o, nullptr, sm, smem + 8192,
-                          kMegaTileSmem - 8192);
+  merge_lists_auto<false>(ls, n, K, K, L.mid_v + o * K, L.mid_i + o * K, L.mid_c + o, nullptr, sm, smem + kMergeHdr,
+                          kMegaTileSmem - kMergeHdr);
 }
 
 // chunk (or group) candidate lists of sequence b -> this rank's top-k, written into the
@@ -223,13 +242,29 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
   const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
   unsigned char* slice = arena.local_ptr(off);
   merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
-                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm, smem + 8192, kMegaTileSmem - 8192);
+                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm, smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
+  if (L.cp == 1) {
+    // one rank: this list IS the selection; publish it and the gather list here (no MERGE_L2 task)
+    __threadfence();
+    sync_workers();
+    const int n = *reinterpret_cast<const int32_t*>(slice + K * 8);
+    const float* sv = reinterpret_cast<const float*>(slice);
+    const int32_t* si = reinterpret_cast<const int32_t*>(slice + K * 4);
+    for (int i = threadIdx.x; i < n; i += kBlockThreads) {
+      L.sel_v[static_cast<int64_t>(b) * K + i] = sv[i];
+      L.sel_i[static_cast<int64_t>(b) * K + i] = si[i];
+    }
+    if (threadIdx.x == 0) L.sel_c[b] = n;
+    int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
+    const int mine = compact_local_ids(si, n, 1, 0, b * L.kv_seq_stride, pt, L.mla.pt_cols, sm.sel);
+    if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
+  }
   if (L.cp > 1) {
     // The slice goes to every peer as ONE bulk copy each (the copy engine keeps NVLink busy with
     // large packets; thousands of 16-byte stores per task do not): stage it in shared memory first.
     __threadfence();
     sync_workers();
-    unsigned char* stage = smem + 8192;
+    unsigned char* stage = smem + kMergeHdr;
     const int n16 = cand_slice_bytes(L) / 16;
     for (int i = threadIdx.x; i < n16; i += kBlockThreads)
       reinterpret_cast<uint4*>(stage)[i] = reinterpret_cast<const uint4*>(slice)[i];
@@ -262,7 +297,7 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   ls.c_stride = cand_slice_bytes(L) / 4;
   int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
   const int n = merge_lists_auto<SYS>(ls, L.cp, K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
-                                     smem + 8192, kMegaTileSmem - 8192);
+                                     smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
   __threadfence();
   sync_workers();
   int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
@@ -455,7 +490,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         else op_logits<MDC_FMT_NVFP4, 128>(p, t.c0, t.c1, cur.phase, smem);
         break;
       case MDC_OP_QPATH:
-        if (worker) op_qpath(p, t.c0, cur.phase);
+        if (worker) op_qpath(p, t.c0, t.c1, cur.phase);
         break;
       case MDC_OP_KVWRITE:
         if (worker) op_kvwrite(p, t.c0);

@@ -206,6 +206,123 @@ __device__ inline int fused_chunk_select(const float* sc_row, uint32_t* keys, in
   return block_emit_keys(keys, n_local, th, sel, emit);
 }
 
+// Row-threshold candidate filter (used by the persistent kernel, one query token).  The chunks of a
+// request run as separate tasks on different blocks; instead of each emitting the exact top-k of its
+// own chunk (a quarter of the chunk at k = 2048 of 8192: long lists, a tree of merges behind them),
+// the tasks agree on a lower bound of the ROW's k-th largest score and emit only what reaches it:
+//
+//   1. every task adds the histogram of its scores (kThrBins bins = the top 11 bits of the sortable
+//      key: sign, exponent, two mantissa bits) to the row's histogram in global memory and counts in;
+//   2. it waits (bounded) until all n_chunks tasks of the row have counted in, reads the summed
+//      histogram and takes the lowest bin B such that the bins >= B hold at least k scores: the
+//      row's k-th largest score lies in bin B, so nothing below B can be selected;
+//   3. it emits its scores in bins >= B, in position order: over the row about k plus one bin's worth.
+//
+// The one merge behind the tasks selects exactly.  Waiting on row mates inside a task cannot deadlock:
+// tasks are dealt to the blocks in row-major order and every block runs its queue in order, so the
+// lowest unfinished row always has all of its tasks running or next in line.  A wait that runs out
+// is reported, and the task falls back to the exact top-k of its own chunk, which is always a valid
+// candidate set; so does a chunk whose filtered set would not fit its list (heavily tied scores).
+constexpr int kThrBins = 2048, kThrShift = 21;
+
+struct RowThreshold {
+  uint32_t* hist;       // (B, kThrBins) of this phase, zero when the step starts
+  uint32_t* hist_next;  // the other phase's histogram: this step zeroes it for the next one
+  uint32_t* done;       // (B,) tasks counted in, monotonic over the steps
+  uint32_t target;      // value of done[b] when all n_chunks tasks of this step have counted in
+  long long budget_ns;
+};
+
+template <typename Emit>
+__device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int32_t* status, int b, int chunk, int n_chunks,
+                                                     const float* sc_row, uint32_t* keys, int n_local, int base_pos, int limit,
+                                                     int top_k, SelectScratch& sel, uint32_t* hs, Emit emit) {
+  const int tid = threadIdx.x;
+  sync_workers();
+  for (int pos = tid; pos < n_local; pos += kBlockThreads)
+    keys[pos] = (base_pos + pos) < limit ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+  for (int i = tid; i < kThrBins; i += kBlockThreads) hs[i] = 0u;
+  sync_workers();
+  for (int pos = tid; pos < n_local; pos += kBlockThreads) {
+    const uint32_t k = keys[pos];
+    if (k) atomicAdd(&hs[k >> kThrShift], 1u);
+  }
+  sync_workers();
+  uint32_t* gh = rt.hist + static_cast<int64_t>(b) * kThrBins;
+  for (int i = tid; i < kThrBins; i += kBlockThreads) {
+    const uint32_t h = hs[i];
+    if (h) atomicAdd(&gh[i], h);
+  }
+  {  // this task's slice of the next step's histogram
+    const int per = ceil_div(kThrBins, n_chunks);
+    uint32_t* gn = rt.hist_next + static_cast<int64_t>(b) * kThrBins;
+    for (int i = chunk * per + tid; i < min(kThrBins, (chunk + 1) * per); i += kBlockThreads) gn[i] = 0u;
+  }
+  __threadfence();
+  sync_workers();
+  if (tid == 0) {
+    atomicAdd(&rt.done[b], 1u);
+    const unsigned long long t0 = global_timer_ns();
+    bool ok = true;
+    while (static_cast<int32_t>(*reinterpret_cast<volatile uint32_t*>(&rt.done[b]) - rt.target) < 0) {
+      nanosleep(64);
+      if (static_cast<long long>(global_timer_ns() - t0) > rt.budget_ns) {
+        ok = false;
+        break;
+      }
+    }
+    __threadfence();
+    if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -1 - b, chunk, rt.done[b], rt.target);
+    sel.bnd = ok ? 0 : -1;
+  }
+  sync_workers();
+  bool use_filter = sel.bnd >= 0;
+  sync_workers();
+  if (use_filter) {
+    // thread t owns the bins kThrBins-1-8t .. kThrBins-8-8t, scanned from the top
+    uint32_t c[8];
+    int local = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      c[j] = __ldcg(&gh[kThrBins - 1 - 8 * tid - j]);
+      local += static_cast<int>(c[j]);
+    }
+    const int lane = tid & 31, warp = tid >> 5;
+    int wtot;
+    int cum = warp_excl_scan(local, lane, &wtot);
+    if (lane == 0) sel.wgt[warp] = wtot;
+    sync_workers();
+    for (int w = 0; w < warp; ++w) cum += sel.wgt[w];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (cum < top_k && cum + static_cast<int>(c[j]) >= top_k) sel.bnd = kThrBins - 1 - 8 * tid - j;  // (one thread at most)
+      cum += static_cast<int>(c[j]);
+    }
+    sync_workers();
+    const uint32_t bin = static_cast<uint32_t>(sel.bnd);   // 0 when the row holds fewer than k scores: everything passes
+    // does this chunk's share fit its list?
+    int mine = 0;
+    for (int i = tid; i < kThrBins; i += kBlockThreads) mine += static_cast<uint32_t>(i) >= bin ? static_cast<int>(hs[i]) : 0;
+    mine = __reduce_add_sync(0xffffffffu, mine);
+    sync_workers();
+    if (lane == 0) sel.weq[warp] = mine;
+    sync_workers();
+    int n_pass = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) n_pass += sel.weq[w];
+    sync_workers();
+    if (n_pass <= top_k) {
+      Threshold<uint32_t> th;
+      th.tau = bin ? (bin << kThrShift) - 1u : 0u;
+      th.need_eq = 0;
+      th.n_sel = n_pass;
+      return block_emit_keys(keys, n_local, th, sel, emit);
+    }
+  }
+  const Threshold<uint32_t> th = block_select_bits_smem(keys, n_local, top_k, sel);
+  return block_emit_keys(keys, n_local, th, sel, emit);
+}
+
 // Exact top-k of a whole request row across the blocks of a thread-block
 // cluster (block rank = chunk).  Every block holds its chunk's scores in shared
 // memory; the k-th largest key of the row is found by a 4-pass byte radix
@@ -359,7 +476,7 @@ __device__ void logits_row_select(const mdc_logits_params& p, int b, int chunk, 
 // The tile.  smem: dynamic shared memory base (1024 B aligned), laid out by
 // logits_smem_layout.  All logits_threads(GG) threads of the block call it.
 template <int FMT, int PAGE, int T, int DG, int GG, bool ROWK = false>
-__device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsigned char* smem) {
+__device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsigned char* smem, const RowThreshold* rt = nullptr) {
   using PG = IdxPage<FMT, PAGE>;
   constexpr int N = T * kIdxHeads;
   constexpr int kThreads = logits_threads(DG, GG);
@@ -675,11 +792,17 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       const float* sc_row = scores + t * chunk_tokens;
       const int64_t slot0 = ((static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk) * p.top_k;
       uint32_t* keys = reinterpret_cast<uint32_t*>(scores + t * chunk_tokens);
-      const int n = fused_chunk_select(sc_row, keys, n_local, base_pos, limit, p.top_k, sel, [&](int pos, int slot) {
+      auto emit = [&](int pos, int slot) {
         const uint32_t kv = keys[pos];
         p.cand_v[slot0 + slot] = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
         p.cand_i[slot0 + slot] = (base_pos + pos) * p.id_mul + p.id_add;
-      });
+      };
+      int n;
+      if (rt && T == 1)  // (the raw ring is idle by now: it holds the chunk's histogram)
+        n = chunk_emit_above_row_threshold(*rt, p.status, b, chunk, p.n_chunks, sc_row, keys, n_local, base_pos, limit, p.top_k,
+                                           sel, reinterpret_cast<uint32_t*>(ring), emit);
+      else
+        n = fused_chunk_select(sc_row, keys, n_local, base_pos, limit, p.top_k, sel, emit);
       if (tid == 0) p.cand_c[(static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk] = n;
     }
   }

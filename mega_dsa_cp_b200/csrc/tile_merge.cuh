@@ -28,6 +28,7 @@ struct MergeSmem {
     RegSelectScratch<kMergeBigE> rsel_big;
   };
   int32_t cnt[kMergeMaxLists];
+  int32_t off[kMergeMaxLists + 1];  // compact staging: first staged position of each list
 };
 
 // The L lists of one row: list l holds values at v + l * stride, ids at
@@ -171,16 +172,21 @@ __device__ inline int merge_lists_regs(const MergeLists& ls, int L, int maxK, in
 // (invalid positions read element 0 of their list and are masked afterwards),
 // so a thread's loads of one batch are all in flight together.
 template <bool SYS>
-__device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, MergeSmem& sm, uint32_t* vb, int32_t* ib) {
-  const int tid = threadIdx.x;
-  const int n_pos = L * maxK;
+__device__ inline void merge_load_counts(const MergeLists& ls, int L, int maxK, MergeSmem& sm) {
   sync_workers();
-  for (int l = tid; l < L; l += kBlockThreads) {
+  for (int l = threadIdx.x; l < L; l += kBlockThreads) {
     const int32_t* cp = ls.c + l * ls.c_stride;
     int c = SYS ? __float_as_int(ld_sys_f32(reinterpret_cast<const float*>(cp))) : *cp;
     sm.cnt[l] = max(0, min(c, maxK));
   }
   sync_workers();
+}
+
+// counts must have been loaded (merge_load_counts)
+template <bool SYS>
+__device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, MergeSmem& sm, uint32_t* vb, int32_t* ib) {
+  const int tid = threadIdx.x;
+  const int n_pos = L * maxK;
   const bool vec = (maxK & 3) == 0 && (ls.stride & 3) == 0 &&
                    ((reinterpret_cast<uintptr_t>(ls.v) | reinterpret_cast<uintptr_t>(ls.i)) & 15) == 0;
   if (vec) {
@@ -255,6 +261,68 @@ __device__ inline void merge_stage_lists(const MergeLists& ls, int L, int maxK, 
     }
   }
   sync_workers();
+}
+
+// Compact staging for lists that are mostly empty (candidates that passed a threshold): only the valid
+// entries are staged, list after list, so the search and the emit run over sum(cnt) positions instead
+// of L * maxK.  The staged order is the padded order without its holes: same output.  Returns the
+// staged length, padded with empty positions to a multiple of four.
+template <bool SYS>
+__device__ inline int merge_stage_compact(const MergeLists& ls, int L, MergeSmem& sm, uint32_t* vb, int32_t* ib) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid < 32) {  // exclusive prefix of the counts (L <= 256: eight per lane)
+    int c[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      c[j] = lane * 8 + j < L ? sm.cnt[lane * 8 + j] : 0;
+      sum += c[j];
+    }
+    int total;
+    int run = warp_excl_scan(sum, lane, &total);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (lane * 8 + j <= L) sm.off[lane * 8 + j] = run;
+      run += c[j];
+    }
+    if (lane == 31 && L == 256) sm.off[256] = total;
+  }
+  sync_workers();
+  const int n = sm.off[L], n4 = (n + 3) & ~3;
+  constexpr int U = 4;  // positions per thread whose loads are in flight together
+  for (int pos0 = tid; pos0 < n4; pos0 += U * kBlockThreads) {
+    int64_t src[U];
+    float v[U], f[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pos = pos0 + u * kBlockThreads;
+      src[u] = -1;
+      if (pos < n) {
+        int lo = 0, hi = L;  // the list l with off[l] <= pos < off[l + 1]
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (sm.off[mid] <= pos) lo = mid;
+          else hi = mid;
+        }
+        src[u] = lo * ls.stride + (pos - sm.off[lo]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t at = src[u] >= 0 ? src[u] : 0;   // (an empty position reads element 0 and is masked below)
+      v[u] = ld_f32(ls.v + at, SYS);
+      f[u] = ld_f32(reinterpret_cast<const float*>(ls.i) + at, SYS);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pos = pos0 + u * kBlockThreads;
+      if (pos < n4) {
+        vb[pos] = src[u] >= 0 ? max(sortable_u32(v[u]), 1u) : 0u;
+        ib[pos] = src[u] >= 0 ? __float_as_int(f[u]) : 0;
+      }
+    }
+  }
+  sync_workers();
+  return n4;
 }
 
 __device__ inline int workers_sum(int x, int32_t* wcnt) {
@@ -379,17 +447,24 @@ template <bool SYS>
 __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, int top_k, float* out_v, int32_t* out_i,
                                        int32_t* out_c, int32_t* dbg, MergeSmem& sm, unsigned char* stage = nullptr,
                                        int stage_bytes = 0) {
-  const int n_pos = L * maxK;
-  if (stage && n_pos * 8 <= stage_bytes && maxK >= 1) {
+  int n_pos = L * maxK;
+  int n_valid = -1;
+  if (stage && maxK >= 1) {
+    merge_load_counts<SYS>(ls, L, maxK, sm);
+    n_valid = 0;
+    for (int l = 0; l < L; ++l) n_valid += sm.cnt[l];
+  }
+  const int n_cap = ((n_valid + 3) & ~3) + 4;
+  const bool compact = n_valid >= 0 && n_valid * 2 <= n_pos && n_cap * 8 <= stage_bytes;   // mostly holes: stage the entries only
+  if (stage && maxK >= 1 && (compact || n_pos * 8 <= stage_bytes)) {
     uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
-    int32_t* ib = reinterpret_cast<int32_t*>(stage) + n_pos;
-    merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
+    int32_t* ib = reinterpret_cast<int32_t*>(stage) + (compact ? n_cap : n_pos);
+    if (compact) n_pos = merge_stage_compact<SYS>(ls, L, sm, vb, ib);
+    else merge_stage_lists<SYS>(ls, L, maxK, sm, vb, ib);
     {
       // Nothing to select when the lists hold no more than top_k entries between them (one rank's
       // list passing through the cross-rank merge, short contexts): every valid position is
       // emitted, in position order like the general path.
-      int n_valid = 0;
-      for (int l = 0; l < L; ++l) n_valid += sm.cnt[l];
       if (n_valid <= top_k) {
         Threshold<uint32_t> all;
         all.tau = 0u;  // valid keys are >= 1

@@ -55,12 +55,14 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
     for b in range(B):
         if l1_groups > 1:
             events += [EventSpec(f"l1a[{b},{g}]", SCOPE_LOCAL) for g in range(l1_groups)]
-        events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL), EventSpec(f"cand[{b}]", cross),
-                   EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
+        events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL)] + ([EventSpec(f"cand[{b}]", cross)] if cp > 1 else [])
+        events += [EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
     n_attn = 2 * (heads // 64)
     per = -(-n_chunks // l1_groups)
-    if qpath:   # QPATH(b) on the owner of b: the step's query block -> every rank's arena, then q_ready[b]
+    if qpath:   # QPATH(b, part) on the owner of b: the step's query block -> every rank's arena; the small indexer
+        # part first (q_ready[b] releases the LOGITS tasks), the attention query behind it (qm_ready[b])
         events += [EventSpec(f"q_ready[{b}]", cross) for b in range(B)]
+        events += [EventSpec(f"qm_ready[{b}]", cross) for b in range(B)]
     if kvwrite:  # KVWRITE(b) on every rank (the owner of the new position acts); the indexer of b waits for it
         events += [EventSpec(f"kv_written[{b}]", SCOPE_LOCAL) for b in range(B)]
     for r in range(cp):
@@ -70,10 +72,11 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                 tasks.append(TaskSpec(name, r, (), (NotifyEdge(f"kv_written[{b}]", r),), (b, 0, 0)))
                 ops[name] = N.OP_KVWRITE
         if qpath:
-            for b in range(r, B, cp):
-                name = f"qpath[{r},{b}]"
-                tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"q_ready[{b}]", d) for d in range(cp)), (b, 0, 0)))
-                ops[name] = N.OP_QPATH
+            for part, ev in ((0, "q_ready"), (1, "qm_ready")):
+                for b in range(r, B, cp):
+                    name = f"qpath{part}[{r},{b}]"
+                    tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"{ev}[{b}]", d) for d in range(cp)), (b, part, 0)))
+                    ops[name] = N.OP_QPATH
         for b in range(B):
             for c in range(n_chunks):
                 name = f"logits[{r},{b},{c}]"
@@ -89,10 +92,11 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                     ops[name] = N.OP_MERGE_L1A
         for b in range(B):
             name = f"merge_l1[{r},{b}]"
-            tasks.append(TaskSpec(name, r, (WaitEdge(f"l1[{b}]"),),
-                                  tuple(NotifyEdge(f"cand[{b}]", d) for d in range(cp)), (b, 0, 0)))
+            # one rank: the local top-k is the selection, MERGE_L1 publishes it and no MERGE_L2 runs
+            out = (NotifyEdge(f"topk[{b}]", r),) if cp == 1 else tuple(NotifyEdge(f"cand[{b}]", d) for d in range(cp))
+            tasks.append(TaskSpec(name, r, (WaitEdge(f"l1[{b}]"),), out, (b, 0, 0)))
             ops[name] = N.OP_MERGE_L1
-        for b in range(B):
+        for b in range(B if cp > 1 else 0):
             name = f"merge_l2[{r},{b}]"
             tasks.append(TaskSpec(name, r, (WaitEdge(f"cand[{b}]"),), (NotifyEdge(f"topk[{b}]", r),), (b, 0, 0)))
             ops[name] = N.OP_MERGE_L2
@@ -100,7 +104,8 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
             for j in range(n_attn):
                 for s in range(attn_splits):
                     name = f"attn[{r},{b},{j},{s}]"
-                    tasks.append(TaskSpec(name, r, (WaitEdge(f"topk[{b}]"),), (NotifyEdge(f"part[{b}]", b % cp),), (b, j, s)))
+                    waits = (WaitEdge(f"topk[{b}]"),) + ((WaitEdge(f"qm_ready[{b}]"),) if qpath else ())
+                    tasks.append(TaskSpec(name, r, waits, (NotifyEdge(f"part[{b}]", b % cp),), (b, j, s)))
                     ops[name] = N.OP_ATTN
         for b in range(B):
             if b % cp == r:
@@ -158,7 +163,8 @@ class DsaDecodeLayer:
                  fmt: str = "nvfp4", page_tokens: int = 64, max_pages: int = 256, blocks_per_chunk: int = 64,
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
-                 attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False):
+                 attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
+                 row_threshold: bool = True):
         """distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
         then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
         compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
@@ -183,7 +189,11 @@ class DsaDecodeLayer:
         assert heads % 64 == 0 and top_k % 2 == 0, "heads must be a multiple of 64, top_k even"
         assert cp * attn_splits <= 16, f"cp * attn_splits = {cp * attn_splits} exceeds the 16 slices the LSE merge takes"
         assert 0 <= rank < cp
-        self.l1_groups = l1_groups_for(self.n_chunks)
+        # row_threshold: the chunk tasks of a sequence agree on a lower bound of the row's k-th score
+        # (shared histogram) and emit only what reaches it, so one merge level suffices; otherwise every
+        # chunk emits its exact top-k and long rows merge in two levels
+        self.row_threshold = row_threshold
+        self.l1_groups = 1 if row_threshold else l1_groups_for(self.n_chunks)
         self.compressor = compressor
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
@@ -192,6 +202,20 @@ class DsaDecodeLayer:
         self.kvwrite = kvwrite
         self.distribute_q = distribute_q
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
+        if row_threshold:
+            # The LOGITS tasks of a row wait for each other inside the task.  That is free of deadlock as
+            # long as, in this rank's dealing order, they come row by row and nothing that depends on a
+            # row's candidates is queued ahead of a LOGITS task (the scheduler's FIFO order gives both).
+            order = [(self.schedule.op_of[i], tasks[i].coords) for i in self.schedule.topo]
+            seen_consumer, last_row, closed = False, None, set()
+            for op, coords in order:
+                if op == N.OP_LOGITS:
+                    if coords[0] != last_row:
+                        closed.add(last_row)
+                        last_row = coords[0]
+                    assert not seen_consumer and coords[0] not in closed, "LOGITS tasks must be queued first, row by row"
+                elif op in (N.OP_MERGE_L1, N.OP_MERGE_L1A, N.OP_MERGE_L2, N.OP_ATTN, N.OP_LSE_MERGE):
+                    seen_consumer = True
         self.dsched = upload_schedule(self.schedule, self.device)
         self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
         from .tiles.compress import stats_bytes
@@ -219,6 +243,8 @@ class DsaDecodeLayer:
         self.mid_v = torch.empty(B, G, K, device=dev)
         self.mid_i = torch.empty(B, G, K, dtype=torch.int32, device=dev)
         self.mid_c = torch.zeros(B, G, dtype=torch.int32, device=dev)
+        self.thr_hist = torch.zeros(2, B, 2048, dtype=torch.int32, device=dev) if row_threshold else None
+        self.thr_done = torch.zeros(B, dtype=torch.int32, device=dev) if row_threshold else None
         self.sel_v = torch.zeros(B, K, device=dev)
         self.sel_i = torch.zeros(B, K, dtype=torch.int32, device=dev)
         self.sel_c = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -276,6 +302,7 @@ class DsaDecodeLayer:
         L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
         if self.distribute_q:
             L.q_stage, L.q_off = N.ptr(self.q_stage), self.arena.regions["q"]
+        L.thr_hist, L.thr_done = N.ptr(self.thr_hist), N.ptr(self.thr_done)
         self._params, self._inputs = L, x
 
     def bind_compressor(self, seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, norm_eps: float,

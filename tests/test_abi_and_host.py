@@ -229,8 +229,17 @@ def test_layer_dag_variants_validate(n_chunks, cp, splits):
             want = cp * 4 * splits if b % cp == r else 0
             assert s.arity[names[f"part[{b}]"]] == want
             assert s.arity[names[f"l1[{b}]"]] == (G if G > 1 else n_chunks)
-            assert s.arity[names[f"cand[{b}]"]] == cp
+            if cp > 1:
+                assert s.arity[names[f"cand[{b}]"]] == cp
+            else:   # one rank: MERGE_L1 publishes the selection itself, no candidate exchange and no MERGE_L2
+                assert f"cand[{b}]" not in names and not any(t.name.startswith("merge_l2") for t in mine)
         n_lse = sum(1 for t in mine if t.name.startswith("lse_merge"))
         assert n_lse == LSE_GROUPS * sum(1 for b in range(B) if b % cp == r)
+    # the optional task families (query distribution, new-token write, compressor) keep the DAG valid
+    tasks, events, ops = build_layer_dag(B, n_chunks, cp, heads, splits, 1, compressor=True, qpath=True, kvwrite=True)
+    errors, _ = validate(tasks, events, cp)
+    assert not errors, errors[:3]
+    for r in range(cp):
+        codegen_schedule(tasks, events, rank=r, n_ctas=7, world_size=cp, op_of=ops)
     reg = arena_regions(B, cp, 2048, heads, splits)
     assert reg["inbox"] == -(-B // cp) * cp * splits * (heads * 512 * 2 + heads * 4)
