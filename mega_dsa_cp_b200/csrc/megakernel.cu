@@ -22,8 +22,9 @@
 
 namespace mdc {
 
-constexpr int kMegaThreads = logits_threads(2, 1);  // one gate group: leaves 128 registers per thread to the attention op
-static_assert(kMegaThreads == kMuThreads, "the attention tile and the logits tile share one warp layout");
+constexpr int kMegaGate = 1;  // gate groups of the indexer tile inside the persistent kernel
+constexpr int kMegaThreads = logits_threads(2, kMegaGate);
+static_assert(kMegaThreads >= kMuThreads, "the block must hold the attention tile's warps (its roles go by warp index; extra warps only join the barriers)");
 constexpr int kStagedWords = 128;  // queue rows up to this length are staged in shared memory
 constexpr int kMegaTileSmem = MlaUmmaSmem<576>::kTotal > MlaSmem<576>::kTotal ? MlaUmmaSmem<576>::kTotal : MlaSmem<576>::kTotal;  // the largest tile
 
@@ -199,10 +200,10 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
     rt.done = L.thr_done;
     rt.target = static_cast<uint32_t>(static_cast<unsigned long long>(L.n_chunks) * (phase + 1ull));
     rt.budget_ns = p.wait_budget_ns;
-    logits_tile<FMT, PAGE, 1, 2, 1>(lp, b, chunk, smem, &rt);
+    logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem, &rt);
     return;
   }
-  logits_tile<FMT, PAGE, 1, 2, 1>(lp, b, chunk, smem);
+  logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem);
 }
 
 // first level of a two-level local merge: the chunk lists of group g of sequence b -> one list

@@ -53,7 +53,7 @@ def test_launchers_reject_bad_arguments_without_a_gpu():
     c = N.CompressParams()
     assert lib.mdc_compress_step_launch(C.byref(c), None) == -4
     assert lib.mdc_megakernel_launch(None, None) == -4
-    assert lib.mdc_megakernel_threads() in (448, 480) and lib.mdc_megakernel_smem_bytes() > 200 * 1024
+    assert lib.mdc_megakernel_threads() in (448, 576) and lib.mdc_megakernel_smem_bytes() > 200 * 1024
 
 
 def _valid_mega_params(N, cp=1, attn_splits=1, bpc=128, heads=128, top_k=2048, layer=True):
