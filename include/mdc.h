@@ -347,7 +347,7 @@ int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
 #define MDC_OP_LSE_MERGE 5  /* c0 = b (owned), c1 = head group of c2 groups: inbox slices -> output */
 #define MDC_OP_CMP_STEP 7   /* c0 = b: compressor step of layer.cmp (record append, statistics push to the entry owner)  */
 #define MDC_OP_CMP_FIN 8    /* c0 = b: entry owner merges the cp statistics and writes its pools                       */
-#define MDC_OP_QPATH 9      /* c0 = b (owned), c1 = part (0 indexer q + weights, 1 attention q, 2 both): this step's query block of sequence b -> every rank's arena */
+#define MDC_OP_QPATH 9      /* c0 = b (owned), c1 = part (0: indexer q + weights; 1 + s: slice s of c2 slices of the attention q): this step's query block of sequence b -> every rank's arena */
 #define MDC_OP_KVWRITE 10   /* c0 = b: the step's new token of sequence b -> index-K page and KV row of its owner (kv_written[b]) */
 #define MDC_OP_SLEEP 16     /* c1 = nanoseconds (test op)                          */
 #define MDC_OP_LOG 17       /* appends c0 to the execution log (test op)           */

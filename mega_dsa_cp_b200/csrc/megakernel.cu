@@ -103,10 +103,14 @@ __device__ __host__ inline int64_t q_w_bytes() { return 64 * 4; }
 __device__ __host__ inline int64_t q_mla_bytes(const mdc_layer_params& L) { return static_cast<int64_t>(L.H) * L.mla.d_qk * 2; }
 
 // Owner of sequence b: its query block from the staging buffer -> the q region of every rank's arena.
-// 16-byte loads from local memory, 16-byte posted stores to each destination (own arena included).
-// part 0: the indexer's share (q_idx, weights: 16.6 KB, what the LOGITS tasks wait for), part 1: the
-// attention query (147 KB, needed only once the selection is done), part 2: both.
-__device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, unsigned long long phase) {
+// Each array goes through shared memory as bulk copies: one global -> shared, then one shared -> (peer)
+// global per destination rank (own arena included), all issued by one thread and carried by the copy
+// engine; 16-byte loads and stores by the threads took 20 us per task at eight ranks.
+// One SM moves about 45 GB/s this way, so the big array is cut into slices that run as separate tasks.
+// part 0: the indexer's share (q_idx, weights: 16.6 KB, what the LOGITS tasks wait for); part 1 + s:
+// slice s of n_slices of the attention query (147 KB in all, needed only once the selection is done).
+__device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, int n_slices, unsigned long long phase,
+                                unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   if (!L.q_stage || b % L.cp != L.rank) return;
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
@@ -118,24 +122,49 @@ __device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, unsig
   const int64_t base = phase_offset(p, phase) + L.q_off;
   const int64_t dst_off[3] = {base + b * q_idx_bytes(), base + L.B * q_idx_bytes() + b * q_w_bytes(),
                               base + L.B * (q_idx_bytes() + q_w_bytes()) + b * q_mla_bytes(L)};
-  const int64_t len[3] = {q_idx_bytes(), q_w_bytes(), q_mla_bytes(L)};
-#pragma unroll 1
-  for (int a = (part == 1 ? 2 : 0); a < (part == 0 ? 2 : 3); ++a) {
-    const uint4* src = reinterpret_cast<const uint4*>(st + src_off[a]);
-    const int n16 = static_cast<int>(len[a] / 16);
-#pragma unroll 1
-    for (int i0 = threadIdx.x; i0 < n16; i0 += 4 * kBlockThreads) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = i0 + u * kBlockThreads < n16 ? __ldg(src + i0 + u * kBlockThreads) : make_uint4(0, 0, 0, 0);
-      for (int dst = 0; dst < L.cp; ++dst) {
-        uint4* d = reinterpret_cast<uint4*>(arena.peer_ptr(dst_off[a], dst));
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (i0 + u * kBlockThreads < n16) d[i0 + u * kBlockThreads] = v[u];
+  int64_t len[3] = {q_idx_bytes(), q_w_bytes(), q_mla_bytes(L)};
+  int64_t skip = 0;
+  if (part >= 1) {  // a 16-byte aligned slice of the attention query
+    n_slices = max(1, n_slices);
+    const int64_t per = (len[2] / n_slices + 15) / 16 * 16;
+    skip = min(len[2], static_cast<int64_t>(part - 1) * per);
+    len[2] = max(static_cast<int64_t>(0), min(per, len[2] - skip));
+  }
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+  unsigned char* buf = smem + 128;
+  if (threadIdx.x == 0) {
+    // all arrays of the part in flight together: global -> shared (one barrier), then every shared ->
+    // (peer) global copy, one wait at the end (a wait per array would pay the NVLink write round trip each time)
+    const int a0 = part >= 1 ? 2 : 0, a1 = part == 0 ? 2 : 3;
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    uint32_t total = 0;
+    for (int a = a0; a < a1; ++a) total += static_cast<uint32_t>(len[a]);
+    if (total > 0) {
+      mbar_expect_tx(bar, total);
+      uint32_t at_smem = 0;
+      for (int a = a0; a < a1; ++a) {
+        if (len[a] > 0) bulk_g2s(buf + at_smem, st + src_off[a] + (a == 2 ? skip : 0), static_cast<uint32_t>(len[a]), bar);
+        at_smem += static_cast<uint32_t>(len[a]);
+      }
+      if (mbar_wait(bar, 0)) {
+        at_smem = 0;
+        for (int a = a0; a < a1; ++a) {
+          if (len[a] > 0)
+            for (int dst = 0; dst < L.cp; ++dst)
+              bulk_s2g(arena.peer_ptr(dst_off[a] + (a == 2 ? skip : 0), dst), buf + at_smem, static_cast<uint32_t>(len[a]));
+          at_smem += static_cast<uint32_t>(len[a]);
+        }
+        bulk_commit();
+        bulk_wait_all();
+        fence_proxy_async_global();
+      } else {
+        report_failure(p.status, MDC_DEV_COPY_TIMEOUT, b, part, 0, 0);
       }
     }
+    mbar_inval(bar);
   }
+  sync_workers();
 }
 
 // The step's new token of sequence b: on the rank that owns its position, the index-K record is
@@ -491,7 +520,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
         else op_logits<MDC_FMT_NVFP4, 128>(p, t.c0, t.c1, cur.phase, smem);
         break;
       case MDC_OP_QPATH:
-        if (worker) op_qpath(p, t.c0, t.c1, cur.phase);
+        if (worker) op_qpath(p, t.c0, t.c1, t.c2, cur.phase, smem);
         break;
       case MDC_OP_KVWRITE:
         if (worker) op_kvwrite(p, t.c0);

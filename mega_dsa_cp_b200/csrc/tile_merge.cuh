@@ -440,6 +440,68 @@ __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int3
   return min(n, top_k);
 }
 
+// Prefilter of a long staged row: one histogram pass over the top 11 key bits finds the bin that
+// holds the k-th largest key; everything below that bin is dropped and the survivors (about k plus one
+// bin's worth) are compacted, in position order, into vb2 / ib2.  The exact search and the emit then run
+// over the survivors instead of over the whole row.  hist: 2048 words of shared memory; cap: capacity of
+// vb2 / ib2.  Returns the compacted length (a multiple of four, padded with empty positions), or -1 when
+// the survivors would not fit (heavily tied keys): the caller then works on the full row.
+__device__ inline int merge_prefilter(const uint32_t* vb, const int32_t* ib, int n_pos, int top_k, MergeSmem& sm,
+                                      uint32_t* hist, uint32_t* vb2, int32_t* ib2, int cap) {
+  constexpr int kBins = 2048, kShift = 21;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < kBins; i += kBlockThreads) hist[i] = 0u;
+  sync_workers();
+  for (int pos = tid; pos < n_pos; pos += kBlockThreads) {
+    const uint32_t k = vb[pos];
+    if (k) atomicAdd(&hist[k >> kShift], 1u);
+  }
+  sync_workers();
+  // thread t owns the bins kBins-1-8t .. kBins-8-8t, scanned from the top
+  uint32_t c[8];
+  int local = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    c[j] = hist[kBins - 1 - 8 * tid - j];
+    local += static_cast<int>(c[j]);
+  }
+  int wtot;
+  int cum = warp_excl_scan(local, lane, &wtot);
+  if (lane == 0) sm.sel.wgt[warp] = wtot;
+  if (tid == 0) sm.sel.bnd = 0;   // fewer than k keys in all: everything survives
+  sync_workers();
+  for (int w = 0; w < warp; ++w) cum += sm.sel.wgt[w];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (cum < top_k && cum + static_cast<int>(c[j]) >= top_k) {
+      sm.sel.bnd = kBins - 1 - 8 * tid - j;
+      sm.sel.c_gt = cum + static_cast<int>(c[j]);   // survivors: keys in the bins >= the boundary bin
+    }
+    cum += static_cast<int>(c[j]);
+  }
+  if (tid == kBlockThreads - 1 && cum < top_k) sm.sel.c_gt = cum;   // (all keys: the last thread's running sum is the total)
+  sync_workers();
+  const uint32_t bin = static_cast<uint32_t>(sm.sel.bnd);
+  const int n_keep = sm.sel.c_gt;
+  sync_workers();
+  if (((n_keep + 3) & ~3) > cap) return -1;
+  Threshold<uint32_t> th;
+  th.tau = bin ? (bin << kShift) - 1u : 0u;
+  th.need_eq = 0;
+  th.n_sel = n_keep;
+  const int n = block_emit_keys(vb, n_pos, th, sm.sel, [&](int pos, int slot) {
+    vb2[slot] = vb[pos];
+    ib2[slot] = ib[pos];
+  });
+  const int n4 = (n + 3) & ~3;
+  for (int i = n + tid; i < n4; i += kBlockThreads) {
+    vb2[i] = 0u;
+    ib2[i] = 0;
+  }
+  sync_workers();
+  return n4;
+}
+
 // Picks the fastest path the row size allows: staged in shared memory (when
 // `stage` offers 8 bytes per position) with register or shared-memory keys,
 // else register keys read from global memory, else re-reading global memory per pass.
@@ -485,6 +547,16 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
         }
         return n;
       }
+    }
+    // a long row (several full lists): drop what cannot reach the top k before the exact search
+    const int used = (compact ? n_cap : n_pos) * 8;
+    const int cap = ((stage_bytes - used - 2048 * 4) / 8) & ~3;
+    if (n_valid >= 2 * top_k && n_pos % 4 == 0 && cap >= top_k + 4) {
+      uint32_t* hist = reinterpret_cast<uint32_t*>(stage + used);
+      uint32_t* vb2 = hist + 2048;
+      int32_t* ib2 = reinterpret_cast<int32_t*>(vb2) + cap;
+      const int n2 = merge_prefilter(vb, ib, n_pos, top_k, sm, hist, vb2, ib2, cap);
+      if (n2 >= 0) return merge_staged_bits(n2, top_k, out_v, out_i, out_c, dbg, sm, vb2, [&](int pos) { return ib2[pos]; });
     }
     return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; });
   }

@@ -35,6 +35,7 @@ from .schedule.device import launch_megakernel, upload_schedule
 
 D_V = 512
 LSE_GROUPS = 8
+QPATH_SLICES = 8
 
 
 def l1_groups_for(n_chunks: int) -> int:
@@ -72,11 +73,11 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                 tasks.append(TaskSpec(name, r, (), (NotifyEdge(f"kv_written[{b}]", r),), (b, 0, 0)))
                 ops[name] = N.OP_KVWRITE
         if qpath:
-            for part, ev in ((0, "q_ready"), (1, "qm_ready")):
-                for b in range(r, B, cp):
-                    name = f"qpath{part}[{r},{b}]"
-                    tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"{ev}[{b}]", d) for d in range(cp)), (b, part, 0)))
-                    ops[name] = N.OP_QPATH
+            for b in range(r, B, cp):
+                name = f"qpath_idx[{r},{b}]"
+                tasks.append(TaskSpec(name, r, (), tuple(NotifyEdge(f"q_ready[{b}]", d) for d in range(cp)), (b, 0, 0)))
+                ops[name] = N.OP_QPATH
+
         for b in range(B):
             for c in range(n_chunks):
                 name = f"logits[{r},{b},{c}]"
@@ -84,6 +85,17 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                 waits = ((WaitEdge(f"q_ready[{b}]"),) if qpath else ()) + ((WaitEdge(f"kv_written[{b}]"),) if kvwrite else ())
                 tasks.append(TaskSpec(name, r, waits, (NotifyEdge(ev, r),), (b, c, 0)))
                 ops[name] = N.OP_LOGITS
+        if qpath:
+            # The attention query in slices (one SM moves only ~45 GB/s), held back until the owner's own
+            # indexer tasks of the row are through (they wait for l1[b] / the row's first-level event): the
+            # attention needs it much later, and nothing is queued ahead of the LOGITS tasks this way.
+            for b in range(r, B, cp):
+                gate = f"l1a[{b},0]" if l1_groups > 1 else f"l1[{b}]"
+                for s in range(QPATH_SLICES):
+                    name = f"qpath_mla[{r},{b},{s}]"
+                    tasks.append(TaskSpec(name, r, (WaitEdge(gate),), tuple(NotifyEdge(f"qm_ready[{b}]", d) for d in range(cp)),
+                                          (b, 1 + s, QPATH_SLICES)))
+                    ops[name] = N.OP_QPATH
         if l1_groups > 1:
             for b in range(B):
                 for g in range(l1_groups):
