@@ -473,7 +473,7 @@ CFG2 = dict(B=32, S=32768, page=64, top_k=2048, q_len=1, copies=4, blocks_per_ch
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one row-mode indexer launch at BASELINE config 2,
 # from the ncu capture summarised in profiles/logits_row_kernel_cfg2.md
-NCU_TRAFFIC_BYTES = 77_734_400
+NCU_TRAFFIC_BYTES = 77_485_056   # 76,164,096 read + 1,320,960 written
 
 
 def cfg2_algorithmic_bytes(c) -> int:
@@ -627,6 +627,35 @@ def mla_alone(args, dev):
             "traffic": None}
 
 
+def merge_alone(args, dev):
+    """The candidate merge alone: 8 queries, 4 lists of 2048 candidates each -> exact top-2048 (the size of a
+    first-level merge of BASELINE config 2's chunk lists)."""
+    import torch
+    from mega_dsa_cp_b200.tiles.merge import run_merge_topk
+
+    B, K, L = 8, 2048, 4
+    g = torch.Generator(device=dev).manual_seed(4)
+    v = torch.randn(B, 1, L, K, generator=g, device=dev)
+    i = torch.randint(0, 1 << 20, (B, 1, L, K), generator=g, device=dev, dtype=torch.int32)
+    c = torch.full((B, 1, L), K, dtype=torch.int32, device=dev)
+    ov = torch.zeros(B, 1, K, device=dev)
+    oi = torch.zeros(B, 1, K, dtype=torch.int32, device=dev)
+    oc = torch.zeros(B, 1, dtype=torch.int32, device=dev)
+    reps = max(args.steps, 20)
+    for _ in range(4):
+        run_merge_topk(v, i, c, ov, oi, oc, None, top_k=K)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run_merge_topk(v, i, c, ov, oi, oc, None, top_k=K)
+    e1.record()
+    torch.cuda.synchronize()
+    return {"kernel": "merge_topk_kernel", "workload": f"{B} queries x {L} lists x {K} candidates -> top-{K}",
+            "launch_us": e0.elapsed_time(e1) / reps * 1e3, "count_ok": bool((oc == K).all()),
+            "note": "launch-to-launch time of back-to-back host launches (a lower bound of ~14 us is the host's launch rate)"}
+
+
 # ----------------------------------------------------------------------------
 # CPU arm: the oracle port of the same path on the host cores
 # ----------------------------------------------------------------------------
@@ -697,7 +726,7 @@ def main():
     ap.add_argument("--copies", type=int, default=None, help="rotation copies of the config-2 index cache (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (profiling runs)")
     ap.add_argument("--skip-alone", action="store_true", help="N=1: omit the kernels-alone legs (indexer, MLA)")
-    ap.add_argument("--only", default=None, choices=["indexer", "mla"],
+    ap.add_argument("--only", default=None, choices=["indexer", "mla", "merge"],
                     help="run only one kernel-alone leg and print its block (profiling runs)")
     args = ap.parse_args()
     if args.copies:
@@ -711,7 +740,7 @@ def main():
 
         torch.cuda.set_device(0)
         dev = torch.device("cuda", 0)
-        out = indexer_alone(args, dev) if args.only == "indexer" else mla_alone(args, dev)
+        out = {"indexer": indexer_alone, "mla": mla_alone, "merge": merge_alone}[args.only](args, dev)
         print(json.dumps(out))
         return
     R, line, layers, inputs = run_layer(args)
