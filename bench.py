@@ -187,7 +187,8 @@ def layer_algorithmic_bytes(c, attn_splits):
     }
 
 
-OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE", 6: "MERGE_L1A"}
+OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE", 6: "MERGE_L1A",
+            7: "CMP_STEP", 8: "CMP_FIN", 9: "QPATH", 10: "KVWRITE"}
 
 
 def task_timeline(layer, dev):
