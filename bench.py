@@ -317,6 +317,51 @@ def parity_block(R, c, layer, inp, q):
             "ok": bool(ok)}
 
 
+def prefill_sample(R, c, inp, tiles=4):
+    """BASELINE config 5's shape on a bounded sample (chunked prefill: B = 2 sequences x 4096 query
+    tokens at 128 K context): `tiles` tiles of 8 x world query tokens at the end of sequence 0's context,
+    each tile one layer-step in which every query token is a batch entry with its own causal length
+    (mega_dsa_cp_b200/prefill.py).  Every rank takes part; returns query tokens/s (max time over ranks)."""
+    import torch
+    from mega_dsa_cp_b200.prefill import DsaPrefillChunk
+
+    world, rank, dev = R.world, R.rank, R.dev
+    cache, bt, kv = inp
+    S, P, K, H, DQK = c["S"], c["page"], c["top_k"], c["H"], c["d_qk"]
+    S_loc = S // world
+    tile = 8 * world
+    Tq = tiles * tile
+    pf = DsaPrefillChunk(tile, cp=world, rank=rank, top_k=K, heads=H, d_qk=DQK, max_pages=S_loc // P,
+                         blocks_per_chunk=c["blocks_per_chunk"], group_name=R.group_name, device=dev)
+    pf.bind(cache, bt[0], kv[:S_loc])
+    gq = torch.Generator(device=dev).manual_seed(11)
+    q_idx = torch.randn(Tq, 64, 128, generator=gq, device=dev).to(torch.bfloat16)
+    w_idx = (torch.randn(Tq, 64, generator=gq, device=dev) / 64.0).contiguous()
+    q_mla = (torch.randn(Tq, 1, H, DQK, generator=gq, device=dev) * 0.5).to(torch.bfloat16)
+    pos = torch.arange(S - Tq, S)
+    out = torch.zeros(Tq // world, H, 512, dtype=torch.bfloat16, device=dev)
+    sel_c = torch.zeros(Tq, dtype=torch.int32, device=dev)
+    pf.run(q_idx, w_idx, q_mla, pos, out, sel_c=sel_c)          # warm-up
+    torch.cuda.synchronize()
+    pf.check_status()
+    R.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    pf.run(q_idx, w_idx, q_mla, pos, out, sel_c=sel_c)
+    ev1.record()
+    torch.cuda.synchronize()
+    pf.check_status()
+    R.barrier()
+    ms = R.reduce_max([ev0.elapsed_time(ev1)])[0]
+    full = bool((sel_c == K).all()) and bool(torch.isfinite(out.float()).all())
+    return {"workload": f"chunked prefill sample: {Tq} query tokens of one sequence at context {S}, tiles of {tile} "
+                        f"query tokens as batch entries of the decode layer-step (causal lengths), cp{world}",
+            "query_tokens_per_s": Tq / (ms * 1e-3), "us_per_tile": ms * 1e3 / tiles, "tiles": tiles,
+            "kernel_launches": tiles, "selected_full_and_finite": full,
+            "note": "the index cache is re-streamed per query token (from L2 within a tile); parity of this path: "
+                    "tests/test_gpu_prefill.py, tests/mp_prefill_worker.py"}
+
+
 def nccl_baseline(R, c, attn_splits, reps=20):
     """NCCL collectives of the same payloads as the two exchange steps, timed beside the P2P path
     (the measured baseline only; the product path never calls them): all-gather of every sequence's
@@ -412,6 +457,7 @@ def run_layer(args):
     e2e_ms = (time.perf_counter() - t0) * 1e3
     ms_step, e2e_step_ms = [x / args.steps for x in R.reduce_max([ms, e2e_ms])]
     nccl = nccl_baseline(R, c, layers[0].attn_splits)
+    prefill = prefill_sample(R, c, inputs[0])
     # notify -> wait one-way latency of the event layer (ping-pong, round trip / 2): block to block on this GPU,
     # and rank 0 <-> rank 1 over NVLink; the reference publishes 1.1 us / 2.85 us on B200 (docs/event-system.md:5)
     from mega_dsa_cp_b200.events.latency import cross_gpu_notify_latency, local_notify_latency
@@ -461,7 +507,7 @@ def run_layer(args):
                          "frac": gbs / peaks["hbm_gbs"], "peak_kind": f"of {peaks['kind']}",
                          "kernel": "mega_kernel (the whole layer-step: a chain of dependent phases)",
                          "algorithmic_bytes": algo, "traffic": None, "phases": per_phase},
-            "nccl_baseline": nccl, "notify_latency": latency,
+            "nccl_baseline": nccl, "notify_latency": latency, "prefill_chunk": prefill,
             "clocks": clk.summary(),
         }
     return R, line, layers, inputs

@@ -365,7 +365,7 @@ int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
 typedef struct {
   int32_t cp, rank, B, top_k, H;
   int32_t n_chunks;             /* chunks per sequence in `logits`             */
-  int32_t kv_seq_stride;        /* KV pool row of local token l of sequence b = b*kv_seq_stride + l */
+  int32_t kv_seq_stride;        /* KV pool row of local token l of sequence b = b*kv_seq_stride + l (see kv_group) */
   int32_t attn_splits;          /* ATTN tasks per (b, block) over the slot range (0 or 1 = no split); inbox holds cp * attn_splits slices per sequence */
   mdc_logits_params logits;     /* fused mode; cand_* = chunk candidate scratch */
   mdc_sparse_mla_params mla;    /* local KV pool; pt_cmp/k_valid = local gather list written by MERGE_L2 */
@@ -421,6 +421,10 @@ typedef struct {
    * kernel keeps the two halves zeroed in turn); thr_done: (B,) u32, zero before the first step. */
   uint32_t* thr_hist;
   uint32_t* thr_done;
+  /* Batch entries that share one sequence's KV rows (chunked prefill: the query tokens of a tile are
+   * batch entries with their own causal lengths): the KV pool row of local token l of entry b is
+   * (b / kv_group) * kv_seq_stride + l.  0 or 1: every entry is its own sequence (decode). */
+  int32_t kv_group;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

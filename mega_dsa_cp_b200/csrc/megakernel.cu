@@ -44,6 +44,10 @@ __device__ inline int64_t phase_offset(const mdc_mega_params& p, unsigned long l
 }
 __device__ inline int cand_slice_bytes(const mdc_layer_params& L) { return L.top_k * 8 + 16; }
 __device__ inline int inbox_slice_bytes(const mdc_layer_params& L) { return L.H * kMlaDv * 2 + L.H * 4; }
+// First KV pool row of batch entry b: kv_group consecutive entries share one sequence's rows.
+__device__ inline int64_t kv_row_base(const mdc_layer_params& L, int b) {
+  return static_cast<int64_t>(L.kv_group > 1 ? b / L.kv_group : b) * L.kv_seq_stride;
+}
 
 // Ordered compaction by the 256 workers: keeps ids[i] (i < n) with
 // ids[i] % cp == rank and writes row_base + ids[i] / cp to out in input order.  Returns the count.
@@ -194,7 +198,7 @@ __device__ inline void op_kvwrite(const mdc_mega_params& p, int b) {
       const int row_bytes = L.mla.d_qk * (L.mla.kv_dtype == MDC_DT_E4M3 ? 1 : 2);
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(L.kvw_kv) + static_cast<int64_t>(b) * row_bytes);
       uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(const_cast<void*>(L.mla.kv_cmp)) +
-                                            (static_cast<int64_t>(b) * L.kv_seq_stride + slot) * row_bytes);
+                                            (kv_row_base(L, b) + slot) * row_bytes);
       for (int i = tid; i < row_bytes / 16; i += kBlockThreads) dst[i] = src[i];
       if (tid == 0) const_cast<int32_t*>(lp.seq_lens)[b] = slot + 1;
     }
@@ -286,7 +290,7 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
     }
     if (threadIdx.x == 0) L.sel_c[b] = n;
     int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
-    const int mine = compact_local_ids(si, n, 1, 0, b * L.kv_seq_stride, pt, L.mla.pt_cols, sm.sel);
+    const int mine = compact_local_ids(si, n, 1, 0, static_cast<int>(kv_row_base(L, b)), pt, L.mla.pt_cols, sm.sel);
     if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
   }
   if (L.cp > 1) {
@@ -331,7 +335,7 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   __threadfence();
   sync_workers();
   int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
-  const int mine = compact_local_ids(sel_i, n, L.cp, L.rank, b * L.kv_seq_stride, pt, L.mla.pt_cols, sm.sel);
+  const int mine = compact_local_ids(sel_i, n, L.cp, L.rank, static_cast<int>(kv_row_base(L, b)), pt, L.mla.pt_cols, sm.sel);
   if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
 }
 
@@ -639,7 +643,11 @@ static int layer_check(const mdc_mega_params& p) {
     return MDC_ERR_BAD_SHAPE;
   if (L.H != L.mla.H || L.H % 64 != 0 || L.mla.n_splits != 1) return MDC_ERR_BAD_SHAPE;
   if ((L.top_k * 8 + 16) % 16 != 0) return MDC_ERR_BAD_ALIGN;  // candidate slices travel as 16-byte bulk copies
-  if (L.mla.pt_cols < 1 || L.kv_seq_stride < 1 || L.phases < 1 || L.phase_bytes < 0) return MDC_ERR_BAD_SHAPE;
+  if (L.mla.pt_cols < 1 || L.kv_seq_stride < 1 || L.phases < 1 || L.phase_bytes < 0 || L.kv_group < 0) return MDC_ERR_BAD_SHAPE;
+  {  // the gather list holds 32-bit pool rows
+    const long long groups = L.kv_group > 1 ? (L.B + L.kv_group - 1) / L.kv_group : L.B;
+    if (groups * L.kv_seq_stride > 0x7fffffffLL) return MDC_ERR_TOO_LARGE;
+  }
   if (!L.sel_v || !L.sel_i || !L.sel_c || !L.out) return MDC_ERR_NULL;
   if (L.out_dtype != MDC_DT_F32 && L.out_dtype != MDC_DT_BF16) return MDC_ERR_BAD_FORMAT;
   if (L.l1_groups > 1 && (!L.mid_v || !L.mid_i || !L.mid_c)) return MDC_ERR_NULL;
@@ -658,6 +666,7 @@ static int layer_check(const mdc_mega_params& p) {
     if (!L.kvw_k_idx || !L.kvw_kv || !L.logits.seq_lens) return MDC_ERR_NULL;
     if ((reinterpret_cast<uintptr_t>(L.kvw_k_idx) | reinterpret_cast<uintptr_t>(L.kvw_kv)) & 15) return MDC_ERR_BAD_ALIGN;
     if (L.mla.page_cmp != 1) return MDC_ERR_BAD_SHAPE;   // the new row goes to pool row b * kv_seq_stride + slot
+    if (L.kv_group > 1) return MDC_ERR_BAD_SHAPE;        // entries that share KV rows would write the same slot
   }
   if (L.cmp.B != 0) {  // compressor tasks: the tiles' own checks, with the fields the kernel fills in
     mdc_compress_params c = L.cmp;

@@ -176,8 +176,10 @@ class DsaDecodeLayer:
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
-                 row_threshold: bool = True):
-        """distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
+                 row_threshold: bool = True, kv_group: int = 1):
+        """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
+        query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
+        distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
         then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
         compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
         runs its step / finalize as tasks (bind_compressor() supplies the per-step tensors)."""
@@ -185,6 +187,8 @@ class DsaDecodeLayer:
         self.fmt, self.P, self.max_pages, self.bpc = fmt, page_tokens, max_pages, blocks_per_chunk
         self.n_chunks = -(-max_pages // blocks_per_chunk)
         self.kv_seq_stride = kv_seq_stride or max_pages * page_tokens
+        self.kv_group = kv_group
+        assert kv_group >= 1 and not (kv_group > 1 and (kvwrite or compressor is not None))
         self.device = torch.device(device)
         self.phases = phases
         self.scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d_qk)
@@ -303,6 +307,7 @@ class DsaDecodeLayer:
         L = N.LayerParams()
         L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = self.cp, self.rank, B, K, self.H, self.n_chunks
         L.kv_seq_stride = self.kv_seq_stride
+        L.kv_group = self.kv_group
         L.attn_splits = self.attn_splits
         L.l1_groups = self.l1_groups
         L.mid_v, L.mid_i, L.mid_c = N.ptr(self.mid_v), N.ptr(self.mid_i), N.ptr(self.mid_c)

@@ -76,8 +76,6 @@ def main():
     ref_sel = layer.sel_i.clone()
     dist.broadcast(ref_sel, 0)
     ok &= bool(torch.equal(ref_sel, layer.sel_i))
-    flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     # ---- the compressor as tasks of the same persistent kernel, across the real ranks: 13 steps of the
     # ratio-4 window machine (3 closing groups), each entry checked on its owner (n % world)
     from test_gpu_compress import _post_checks
@@ -119,6 +117,8 @@ def main():
     except AssertionError as e:   # report through the common flag so every rank leaves together
         print(f"[rank {rank}] compressor check failed: {e}", flush=True)
         ok = False
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     worst = torch.tensor([worst_o, worst_l], device=dev)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     if rank == 0:

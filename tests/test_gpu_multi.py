@@ -35,3 +35,12 @@ def test_events_comm_scheduler_across_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, "mp_events_worker.py", "MP_EVENTS_OK", port=29600)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_prefill_chunk_across_gpus(world):
+    """Chunked prefill on the decode tiles at cp = world: per query token the causal selection and the
+    merged attention against the oracle, on the owner rank; selections identical on all ranks."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, "mp_prefill_worker.py", "MP_PREFILL_OK", port=29700)
