@@ -178,13 +178,17 @@ def layer_algorithmic_bytes(c, attn_splits):
     n_chunks = -(-pages // c["blocks_per_chunk"])
     part = 128 * 512 * 2 + 128 * 4
     owned = -(-B // cp)
-    return {
-        "LOGITS": B * S_loc * 72 + B * pages * 4 + B * 16640 + B * n_chunks * K * 8,
-        "MERGE_L1": B * n_chunks * K * 8 + B * K * 8 * cp,
+    phases = {
+        # the chunk tasks of a row emit about top-k candidates between them (row threshold); at cp > 1 they
+        # store them into every rank's arena themselves and no local merge runs
+        "LOGITS": B * S_loc * 72 + B * pages * 4 + B * 16640 + B * K * 8 * cp,
+        "MERGE_L1": B * K * 8 + B * K * 12,
         "MERGE_L2": B * cp * K * 8 + B * K * 12,
         "ATTN": B * (K // cp) * 1152 + B * 128 * 576 * 2 + B * attn_splits * part,
         "LSE_MERGE": owned * (cp * attn_splits * part + part),
     }
+    phases.pop("MERGE_L1" if cp > 1 else "MERGE_L2")
+    return phases
 
 
 OP_NAMES = {1: "LOGITS", 2: "MERGE_L1", 3: "MERGE_L2", 4: "ATTN", 5: "LSE_MERGE", 6: "MERGE_L1A",

@@ -425,6 +425,10 @@ typedef struct {
    * batch entries with their own causal lengths): the KV pool row of local token l of entry b is
    * (b / kv_group) * kv_seq_stride + l.  0 or 1: every entry is its own sequence (decode). */
   int32_t kv_group;
+  /* cp > 1 only.  1: the LOGITS tasks store their chunk lists into every rank's cand region themselves
+   * (the region then holds (B, cp, n_chunks, cand_slice): rank-major, chunk-minor) and MERGE_L2 merges
+   * cp * n_chunks lists; no MERGE_L1 task may be queued.  0: MERGE_L1 stores one exact list per rank. */
+  int32_t cand_direct;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

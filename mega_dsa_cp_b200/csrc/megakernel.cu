@@ -44,6 +44,8 @@ __device__ inline int64_t phase_offset(const mdc_mega_params& p, unsigned long l
 }
 __device__ inline int cand_slice_bytes(const mdc_layer_params& L) { return L.top_k * 8 + 16; }
 __device__ inline int inbox_slice_bytes(const mdc_layer_params& L) { return L.H * kMlaDv * 2 + L.H * 4; }
+// Lists each rank contributes to a row's candidate region.
+__device__ __host__ inline int cand_lists_per_rank(const mdc_layer_params& L) { return L.cand_direct && L.cp > 1 ? L.n_chunks : 1; }
 // First KV pool row of batch entry b: kv_group consecutive entries share one sequence's rows.
 __device__ inline int64_t kv_row_base(const mdc_layer_params& L, int b) {
   return static_cast<int64_t>(L.kv_group > 1 ? b / L.kv_group : b) * L.kv_seq_stride;
@@ -234,9 +236,50 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
     rt.target = static_cast<uint32_t>(static_cast<unsigned long long>(L.n_chunks) * (phase + 1ull));
     rt.budget_ns = p.wait_budget_ns;
     logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem, &rt);
-    return;
+  } else {
+    logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem);
   }
-  logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem);
+  if (L.cand_direct && L.cp > 1 && threadIdx.x < kBlockThreads) {
+    // The chunk's list goes to every rank's candidate region (slot rank * n_chunks + chunk of the
+    // row) as bulk copies of the filled part only: stage it in the tile's idle raw ring first.  The
+    // pipeline's warps have left the tile; the worker threads wrote the list and are all here.
+    const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
+                           p.arena.mc_base};
+    const int K = L.top_k, C = L.n_chunks;
+    __threadfence();
+    sync_workers();
+    const int64_t row = static_cast<int64_t>(b) * C + chunk;
+    int n = lp.cand_c[row];
+    n = min(max(n, 0), K);
+    const int n4 = (n + 3) & ~3;   // K is even and the slice 16-byte aligned: the rounded part stays inside it
+    unsigned char* stage = smem + logits_smem_layout<FMT, PAGE>(1, lp.blocks_per_chunk * PAGE, true).ring;
+    uint32_t* sv = reinterpret_cast<uint32_t*>(stage);
+    uint32_t* si = sv + n4;
+    int32_t* sc = reinterpret_cast<int32_t*>(si + n4);
+    const uint32_t* gv = reinterpret_cast<const uint32_t*>(lp.cand_v + row * K);
+    const uint32_t* gi = reinterpret_cast<const uint32_t*>(lp.cand_i + row * K);
+    for (int i = threadIdx.x; i < n4; i += kBlockThreads) {
+      sv[i] = i < n ? __ldcg(gv + i) : 0u;
+      si[i] = i < n ? __ldcg(gi + i) : 0u;
+    }
+    if (threadIdx.x < 4) sc[threadIdx.x] = threadIdx.x == 0 ? n : 0;
+    fence_proxy_async_smem();
+    sync_workers();
+    if (threadIdx.x < L.cp) {
+      const int64_t off = phase_offset(p, phase) + L.cand_off +
+                          ((static_cast<int64_t>(b) * L.cp + L.rank) * C + chunk) * cand_slice_bytes(L);
+      unsigned char* dst = arena.peer_ptr(off, threadIdx.x);
+      if (n4 > 0) {
+        bulk_s2g(dst, sv, n4 * 4);
+        bulk_s2g(dst + K * 4, si, n4 * 4);
+      }
+      bulk_s2g(dst + K * 8, sc, 16);
+      bulk_commit();
+      bulk_wait_all();
+      fence_proxy_async_global();
+    }
+    sync_workers();
+  }
 }
 
 // first level of a two-level local merge: the chunk lists of group g of sequence b -> one list
@@ -321,7 +364,8 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   const mdc_layer_params& L = p.layer;
   MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
   const int K = L.top_k;
-  const int64_t off = phase_offset(p, phase) + L.cand_off + static_cast<int64_t>(b) * L.cp * cand_slice_bytes(L);
+  const int64_t off = phase_offset(p, phase) + L.cand_off +
+                      static_cast<int64_t>(b) * L.cp * cand_lists_per_rank(L) * cand_slice_bytes(L);
   const unsigned char* first = static_cast<const unsigned char*>(p.arena.base) + off;
   MergeLists ls;
   ls.v = reinterpret_cast<const float*>(first);
@@ -330,7 +374,7 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   ls.stride = cand_slice_bytes(L) / 4;
   ls.c_stride = cand_slice_bytes(L) / 4;
   int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
-  const int n = merge_lists_auto<SYS>(ls, L.cp, K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
+  const int n = merge_lists_auto<SYS>(ls, L.cp * cand_lists_per_rank(L), K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
                                      smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
   __threadfence();
   sync_workers();
@@ -652,6 +696,7 @@ static int layer_check(const mdc_mega_params& p) {
   if (L.out_dtype != MDC_DT_F32 && L.out_dtype != MDC_DT_BF16) return MDC_ERR_BAD_FORMAT;
   if (L.l1_groups > 1 && (!L.mid_v || !L.mid_i || !L.mid_c)) return MDC_ERR_NULL;
   if (L.l1_groups < 0 || L.l1_groups > L.n_chunks) return MDC_ERR_BAD_SHAPE;
+  if (L.cand_direct && L.cp > 1 && (L.l1_groups > 1 || L.cp * L.n_chunks > 256)) return MDC_ERR_BAD_SHAPE;  // the merge takes 256 lists
   if (static_cast<long long>(L.cp) * (L.attn_splits > 1 ? L.attn_splits : 1) > kLseMaxSlices) return MDC_ERR_TOO_LARGE;
   // the chunk's scores stay in shared memory: the tile's layout must fit the kernel's allocation
   const int ct = L.logits.blocks_per_chunk * L.logits.page_tokens;

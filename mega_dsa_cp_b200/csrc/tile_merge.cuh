@@ -517,7 +517,8 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
     for (int l = 0; l < L; ++l) n_valid += sm.cnt[l];
   }
   const int n_cap = ((n_valid + 3) & ~3) + 4;
-  const bool compact = n_valid >= 0 && n_valid * 2 <= n_pos && n_cap * 8 <= stage_bytes;   // mostly holes: stage the entries only
+  // mostly holes, or too long to stage with its holes: stage the entries only
+  const bool compact = n_valid >= 0 && (n_valid * 2 <= n_pos || n_pos * 8 > stage_bytes) && n_cap * 8 <= stage_bytes;
   if (stage && maxK >= 1 && (compact || n_pos * 8 <= stage_bytes)) {
     uint32_t* vb = reinterpret_cast<uint32_t*>(stage);
     int32_t* ib = reinterpret_cast<int32_t*>(stage) + (compact ? n_cap : n_pos);

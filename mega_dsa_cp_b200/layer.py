@@ -46,17 +46,23 @@ def l1_groups_for(n_chunks: int) -> int:
 
 
 def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_splits: int = 1, l1_groups: int = 1,
-                    compressor: bool = False, qpath: bool = False, kvwrite: bool = False):
-    """Tasks / events of one layer-step for ALL ranks, plus op codes by task name.  With `compressor`
+                    compressor: bool = False, qpath: bool = False, kvwrite: bool = False, cand_direct: bool = False):
+    """Tasks / events of one layer-step for ALL ranks, plus op codes by task name.  With `cand_direct`
+    (cp > 1, one merge level) the LOGITS tasks store their chunk lists into every rank's arena
+    themselves and notify cand[b] there (arity cp x n_chunks); no MERGE_L1 task runs.  With `compressor`
     every rank also runs CMP_STEP(b) (record append + statistics push, notifies cmp_stats[b] on all
     ranks) and CMP_FIN(b) (entry owner, waits for the cp statistics); they are listed last, so the
     queues hold them behind the attention path (docs/phase1.4-comm-tasks.md:37-38,52 of the reference)."""
     cross = SCOPE_SYS if cp > 1 else SCOPE_LOCAL
+    cand_direct = cand_direct and cp > 1
+    assert not (cand_direct and l1_groups > 1)
     events, tasks, ops = [], [], {}
     for b in range(B):
         if l1_groups > 1:
             events += [EventSpec(f"l1a[{b},{g}]", SCOPE_LOCAL) for g in range(l1_groups)]
-        events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL)] + ([EventSpec(f"cand[{b}]", cross)] if cp > 1 else [])
+        if qpath or not cand_direct:    # (direct: only the held-back attention-query slices wait for it)
+            events += [EventSpec(f"l1[{b}]", SCOPE_LOCAL)]
+        events += [EventSpec(f"cand[{b}]", cross)] if cp > 1 else []
         events += [EventSpec(f"topk[{b}]", SCOPE_LOCAL), EventSpec(f"part[{b}]", cross)]
     n_attn = 2 * (heads // 64)
     per = -(-n_chunks // l1_groups)
@@ -83,7 +89,11 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                 name = f"logits[{r},{b},{c}]"
                 ev = f"l1a[{b},{c // per}]" if l1_groups > 1 else f"l1[{b}]"
                 waits = ((WaitEdge(f"q_ready[{b}]"),) if qpath else ()) + ((WaitEdge(f"kv_written[{b}]"),) if kvwrite else ())
-                tasks.append(TaskSpec(name, r, waits, (NotifyEdge(ev, r),), (b, c, 0)))
+                # (direct: l1[b] only gates the owner's held-back attention-query slices)
+                out = (NotifyEdge(ev, r),) if not cand_direct or (qpath and b % cp == r) else ()
+                if cand_direct:
+                    out += tuple(NotifyEdge(f"cand[{b}]", d) for d in range(cp))
+                tasks.append(TaskSpec(name, r, waits, out, (b, c, 0)))
                 ops[name] = N.OP_LOGITS
         if qpath:
             # The attention query in slices (one SM moves only ~45 GB/s), held back until the owner's own
@@ -102,7 +112,7 @@ def build_layer_dag(B: int, n_chunks: int, cp: int, heads: int = 128, attn_split
                     name = f"merge_l1a[{r},{b},{g}]"
                     tasks.append(TaskSpec(name, r, (WaitEdge(f"l1a[{b},{g}]"),), (NotifyEdge(f"l1[{b}]", r),), (b, g, 0)))
                     ops[name] = N.OP_MERGE_L1A
-        for b in range(B):
+        for b in range(0 if cand_direct else B):
             name = f"merge_l1[{r},{b}]"
             # one rank: the local top-k is the selection, MERGE_L1 publishes it and no MERGE_L2 runs
             out = (NotifyEdge(f"topk[{b}]", r),) if cp == 1 else tuple(NotifyEdge(f"cand[{b}]", d) for d in range(cp))
@@ -145,8 +155,8 @@ def q_block_bytes(heads: int = 128, d_qk: int = 576) -> int:
 
 
 def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1, cmp_stats_bytes: int = 0,
-                  q_bytes: int = 0):
-    cand = B * cp * (top_k * 8 + 16)
+                  q_bytes: int = 0, cand_lists: int = 1):
+    cand = B * cp * cand_lists * (top_k * 8 + 16)
     inbox = -(-B // cp) * cp * attn_splits * (heads * D_V * 2 + heads * 4)
     regions = {"cand": cand, "inbox": inbox}
     if q_bytes:
@@ -176,7 +186,7 @@ class DsaDecodeLayer:
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
-                 row_threshold: bool = True, kv_group: int = 1):
+                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
         distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
@@ -210,11 +220,15 @@ class DsaDecodeLayer:
         # chunk emits its exact top-k and long rows merge in two levels
         self.row_threshold = row_threshold
         self.l1_groups = 1 if row_threshold else l1_groups_for(self.n_chunks)
+        # several ranks, one merge level: the chunk lists go straight to every rank (no exact local top-k
+        # in between: the global top-k lies inside the union of what the chunks emit)
+        self.cand_direct = cand_direct and row_threshold and cp > 1 and self.l1_groups == 1 and cp * self.n_chunks <= 256
         self.compressor = compressor
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
         tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups,
-                                             compressor=compressor is not None, qpath=distribute_q, kvwrite=kvwrite)
+                                             compressor=compressor is not None, qpath=distribute_q, kvwrite=kvwrite,
+                                             cand_direct=self.cand_direct)
         self.kvwrite = kvwrite
         self.distribute_q = distribute_q
         self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
@@ -237,7 +251,8 @@ class DsaDecodeLayer:
         from .tiles.compress import stats_bytes
         cmp_bytes = stats_bytes(compressor.ratio) if compressor is not None else 0
         self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes,
-                                               q_block_bytes(heads, d_qk) if distribute_q else 0),
+                                               q_block_bytes(heads, d_qk) if distribute_q else 0,
+                                               self.n_chunks if self.cand_direct else 1),
                                  phases, rank, cp, group_name, self.device)
         self.n_owned = len(range(rank, B, cp))
         # distribute_q: the owned sequences' query blocks, one contiguous block [q_idx | w | q_mla] that a
@@ -308,6 +323,7 @@ class DsaDecodeLayer:
         L.cp, L.rank, L.B, L.top_k, L.H, L.n_chunks = self.cp, self.rank, B, K, self.H, self.n_chunks
         L.kv_seq_stride = self.kv_seq_stride
         L.kv_group = self.kv_group
+        L.cand_direct = int(self.cand_direct)
         L.attn_splits = self.attn_splits
         L.l1_groups = self.l1_groups
         L.mid_v, L.mid_i, L.mid_c = N.ptr(self.mid_v), N.ptr(self.mid_i), N.ptr(self.mid_c)

@@ -241,5 +241,19 @@ def test_layer_dag_variants_validate(n_chunks, cp, splits):
     assert not errors, errors[:3]
     for r in range(cp):
         codegen_schedule(tasks, events, rank=r, n_ctas=7, world_size=cp, op_of=ops)
+    # several ranks, chunk lists stored by the LOGITS tasks themselves: no MERGE_L1, cand[b] counts cp x chunks
+    for qp in (False, True):
+        tasks, events, ops = build_layer_dag(B, n_chunks, cp, heads, splits, 1, qpath=qp, cand_direct=True)
+        errors, _ = validate(tasks, events, cp)
+        assert not errors, errors[:3]
+        names = {e.name: i for i, e in enumerate(events)}
+        for r in range(cp):
+            s = codegen_schedule(tasks, events, rank=r, n_ctas=7, world_size=cp, op_of=ops)
+            has_l1 = any(t.name.startswith("merge_l1") for t in tasks if t.rank == r)
+            assert has_l1 == (cp == 1)
+            if cp > 1:
+                assert all(s.arity[names[f"cand[{b}]"]] == cp * n_chunks for b in range(B))
+                assert ("l1[0]" in names) == qp
     reg = arena_regions(B, cp, 2048, heads, splits)
     assert reg["inbox"] == -(-B // cp) * cp * splits * (heads * 512 * 2 + heads * 4)
+    assert arena_regions(B, cp, 2048, heads, splits, cand_lists=n_chunks)["cand"] == n_chunks * reg["cand"]
