@@ -362,6 +362,8 @@ int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
  *                 [top_k f32 logits][top_k i32 global ids][i32 count, pad]
  *   inbox region: (B_owned, cp, H*512*2 + H*4) bytes, owner(b) = b % cp,
  *                 owned index b / cp: [H x 512 bf16 partial O][H f32 log2-LSE]  */
+#define MDC_THR_BINS 4096  /* bins of the row histogram: the upper 12 bits of the order-preserving u32 image of a score */
+
 typedef struct {
   int32_t cp, rank, B, top_k, H;
   int32_t n_chunks;             /* chunks per sequence in `logits`             */
@@ -414,10 +416,10 @@ typedef struct {
   int32_t* kvw_glen;            /* (B,)                                          */
   int32_t kvw_advance;
   /* Row-threshold candidate filter (no counterpart in the reference, whose chunk tasks emit exact chunk
-   * top-k lists).  thr_hist != NULL: the LOGITS tasks of a sequence sum a 2048-bin histogram of their
+   * top-k lists).  thr_hist != NULL: the LOGITS tasks of a sequence sum an MDC_THR_BINS-bin histogram of their
    * scores in thr_hist, wait for each other (bounded), and emit only the scores in the bins that can
    * still hold the row's top_k: about top_k candidates per sequence instead of top_k per chunk, one
-   * MERGE_L1 behind them (l1_groups = 1).  thr_hist: (2, B, 2048) u32, zero before the first step (the
+   * MERGE_L1 behind them (l1_groups = 1).  thr_hist: (2, B, MDC_THR_BINS) u32, zero before the first step (the
    * kernel keeps the two halves zeroed in turn); thr_done: (B,) u32, zero before the first step. */
   uint32_t* thr_hist;
   uint32_t* thr_done;
@@ -429,6 +431,17 @@ typedef struct {
    * (the region then holds (B, cp, n_chunks, cand_slice): rank-major, chunk-minor) and MERGE_L2 merges
    * cp * n_chunks lists; no MERGE_L1 task may be queued.  0: MERGE_L1 stores one exact list per rank. */
   int32_t cand_direct;
+  /* Exact row selection inside the LOGITS tasks (needs thr_hist / thr_done; no counterpart in the
+   * reference).  thr_exact = 1: the chunk tasks of a row, on all ranks, agree on the row's exact top-k
+   * through a histogram exchange and a short list of undecided keys, write the selection and the gather
+   * lists themselves and mark their candidate counts -1; the merge task of the row (MERGE_L1 with one
+   * rank, MERGE_L2 with several and cand_direct = 1, which it requires there) then only passes the result
+   * on.  Heavily tied rows fall back to the merge.  thr_off: byte offset inside one arena phase of
+   * (B, cp * 4 * MDC_THR_BINS + cp * n_chunks * 2064) bytes of exchange space (histograms per rank, then one slot per
+   * rank and chunk); thr_ev_base: first of 2 * B extra event cells (beyond the queue's events) of the
+   * event buffer: cell thr_ev_base + b counts histogram arrivals, thr_ev_base + B + b slot arrivals. */
+  int32_t thr_exact, thr_ev_base;
+  int64_t thr_off;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

@@ -235,6 +235,36 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
     rt.done = L.thr_done;
     rt.target = static_cast<uint32_t>(static_cast<unsigned long long>(L.n_chunks) * (phase + 1ull));
     rt.budget_ns = p.wait_budget_ns;
+    rt.x = nullptr;
+    RowExact x;
+    static_assert(kThrBins * 4 + sizeof(RowExactScratch) <= kRawStages * IdxPage<FMT, PAGE>::kStageBytes,
+                  "the exact selection's scratch lives in the idle raw ring");
+    if (L.thr_exact) {
+      const int C = L.n_chunks, K = L.top_k;
+      x.ev = EventSet{static_cast<unsigned char*>(p.events.base), p.events.offsets, p.events.my_rank, p.events.world};
+      x.ev_hist = L.thr_ev_base + b;
+      x.ev_keys = L.thr_ev_base + L.B + b;
+      x.hist_target = static_cast<unsigned long long>(L.cp) * (phase + 1ull);
+      x.keys_target = static_cast<unsigned long long>(L.cp) * C * (phase + 1ull);
+      x.arena = static_cast<unsigned char*>(p.arena.base);
+      x.arena_offsets = p.arena.offsets;
+      const int64_t row_bytes = static_cast<int64_t>(L.cp) * (kRowHistBytes + static_cast<int64_t>(C) * kRowSlotBytes);
+      x.hist_off = phase_offset(p, phase) + L.thr_off + b * row_bytes;
+      x.slot_off = x.hist_off + static_cast<int64_t>(L.cp) * kRowHistBytes;
+      x.slice_bytes = cand_slice_bytes(L);
+      x.out_off = phase_offset(p, phase) + L.cand_off + static_cast<int64_t>(b) * L.cp * C * x.slice_bytes;
+      x.cp = L.cp;
+      x.rank = L.rank;
+      x.out_v = L.sel_v + static_cast<int64_t>(b) * K;
+      x.out_i = L.sel_i + static_cast<int64_t>(b) * K;
+      x.sel_c = L.sel_c + b;
+      x.pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
+      x.pt_cols = L.mla.pt_cols;
+      x.k_valid = const_cast<int32_t*>(L.mla.k_valid) + b;
+      x.row_base = static_cast<int>(kv_row_base(L, b));
+      x.win_slots = kWinSlots;
+      rt.x = &x;
+    }
     logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem, &rt);
   } else {
     logits_tile<FMT, PAGE, 1, 2, kMegaGate>(lp, b, chunk, smem);
@@ -250,7 +280,8 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
     sync_workers();
     const int64_t row = static_cast<int64_t>(b) * C + chunk;
     int n = lp.cand_c[row];
-    n = min(max(n, 0), K);
+    if (n < 0) return;   // (uniform over the block) the row was published by the tasks themselves, cells included
+    n = min(n, K);
     const int n4 = (n + 3) & ~3;   // K is even and the slice 16-byte aligned: the rounded part stays inside it
     unsigned char* stage = smem + logits_smem_layout<FMT, PAGE>(1, lp.blocks_per_chunk * PAGE, true).ring;
     uint32_t* sv = reinterpret_cast<uint32_t*>(stage);
@@ -316,6 +347,20 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
   ls.c = (two_level ? L.mid_c : L.logits.cand_c) + static_cast<int64_t>(b) * C;
   ls.stride = K;
   ls.c_stride = 1;
+  if (L.thr_exact && L.cp == 1 && !two_level) {
+    // the LOGITS tasks of the row published the selection and the gather list themselves: nothing to do
+    int pub = 0;
+    if (threadIdx.x < 32) {
+      int all = 1;
+      for (int c = threadIdx.x; c < C; c += 32) all &= __ldcg(ls.c + c) < 0;
+      pub = __all_sync(0xffffffffu, all);
+      if (threadIdx.x == 0) sm.sel.bnd = pub;
+    }
+    sync_workers();
+    pub = sm.sel.bnd;
+    sync_workers();
+    if (pub) return;
+  }
   const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
   unsigned char* slice = arena.local_ptr(off);
   merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
@@ -374,6 +419,34 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
   ls.stride = cand_slice_bytes(L) / 4;
   ls.c_stride = cand_slice_bytes(L) / 4;
   int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
+  if (L.thr_exact && L.cand_direct) {
+    // published by the LOGITS tasks of all ranks (every slice's cell holds {-1, length}): the selection lies
+    // in slice 0 of the row; the gather list and its length are already in place
+    const int J = L.cp * L.n_chunks;
+    if (threadIdx.x < 32) {
+      int all = 1;
+      for (int j = threadIdx.x; j < J; j += 32)
+        all &= __float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + static_cast<int64_t>(j) * cand_slice_bytes(L) + K * 8))) < 0;
+      const int pub = __all_sync(0xffffffffu, all);
+      if (threadIdx.x == 0) sm.sel.bnd = pub;
+    }
+    sync_workers();
+    const int pub = sm.sel.bnd;
+    sync_workers();
+    if (pub) {
+      const int n = min(max(__float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + K * 8 + 4))), 0), K);
+      const int n4 = (n + 3) >> 2;
+      float* ov = L.sel_v + static_cast<int64_t>(b) * K;
+      for (int i = threadIdx.x; i < n4; i += kBlockThreads) {
+        const uint4 v = ld_sys_u4(reinterpret_cast<const uint4*>(first) + i);
+        const uint4 d = ld_sys_u4(reinterpret_cast<const uint4*>(first + K * 4) + i);
+        reinterpret_cast<uint4*>(ov)[i] = v;
+        reinterpret_cast<uint4*>(sel_i)[i] = d;
+      }
+      if (threadIdx.x == 0) L.sel_c[b] = n;
+      return;
+    }
+  }
   const int n = merge_lists_auto<SYS>(ls, L.cp * cand_lists_per_rank(L), K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
                                      smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
   __threadfence();
@@ -697,6 +770,11 @@ static int layer_check(const mdc_mega_params& p) {
   if (L.l1_groups > 1 && (!L.mid_v || !L.mid_i || !L.mid_c)) return MDC_ERR_NULL;
   if (L.l1_groups < 0 || L.l1_groups > L.n_chunks) return MDC_ERR_BAD_SHAPE;
   if (L.cand_direct && L.cp > 1 && (L.l1_groups > 1 || L.cp * L.n_chunks > 256)) return MDC_ERR_BAD_SHAPE;  // the merge takes 256 lists
+  if (L.thr_exact) {
+    if (!L.thr_hist || !L.thr_done || L.thr_ev_base < p.n_events || (L.thr_off & 15)) return MDC_ERR_BAD_SHAPE;
+    if (L.cp * L.n_chunks > kRowMaxSlots || L.l1_groups > 1 || (L.cp > 1 && !L.cand_direct)) return MDC_ERR_BAD_SHAPE;
+    if (L.top_k % 4 != 0) return MDC_ERR_BAD_ALIGN;   // the published selection is copied in 16-byte pieces
+  }
   if (static_cast<long long>(L.cp) * (L.attn_splits > 1 ? L.attn_splits : 1) > kLseMaxSlices) return MDC_ERR_TOO_LARGE;
   // the chunk's scores stay in shared memory: the tile's layout must fit the kernel's allocation
   const int ct = L.logits.blocks_per_chunk * L.logits.page_tokens;

@@ -55,6 +55,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "events.cuh"
 #include "fp4.cuh"
 #include "radix.cuh"
 #include "radix_regs.cuh"
@@ -211,8 +212,8 @@ __device__ inline int fused_chunk_select(const float* sc_row, uint32_t* keys, in
 // own chunk (a quarter of the chunk at k = 2048 of 8192: long lists, a tree of merges behind them),
 // the tasks agree on a lower bound of the ROW's k-th largest score and emit only what reaches it:
 //
-//   1. every task adds the histogram of its scores (kThrBins bins = the top 11 bits of the sortable
-//      key: sign, exponent, two mantissa bits) to the row's histogram in global memory and counts in;
+//   1. every task adds the histogram of its scores (kThrBins bins = the top 12 bits of the sortable
+//      key: sign, exponent, three mantissa bits) to the row's histogram in global memory and counts in;
 //   2. it waits (bounded) until all n_chunks tasks of the row have counted in, reads the summed
 //      histogram and takes the lowest bin B such that the bins >= B hold at least k scores: the
 //      row's k-th largest score lies in bin B, so nothing below B can be selected;
@@ -223,7 +224,47 @@ __device__ inline int fused_chunk_select(const float* sc_row, uint32_t* keys, in
 // lowest unfinished row always has all of its tasks running or next in line.  A wait that runs out
 // is reported, and the task falls back to the exact top-k of its own chunk, which is always a valid
 // candidate set; so does a chunk whose filtered set would not fit its list (heavily tied scores).
-constexpr int kThrBins = 2048, kThrShift = 21;
+constexpr int kThrBins = MDC_THR_BINS, kThrShift = 32 - 12;   // sign, exponent, three mantissa bits
+static_assert(kThrBins == 1 << (32 - kThrShift), "bins = the key's upper bits");
+
+// Exact mode (RowThreshold::x set).  The chunk tasks of a row, on ALL ranks of a context-parallel group,
+// settle the row's exact top-k between them, so that no merge has to run behind them:
+//   a. the last task of a rank's row to count in stores the rank's row histogram into every rank's arena
+//      and notifies the row's "histograms" cell there; every task waits for the cp histograms, sums them
+//      and finds the boundary bin of the GLOBAL row (one rank: the local histogram is the global one);
+//   b. every task stores a slot {scores above the bin, scores inside it, overflow flag, the keys inside
+//      it} into every rank's arena and notifies the row's "keys" cell; it waits for all cp x n_chunks slots;
+//   c. every task finds the exact threshold among the undecided keys of all slots (the same computation
+//      on the same data everywhere), derives each slot's share (ties go to the lower rank, chunk,
+//      position) and emits its own share: the gather list of this rank at its local offset, and the
+//      selection list at its global offset on every rank.  Its candidate count is then -1 ("published").
+// A slot that would overflow (heavily tied scores) makes every task of the row fall back to emitting
+// candidates for the merge task, which always remains in the task graph.  All waits are bounded.
+constexpr int kUndCap = 512;                      // boundary-bin keys one chunk contributes at most
+constexpr int kUndRowCap = 4096;                  // ... and a whole row (the exact search's shared-memory list)
+constexpr int kRowSlotBytes = 16 + kUndCap * 4;   // {n_above, n_und, overflow, 0} then the keys
+constexpr int kRowHistBytes = MDC_THR_BINS * 4;
+constexpr int kRowMaxSlots = 256;
+
+struct RowExact {
+  EventSet ev;
+  int ev_hist, ev_keys;                        // the row's two cells
+  unsigned long long hist_target, keys_target;  // cp and cp * n_chunks arrivals per step
+  unsigned char* arena;                        // this rank's arena; rank d's is at arena + arena_offsets[d]
+  const int64_t* arena_offsets;
+  int64_t hist_off;                            // this step, this row: [cp][bins] u32 (unused with one rank)
+  int64_t slot_off;                            // this step, this row: [cp * n_chunks] slots
+  int64_t out_off;                             // several ranks: the row's candidate slices (slice 0 receives the
+  int64_t slice_bytes;                         //   selection: [K f32][K i32]; every slice's cell: {-1, total})
+  int cp, rank;
+  float* out_v;                                // one rank: the row of the selection lists, written directly
+  int32_t* out_i;
+  int32_t* sel_c;
+  int32_t* pt;                                 // the row of this rank's gather list (pool rows)
+  int pt_cols;
+  int32_t* k_valid;
+  int row_base, win_slots;
+};
 
 struct RowThreshold {
   uint32_t* hist;       // (B, kThrBins) of this phase, zero when the step starts
@@ -231,20 +272,255 @@ struct RowThreshold {
   uint32_t* done;       // (B,) tasks counted in, monotonic over the steps
   uint32_t target;      // value of done[b] when all n_chunks tasks of this step have counted in
   long long budget_ns;
+  const RowExact* x;    // exact mode, or nullptr
 };
+
+// exclusive prefix sums of n <= 256 ints in shared memory, by one warp (eight consecutive per lane);
+// out[n] receives the total
+__device__ inline void warp_prefix256(const int* in, int* out, int n, int lane) {
+  int c[8], sum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    c[j] = lane * 8 + j < n ? in[lane * 8 + j] : 0;
+    sum += c[j];
+  }
+  int total;
+  int run = warp_excl_scan(sum, lane, &total);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (lane * 8 + j <= n) out[lane * 8 + j] = run;
+    run += c[j];
+  }
+}
+
+struct RowExactSmem {
+  int32_t na[kRowMaxSlots], nu[kRowMaxSlots];     // slot headers
+  int32_t g[kRowMaxSlots], e[kRowMaxSlots];       // per slot: selected above the threshold, tied at it
+  int32_t take[kRowMaxSlots];
+  int32_t uo[kRowMaxSlots + 1], eo[kRowMaxSlots + 1], to[kRowMaxSlots + 1];  // prefixes of nu, e, take
+  int32_t overflow, my_n, ok, pad;
+};
+
+constexpr int kSurvCap = 2048;   // scores of one chunk at or above the row's boundary bin (more: the row falls back)
+
+// Shared-memory scratch of the exact mode behind the chunk's histogram (all inside the idle raw ring).
+// (hs, kThrBins words, then this struct: checked against the ring's size where the tile is instantiated)
+struct RowExactScratch {
+  uint32_t skey[kSurvCap];    // the chunk's survivors (keys in bins >= the boundary bin), in position order
+  uint16_t spos[kSurvCap];    // ... and their positions inside the chunk
+  uint32_t mylist[kUndCap];   // those inside the boundary bin: this chunk's slot
+  uint32_t und[kUndRowCap];   // the undecided keys of the whole row
+  RowExactSmem xs;
+};
+
+// Steps b and c of the exact mode, after the boundary bin `bin` of the global row is known (0: the row
+// holds fewer than top_k scores, everything valid is selected).  n_pass: this chunk's scores in bins >= bin.
+// Returns true when the row was published (this task emitted its share), false when the row falls back.
+__device__ inline bool chunk_publish_row_exact(const RowThreshold& rt, int32_t* status, int b, int chunk, int n_chunks,
+                                               const uint32_t* keys, int n_local, int base_pos, int top_k, int id_mul,
+                                               int id_add, uint32_t bin, int n_pass, SelectScratch& sel,
+                                               RowExactScratch& rs) {
+  const RowExact& x = *rt.x;
+  RowExactSmem& xs = rs.xs;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int J = x.cp * n_chunks, me = x.rank * n_chunks + chunk;
+  const uint32_t floor_tau = bin ? (bin << kThrShift) - 1u : 0u;   // keys > floor_tau: the bins >= bin
+  // ---- the chunk's survivors, compacted in position order: every later step works on this short list
+  const bool fits = n_pass <= kSurvCap;
+  int n_s = 0;
+  if (fits) {
+    Threshold<uint32_t> th;
+    th.tau = floor_tau;
+    th.need_eq = 0;
+    th.n_sel = n_pass;
+    n_s = block_emit_keys(keys, n_local, th, sel, [&](int pos, int slot) {
+      if (slot < kSurvCap) {
+        rs.skey[slot] = keys[pos];
+        rs.spos[slot] = static_cast<uint16_t>(pos);
+      }
+    });
+    n_s = min(n_s, kSurvCap);
+  }
+  const int n_s4 = (n_s + 3) & ~3;
+  if (tid < n_s4 - n_s) rs.skey[n_s + tid] = 0u;
+  if (tid == 0) xs.my_n = 0;
+  sync_workers();
+  // ---- b. this chunk's slot: how many above the bin, and the keys inside it
+  int above = 0;
+  for (int i0 = 0; i0 < n_s; i0 += kBlockThreads) {
+    const int i = i0 + tid;
+    const uint32_t v = i < n_s ? rs.skey[i] : 0u;
+    const bool in = v != 0u && bin != 0u && (v >> kThrShift) == bin;
+    above += v != 0u && !in;
+    const uint32_t m = __ballot_sync(0xffffffffu, in);
+    if (m != 0u) {
+      int base = 0;
+      if (lane == 0) base = atomicAdd(&xs.my_n, __popc(m));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      const int slot = base + __popc(m & ((1u << lane) - 1u));
+      if (in && slot < kUndCap) rs.mylist[slot] = v;
+    }
+  }
+  above = __reduce_add_sync(0xffffffffu, above);
+  if (lane == 0) sel.weq[warp] = above;
+  sync_workers();
+  int n_above = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) n_above += sel.weq[w];
+  const int n_und = xs.my_n;
+  const bool over = !fits || n_und > kUndCap;
+  {
+    const int n_keys = over ? 0 : n_und;
+    const int64_t at = x.slot_off + static_cast<int64_t>(me) * kRowSlotBytes;
+    for (int d = 0; d < x.cp; ++d) {
+      unsigned char* dst = x.arena + x.arena_offsets[d] + at;
+      if (tid == 0) *reinterpret_cast<int4*>(dst) = make_int4(n_above, n_keys, over ? 1 : 0, 0);
+      for (int i = tid; i < n_keys; i += kBlockThreads) reinterpret_cast<uint32_t*>(dst + 16)[i] = rs.mylist[i];
+    }
+    if (x.cp > 1) __threadfence_system();
+    else __threadfence();
+    sync_workers();
+    if (tid == 0) {
+      for (int d = 0; d < x.cp; ++d) x.ev.notify_1t(x.ev_keys, d);
+      unsigned long long seen = 0;
+      const bool ok = x.ev.poll_1t(x.ev_keys, x.keys_target, x.cp > 1, rt.budget_ns, &seen);
+      if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -1000 - b, chunk, seen, x.keys_target);
+      xs.ok = ok ? 1 : 0;
+      xs.overflow = 0;
+    }
+    sync_workers();
+    if (!xs.ok) return false;
+  }
+  // ---- c. all slots -> the exact threshold and every slot's share
+  const unsigned char* slots = x.arena + x.slot_off;
+  for (int j = tid; j < J; j += kBlockThreads) {
+    const uint4 h = ld_sys_u4(reinterpret_cast<const uint4*>(slots + static_cast<int64_t>(j) * kRowSlotBytes));
+    xs.na[j] = static_cast<int>(h.x);
+    xs.nu[j] = min(max(static_cast<int>(h.y), 0), kUndCap);
+    if (h.z != 0u) xs.overflow = 1;
+  }
+  sync_workers();
+  if (warp == 0) warp_prefix256(xs.nu, xs.uo, J, lane);
+  if (warp == 1) warp_prefix256(xs.na, xs.to, J, lane);   // (to: scratch here, its total is the count above the bin)
+  sync_workers();
+  const int U = xs.uo[J], A = xs.to[J];
+  if (xs.overflow != 0 || U > kUndRowCap) return false;
+  uint32_t* und = rs.und;
+  for (int i0 = tid; i0 < U; i0 += 4 * kBlockThreads) {   // (independent loads: four in flight per thread)
+    const float* src[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = min(i0 + u * kBlockThreads, U - 1);
+      int lo = 0, hi = J;   // the slot j with uo[j] <= i < uo[j + 1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (xs.uo[mid] <= i) lo = mid;
+        else hi = mid;
+      }
+      src[u] = reinterpret_cast<const float*>(slots + static_cast<int64_t>(lo) * kRowSlotBytes + 16) + (i - xs.uo[lo]);
+    }
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = ld_sys_f32(src[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * kBlockThreads < U) und[i0 + u * kBlockThreads] = __float_as_uint(v[u]);
+  }
+  const int U4 = (U + 3) & ~3;
+  if (tid < U4 - U) und[U + tid] = 0u;
+  sync_workers();
+  uint32_t tau = floor_tau;   // bin == 0, or the whole bin is taken: everything above the floor
+  int need_eq = 0;
+  if (bin != 0u) {
+    const int need = top_k - A;   // 1 <= need <= U by the choice of the bin
+    if (need > 0 && need < U) {
+      const Threshold<uint32_t> th = block_select_bits_smem(und, U4, need, sel);
+      if (th.need_eq != 0x7fffffff) {
+        tau = th.tau;
+        need_eq = th.need_eq;
+      }
+    }
+  }
+  // per slot: keys above the threshold and tied at it (one warp per slot in turn)
+  for (int j = warp; j < J; j += kWarps) {
+    int g = 0, e = 0;
+    const int n = xs.nu[j], o = xs.uo[j];
+    for (int i = lane; i < n; i += 32) {
+      const uint32_t v = und[o + i];
+      g += v > tau;
+      e += v == tau;
+    }
+    g = __reduce_add_sync(0xffffffffu, g);
+    e = __reduce_add_sync(0xffffffffu, e);
+    if (lane == 0) {
+      xs.g[j] = xs.na[j] + g;
+      xs.e[j] = need_eq > 0 ? e : 0;
+    }
+  }
+  sync_workers();
+  if (warp == 0) warp_prefix256(xs.e, xs.eo, J, lane);
+  sync_workers();
+  for (int j = tid; j < J; j += kBlockThreads) xs.take[j] = xs.g[j] + min(xs.e[j], max(0, need_eq - xs.eo[j]));
+  sync_workers();
+  if (warp == 0) warp_prefix256(xs.take, xs.to, J, lane);
+  sync_workers();
+  const int my_eq = min(xs.e[me], max(0, need_eq - xs.eo[me]));
+  const int off_g = xs.to[me], off_l = xs.to[me] - xs.to[x.rank * n_chunks];
+  const int total = xs.to[J], local_total = xs.to[(x.rank + 1) * n_chunks] - xs.to[x.rank * n_chunks];
+  // ---- this chunk's share, from its survivor list (position order)
+  Threshold<uint32_t> th;
+  th.tau = tau;
+  th.need_eq = my_eq;
+  th.n_sel = xs.take[me];
+  const int K = top_k;
+  block_emit_keys(rs.skey, n_s4, th, sel, [&](int idx, int slot) {
+    const uint32_t kv = rs.skey[idx];
+    const int pos = rs.spos[idx];
+    const float v = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
+    const int id = (base_pos + pos) * id_mul + id_add;
+    if (off_l + slot < x.pt_cols) x.pt[off_l + slot] = x.row_base + base_pos + pos;
+    const int o = off_g + slot;
+    if (o < K) {
+      if (x.cp == 1) {
+        x.out_v[o] = v;
+        x.out_i[o] = id;
+      } else {
+        for (int d = 0; d < x.cp; ++d) {
+          unsigned char* dst = x.arena + x.arena_offsets[d] + x.out_off;
+          reinterpret_cast<float*>(dst)[o] = v;
+          reinterpret_cast<int32_t*>(dst + static_cast<int64_t>(K) * 4)[o] = id;
+        }
+      }
+    }
+  });
+  if (tid == 0) {
+    if (chunk == 0) {
+      *x.k_valid = x.win_slots + min(local_total, x.pt_cols);
+      if (x.cp == 1) *x.sel_c = min(total, K);
+    }
+    if (x.cp > 1) {  // this task's slice on every rank: "published", and the length of the selection
+      for (int d = 0; d < x.cp; ++d)
+        *reinterpret_cast<int4*>(x.arena + x.arena_offsets[d] + x.out_off + static_cast<int64_t>(me) * x.slice_bytes +
+                                 static_cast<int64_t>(K) * 8) = make_int4(-1, min(total, K), 0, 0);
+    }
+  }
+  return true;
+}
 
 template <typename Emit>
 __device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int32_t* status, int b, int chunk, int n_chunks,
                                                      const float* sc_row, uint32_t* keys, int n_local, int base_pos, int limit,
-                                                     int top_k, SelectScratch& sel, uint32_t* hs, Emit emit) {
+                                                     int top_k, SelectScratch& sel, uint32_t* hs, Emit emit, int id_mul = 1,
+                                                     int id_add = 0) {
+  constexpr int PER = kThrBins / kBlockThreads;   // bins a thread owns in the scan from the top
+  static_assert(kThrBins % (4 * kBlockThreads) == 0, "the bin scan reads whole 16-byte pieces");
   const int tid = threadIdx.x;
   sync_workers();
-  for (int pos = tid; pos < n_local; pos += kBlockThreads)
-    keys[pos] = (base_pos + pos) < limit ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
   for (int i = tid; i < kThrBins; i += kBlockThreads) hs[i] = 0u;
   sync_workers();
   for (int pos = tid; pos < n_local; pos += kBlockThreads) {
-    const uint32_t k = keys[pos];
+    const uint32_t k = (base_pos + pos) < limit ? max(sortable_u32(sc_row[pos]), 1u) : 0u;
+    keys[pos] = k;
     if (k) atomicAdd(&hs[k >> kThrShift], 1u);
   }
   sync_workers();
@@ -260,33 +536,72 @@ __device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int
   }
   __threadfence();
   sync_workers();
+  const RowExact* x = rt.x;
+  const bool many = x != nullptr && x->cp > 1;   // the row spans several ranks: the histograms are exchanged
   if (tid == 0) {
-    atomicAdd(&rt.done[b], 1u);
-    const unsigned long long t0 = global_timer_ns();
+    const uint32_t before = atomicAdd(&rt.done[b], 1u);
+    sel.hist_bnd = (before + 1u == rt.target) ? 1 : 0;   // the last task of this rank's row to count in
     bool ok = true;
-    while (static_cast<int32_t>(*reinterpret_cast<volatile uint32_t*>(&rt.done[b]) - rt.target) < 0) {
-      nanosleep(64);
-      if (static_cast<long long>(global_timer_ns() - t0) > rt.budget_ns) {
-        ok = false;
-        break;
+    if (!many) {
+      const unsigned long long t0 = global_timer_ns();
+      while (static_cast<int32_t>(*reinterpret_cast<volatile uint32_t*>(&rt.done[b]) - rt.target) < 0) {
+        nanosleep(64);
+        if (static_cast<long long>(global_timer_ns() - t0) > rt.budget_ns) {
+          ok = false;
+          break;
+        }
       }
+      __threadfence();
+      if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -1 - b, chunk, rt.done[b], rt.target);
     }
-    __threadfence();
-    if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -1 - b, chunk, rt.done[b], rt.target);
     sel.bnd = ok ? 0 : -1;
   }
   sync_workers();
+  if (many) {
+    if (sel.hist_bnd) {  // this rank's row histogram is complete: it goes to every rank, then one notify each
+      __threadfence();
+      const int64_t at = x->hist_off + static_cast<int64_t>(x->rank) * kRowHistBytes;
+      for (int i = tid; i < kThrBins / 4; i += kBlockThreads) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(gh) + i);
+        for (int d = 0; d < x->cp; ++d) reinterpret_cast<uint4*>(x->arena + x->arena_offsets[d] + at)[i] = v;
+      }
+      __threadfence_system();
+      sync_workers();
+      if (tid == 0)
+        for (int d = 0; d < x->cp; ++d) x->ev.notify_1t(x->ev_hist, d);
+    }
+    if (tid == 0) {
+      unsigned long long seen = 0;
+      const bool ok = x->ev.poll_1t(x->ev_hist, x->hist_target, true, rt.budget_ns, &seen);
+      if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -500 - b, chunk, seen, x->hist_target);
+      sel.bnd = ok ? 0 : -1;
+    }
+    sync_workers();
+  }
   bool use_filter = sel.bnd >= 0;
   sync_workers();
   if (use_filter) {
-    // thread t owns the bins kThrBins-1-8t .. kThrBins-8-8t, scanned from the top
-    uint32_t c[8];
+    // thread t owns the bins kThrBins-1-PER*t .. kThrBins-PER-PER*t, scanned from the top
+    uint32_t c[PER];
     int local = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      c[j] = __ldcg(&gh[kThrBins - 1 - 8 * tid - j]);
-      local += static_cast<int>(c[j]);
+    for (int j = 0; j < PER; ++j) c[j] = 0u;
+    const int first = kThrBins - PER - PER * tid;   // lowest bin of this thread, a multiple of 4
+    for (int r = 0; r < (many ? x->cp : 1); ++r) {
+      const uint4* src = many ? reinterpret_cast<const uint4*>(x->arena + x->hist_off + static_cast<int64_t>(r) * kRowHistBytes)
+                              : reinterpret_cast<const uint4*>(gh);
+      src += first / 4;
+#pragma unroll
+      for (int q = 0; q < PER / 4; ++q) {
+        const uint4 v = many ? ld_sys_u4(src + q) : __ldcg(src + q);   // bins first + 4q .. first + 4q + 3, ascending
+        c[PER - 1 - 4 * q] += v.x;
+        c[PER - 2 - 4 * q] += v.y;
+        c[PER - 3 - 4 * q] += v.z;
+        c[PER - 4 - 4 * q] += v.w;
+      }
     }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) local += static_cast<int>(c[j]);
     const int lane = tid & 31, warp = tid >> 5;
     int wtot;
     int cum = warp_excl_scan(local, lane, &wtot);
@@ -294,13 +609,13 @@ __device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int
     sync_workers();
     for (int w = 0; w < warp; ++w) cum += sel.wgt[w];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (cum < top_k && cum + static_cast<int>(c[j]) >= top_k) sel.bnd = kThrBins - 1 - 8 * tid - j;  // (one thread at most)
+    for (int j = 0; j < PER; ++j) {
+      if (cum < top_k && cum + static_cast<int>(c[j]) >= top_k) sel.bnd = kThrBins - 1 - PER * tid - j;  // (one thread at most)
       cum += static_cast<int>(c[j]);
     }
     sync_workers();
     const uint32_t bin = static_cast<uint32_t>(sel.bnd);   // 0 when the row holds fewer than k scores: everything passes
-    // does this chunk's share fit its list?
+    // this chunk's scores in the bins >= bin
     int mine = 0;
     for (int i = tid; i < kThrBins; i += kBlockThreads) mine += static_cast<uint32_t>(i) >= bin ? static_cast<int>(hs[i]) : 0;
     mine = __reduce_add_sync(0xffffffffu, mine);
@@ -311,7 +626,13 @@ __device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) n_pass += sel.weq[w];
     sync_workers();
-    if (n_pass <= top_k) {
+    if (x != nullptr) {
+      if (chunk_publish_row_exact(rt, status, b, chunk, n_chunks, keys, n_local, base_pos, top_k, id_mul, id_add, bin, n_pass,
+                                  sel, *reinterpret_cast<RowExactScratch*>(hs + kThrBins)))
+        return -1;
+      sync_workers();
+    }
+    if (n_pass <= top_k) {   // the chunk's share fits its list
       Threshold<uint32_t> th;
       th.tau = bin ? (bin << kThrShift) - 1u : 0u;
       th.need_eq = 0;
@@ -800,7 +1121,7 @@ __device__ void logits_tile(const mdc_logits_params& p, int b, int chunk, unsign
       int n;
       if (rt && T == 1)  // (the raw ring is idle by now: it holds the chunk's histogram)
         n = chunk_emit_above_row_threshold(*rt, p.status, b, chunk, p.n_chunks, sc_row, keys, n_local, base_pos, limit, p.top_k,
-                                           sel, reinterpret_cast<uint32_t*>(ring), emit);
+                                           sel, reinterpret_cast<uint32_t*>(ring), emit, p.id_mul, p.id_add);
       else
         n = fused_chunk_select(sc_row, keys, n_local, base_pos, limit, p.top_k, sel, emit);
       if (tid == 0) p.cand_c[(static_cast<int64_t>(b) * T + t) * p.n_chunks + chunk] = n;

@@ -36,6 +36,8 @@ from .schedule.device import launch_megakernel, upload_schedule
 D_V = 512
 LSE_GROUPS = 8
 QPATH_SLICES = 8
+THR_BINS = 4096   # MDC_THR_BINS of include/mdc.h
+THR_HIST_BYTES, THR_SLOT_BYTES = THR_BINS * 4, 16 + 512 * 4   # exchange space of the exact row selection
 
 
 def l1_groups_for(n_chunks: int) -> int:
@@ -155,7 +157,7 @@ def q_block_bytes(heads: int = 128, d_qk: int = 576) -> int:
 
 
 def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: int = 1, cmp_stats_bytes: int = 0,
-                  q_bytes: int = 0, cand_lists: int = 1):
+                  q_bytes: int = 0, cand_lists: int = 1, thr_chunks: int = 0):
     cand = B * cp * cand_lists * (top_k * 8 + 16)
     inbox = -(-B // cp) * cp * attn_splits * (heads * D_V * 2 + heads * 4)
     regions = {"cand": cand, "inbox": inbox}
@@ -163,6 +165,8 @@ def arena_regions(B: int, cp: int, top_k: int, heads: int = 128, attn_splits: in
         regions["q"] = B * q_bytes
     if cmp_stats_bytes:
         regions["cmp_stats"] = B * cp * cmp_stats_bytes
+    if thr_chunks:   # exact row selection: per row, per rank a histogram, per (rank, chunk) a key slot
+        regions["thr"] = B * cp * (THR_HIST_BYTES + thr_chunks * THR_SLOT_BYTES)
     return regions
 
 
@@ -186,7 +190,7 @@ class DsaDecodeLayer:
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
-                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True):
+                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact: bool = True):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
         distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
@@ -223,6 +227,10 @@ class DsaDecodeLayer:
         # several ranks, one merge level: the chunk lists go straight to every rank (no exact local top-k
         # in between: the global top-k lies inside the union of what the chunks emit)
         self.cand_direct = cand_direct and row_threshold and cp > 1 and self.l1_groups == 1 and cp * self.n_chunks <= 256
+        # row_exact: the chunk tasks of a row (on all ranks) settle the exact top-k themselves; the merge
+        # task behind them stays in the graph and only acts on rows that fell back (heavy ties)
+        self.row_exact = (row_exact and row_threshold and cp * self.n_chunks <= 256 and top_k % 4 == 0
+                          and (cp == 1 or self.cand_direct))
         self.compressor = compressor
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
@@ -247,12 +255,14 @@ class DsaDecodeLayer:
                 elif op in (N.OP_MERGE_L1, N.OP_MERGE_L1A, N.OP_MERGE_L2, N.OP_ATTN, N.OP_LSE_MERGE):
                     seen_consumer = True
         self.dsched = upload_schedule(self.schedule, self.device)
-        self.events = alloc_event_buffer(len(events), rank, cp, group_name, self.device)
+        self.n_dag_events = len(events)
+        self.events = alloc_event_buffer(len(events) + (2 * B if self.row_exact else 0), rank, cp, group_name, self.device)
         from .tiles.compress import stats_bytes
         cmp_bytes = stats_bytes(compressor.ratio) if compressor is not None else 0
         self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes,
                                                q_block_bytes(heads, d_qk) if distribute_q else 0,
-                                               self.n_chunks if self.cand_direct else 1),
+                                               self.n_chunks if self.cand_direct else 1,
+                                               self.n_chunks if self.row_exact else 0),
                                  phases, rank, cp, group_name, self.device)
         self.n_owned = len(range(rank, B, cp))
         # distribute_q: the owned sequences' query blocks, one contiguous block [q_idx | w | q_mla] that a
@@ -274,7 +284,7 @@ class DsaDecodeLayer:
         self.mid_v = torch.empty(B, G, K, device=dev)
         self.mid_i = torch.empty(B, G, K, dtype=torch.int32, device=dev)
         self.mid_c = torch.zeros(B, G, dtype=torch.int32, device=dev)
-        self.thr_hist = torch.zeros(2, B, 2048, dtype=torch.int32, device=dev) if row_threshold else None
+        self.thr_hist = torch.zeros(2, B, THR_BINS, dtype=torch.int32, device=dev) if row_threshold else None
         self.thr_done = torch.zeros(B, dtype=torch.int32, device=dev) if row_threshold else None
         self.sel_v = torch.zeros(B, K, device=dev)
         self.sel_i = torch.zeros(B, K, dtype=torch.int32, device=dev)
@@ -324,6 +334,8 @@ class DsaDecodeLayer:
         L.kv_seq_stride = self.kv_seq_stride
         L.kv_group = self.kv_group
         L.cand_direct = int(self.cand_direct)
+        if self.row_exact:
+            L.thr_exact, L.thr_ev_base, L.thr_off = 1, self.n_dag_events, self.arena.regions["thr"]
         L.attn_splits = self.attn_splits
         L.l1_groups = self.l1_groups
         L.mid_v, L.mid_i, L.mid_c = N.ptr(self.mid_v), N.ptr(self.mid_i), N.ptr(self.mid_c)
