@@ -53,7 +53,7 @@ struct EventSet {
   }
   // single-thread bounded poll; returns the last value seen through *seen
   __device__ bool poll_1t(int ev, unsigned long long target, bool sys, long long budget_ns,
-                          unsigned long long* seen) const {
+                          unsigned long long* seen, uint32_t max_backoff = 512) const {
     const unsigned long long* p = cell(ev);
     unsigned long long v = sys ? ld_acquire_sys_u64(p) : ld_acquire_gpu_u64(p);
     if (v < target) {
@@ -61,7 +61,7 @@ struct EventSet {
       uint32_t backoff = 32;
       while (v < target) {
         nanosleep(backoff);
-        if (backoff < 512) backoff <<= 1;
+        if (backoff < max_backoff) backoff <<= 1;
         v = sys ? ld_acquire_sys_u64(p) : ld_acquire_gpu_u64(p);
         if (v < target && static_cast<long long>(global_timer_ns() - t0) > budget_ns) break;
       }

@@ -115,7 +115,7 @@ __device__ __host__ inline int64_t q_mla_bytes(const mdc_layer_params& L) { retu
 // One SM moves about 45 GB/s this way, so the big array is cut into slices that run as separate tasks.
 // part 0: the indexer's share (q_idx, weights: 16.6 KB, what the LOGITS tasks wait for); part 1 + s:
 // slice s of n_slices of the attention query (147 KB in all, needed only once the selection is done).
-__device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, int n_slices, unsigned long long phase,
+__device__ __noinline__ void op_qpath(const mdc_mega_params& p, int b, int part, int n_slices, unsigned long long phase,
                                 unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   if (!L.q_stage || b % L.cp != L.rank) return;
@@ -176,7 +176,7 @@ __device__ inline void op_qpath(const mdc_mega_params& p, int b, int part, int n
 // The step's new token of sequence b: on the rank that owns its position, the index-K record is
 // quantised into the paged cache, the KV row is copied into the pool and the rank-local length grows
 // by one; every rank then (optionally) advances its copy of the global length.
-__device__ inline void op_kvwrite(const mdc_mega_params& p, int b) {
+__device__ __noinline__ void op_kvwrite(const mdc_mega_params& p, int b) {
   const mdc_layer_params& L = p.layer;
   if (!L.kvw_glen) return;
   const mdc_logits_params& lp = L.logits;
@@ -223,7 +223,7 @@ __device__ inline void redirect_q(const mdc_mega_params& p, unsigned long long p
 }
 
 template <int FMT, int PAGE>
-__device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned long long phase, unsigned char* smem) {
+__device__ __noinline__ void op_logits(const mdc_mega_params& p, int b, int chunk, unsigned long long phase, unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   mdc_logits_params lp = L.logits;
   redirect_q(p, phase, &lp, nullptr);
@@ -314,7 +314,7 @@ __device__ inline void op_logits(const mdc_mega_params& p, int b, int chunk, uns
 }
 
 // first level of a two-level local merge: the chunk lists of group g of sequence b -> one list
-__device__ inline void op_merge_l1a(const mdc_mega_params& p, int b, int g, unsigned char* smem) {
+__device__ __noinline__ void op_merge_l1a(const mdc_mega_params& p, int b, int g, unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
   const int K = L.top_k, C = L.n_chunks, G = max(1, L.l1_groups);
@@ -333,7 +333,7 @@ __device__ inline void op_merge_l1a(const mdc_mega_params& p, int b, int g, unsi
 
 // chunk (or group) candidate lists of sequence b -> this rank's top-k, written into the
 // own slice of the candidate region and copied to every peer's arena
-__device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+__device__ __noinline__ void op_merge_l1(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
@@ -405,7 +405,7 @@ __device__ inline void op_merge_l1(const mdc_mega_params& p, int b, unsigned lon
 // cp candidate lists of sequence b (one per rank, in the own arena) -> global
 // top-k (identical on every rank) and this rank's gather list for attention
 template <bool SYS>
-__device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
+__device__ __noinline__ void op_merge_l2(const mdc_mega_params& p, int b, unsigned long long phase, unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   MergeSmem& sm = *reinterpret_cast<MergeSmem*>(smem);
   const int K = L.top_k;
@@ -461,7 +461,7 @@ __device__ inline void op_merge_l2(const mdc_mega_params& p, int b, unsigned lon
 // blocks of 128 a task is 128 heads x 128 output columns on the tcgen05 tile (task index =
 // 4 * head block + column block, all threads take part); otherwise 64 heads x 256 columns on
 // the mma.sync tile (task index = 2 * head block + column half, worker threads only).
-__device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, int split, unsigned long long phase,
+__device__ __noinline__ void op_attn(const mdc_mega_params& p, int b, int hbv, int split, unsigned long long phase,
                                unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
@@ -494,7 +494,7 @@ __device__ inline void op_attn(const mdc_mega_params& p, int b, int hbv, int spl
 // owner of sequence b: cp inbox slices -> merged output
 // (task = head group hq of n_groups: the merge of one sequence is spread over several blocks)
 template <bool SYS>
-__device__ inline void op_lse_merge(const mdc_mega_params& p, int b, int hq, int n_groups, unsigned long long phase,
+__device__ __noinline__ void op_lse_merge(const mdc_mega_params& p, int b, int hq, int n_groups, unsigned long long phase,
                                     unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   n_groups = max(1, min(n_groups, L.H));
@@ -519,7 +519,7 @@ __device__ inline void op_lse_merge(const mdc_mega_params& p, int b, int hq, int
 // step, pushes this rank's statistics to the entry's owner; the finalize runs on the owner after all
 // cp statistics have arrived (the task's wait edge) and writes the pools.  Off the critical path:
 // the new entry becomes visible to the next step.
-__device__ inline void op_cmp(const mdc_mega_params& p, int b, bool finalize, unsigned long long phase, unsigned char* smem) {
+__device__ __noinline__ void op_cmp(const mdc_mega_params& p, int b, bool finalize, unsigned long long phase, unsigned char* smem) {
   mdc_compress_params c = p.layer.cmp;
   c.arena = p.arena;
   c.stats_off += phase_offset(p, phase);

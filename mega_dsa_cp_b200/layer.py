@@ -190,11 +190,16 @@ class DsaDecodeLayer:
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
-                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact: bool = True):
+                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact: bool | None = None,
+                 q_tasks: bool | None = None):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
         distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
         then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
+        With one rank the kernels read the staging block in place and no QPATH task runs, unless
+        q_tasks=True asks for them.
+        row_exact: the chunk tasks settle the row's exact top-k themselves (default: with one rank;
+        across ranks the two exchange rounds cost more than the merge they save: measured).
         compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
         runs its step / finalize as tasks (bind_compressor() supplies the per-step tensors)."""
         self.B, self.cp, self.rank, self.K, self.H, self.d_qk = B, cp, rank, top_k, heads, d_qk
@@ -202,6 +207,7 @@ class DsaDecodeLayer:
         self.n_chunks = -(-max_pages // blocks_per_chunk)
         self.kv_seq_stride = kv_seq_stride or max_pages * page_tokens
         self.kv_group = kv_group
+        self.q_tasks = distribute_q and (cp > 1 if q_tasks is None else bool(q_tasks))
         assert kv_group >= 1 and not (kv_group > 1 and (kvwrite or compressor is not None))
         self.device = torch.device(device)
         self.phases = phases
@@ -229,13 +235,15 @@ class DsaDecodeLayer:
         self.cand_direct = cand_direct and row_threshold and cp > 1 and self.l1_groups == 1 and cp * self.n_chunks <= 256
         # row_exact: the chunk tasks of a row (on all ranks) settle the exact top-k themselves; the merge
         # task behind them stays in the graph and only acts on rows that fell back (heavy ties)
+        if row_exact is None:
+            row_exact = cp == 1
         self.row_exact = (row_exact and row_threshold and cp * self.n_chunks <= 256 and top_k % 4 == 0
                           and (cp == 1 or self.cand_direct))
         self.compressor = compressor
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
         tasks, events, ops = build_layer_dag(B, self.n_chunks, cp, heads, attn_splits, self.l1_groups,
-                                             compressor=compressor is not None, qpath=distribute_q, kvwrite=kvwrite,
+                                             compressor=compressor is not None, qpath=self.q_tasks, kvwrite=kvwrite,
                                              cand_direct=self.cand_direct)
         self.kvwrite = kvwrite
         self.distribute_q = distribute_q
@@ -260,7 +268,7 @@ class DsaDecodeLayer:
         from .tiles.compress import stats_bytes
         cmp_bytes = stats_bytes(compressor.ratio) if compressor is not None else 0
         self.arena = alloc_arena(arena_regions(B, cp, top_k, heads, attn_splits, cmp_bytes,
-                                               q_block_bytes(heads, d_qk) if distribute_q else 0,
+                                               q_block_bytes(heads, d_qk) if self.q_tasks else 0,
                                                self.n_chunks if self.cand_direct else 1,
                                                self.n_chunks if self.row_exact else 0),
                                  phases, rank, cp, group_name, self.device)
@@ -309,8 +317,11 @@ class DsaDecodeLayer:
                 self.q_idx_owned.copy_(x.q_idx)
                 self.w_idx_owned.copy_(x.w_idx)
                 self.q_mla_owned.copy_(x.q_mla)
-            qbase = self.arena.tensor.data_ptr() + self.arena.regions["q"]
-            q_ptr, w_ptr, qm_ptr = qbase, qbase + B * 64 * 128 * 2, qbase + B * (64 * 128 * 2 + 64 * 4)
+            if self.q_tasks:
+                qbase = self.arena.tensor.data_ptr() + self.arena.regions["q"]
+                q_ptr, w_ptr, qm_ptr = qbase, qbase + B * 64 * 128 * 2, qbase + B * (64 * 128 * 2 + 64 * 4)
+            else:   # one rank: every sequence is owned, the kernels read the staging block in place
+                q_ptr, w_ptr, qm_ptr = N.ptr(self.q_idx_owned), N.ptr(self.w_idx_owned), N.ptr(self.q_mla_owned)
         else:
             assert x.q_idx.dtype == torch.bfloat16 and x.q_mla.dtype == torch.bfloat16
             q_ptr, w_ptr, qm_ptr = N.ptr(x.q_idx), N.ptr(x.w_idx), N.ptr(x.q_mla)
@@ -345,7 +356,7 @@ class DsaDecodeLayer:
         L.sel_v, L.sel_i, L.sel_c = N.ptr(self.sel_v), N.ptr(self.sel_i), N.ptr(self.sel_c)
         L.out, L.out_lse = N.ptr(self.out), N.ptr(self.out_lse)
         L.out_dtype = N.DT_F32 if self.out.dtype == torch.float32 else N.DT_BF16
-        if self.distribute_q:
+        if self.q_tasks:
             L.q_stage, L.q_off = N.ptr(self.q_stage), self.arena.regions["q"]
         L.thr_hist, L.thr_done = N.ptr(self.thr_hist), N.ptr(self.thr_done)
         self._params, self._inputs = L, x

@@ -76,6 +76,25 @@ def main():
     ref_sel = layer.sel_i.clone()
     dist.broadcast(ref_sel, 0)
     ok &= bool(torch.equal(ref_sel, layer.sel_i))
+    # ---- the exact row selection across ranks (histogram exchange + undecided keys; not the default there):
+    # same selection, same order, same output as the candidate-list path above
+    xlayer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
+                            kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
+                            group_name=dist.group.WORLD.group_name, device=dev, row_exact=True)
+    assert xlayer.row_exact
+    xlayer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx), d(w_idx), d(q_mla), d(kv_loc)))
+    dist.barrier()
+    for _ in range(3):
+        xlayer.step(wait_budget_ns=5_000_000_000)
+        torch.cuda.synchronize()
+        xlayer.check_status()
+        dist.barrier()
+    ok &= bool(torch.equal(xlayer.sel_c, layer.sel_c))
+    for b in range(B):
+        n = int(layer.sel_c[b])
+        ok &= bool(torch.equal(xlayer.sel_i[b, :n], layer.sel_i[b, :n]))
+        if b % world == rank:
+            ok &= float((xlayer.out[b // world] - layer.out[b // world]).abs().max()) < 1e-3
     # ---- the compressor as tasks of the same persistent kernel, across the real ranks: 13 steps of the
     # ratio-4 window machine (3 closing groups), each entry checked on its owner (n % world)
     from test_gpu_compress import _post_checks

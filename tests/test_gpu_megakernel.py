@@ -130,7 +130,7 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc, qpath, exact):
     kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
     seq = torch.tensor([S - 100 * b for b in range(B)], dtype=torch.int32)
     layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
-                           out_dtype=torch.float32, n_ctas=64, distribute_q=qpath,   # qpath: q through the QPATH task
+                           out_dtype=torch.float32, n_ctas=64, distribute_q=qpath, q_tasks=qpath,   # qpath: q through the QPATH task
                            row_exact=exact)   # exact: the chunk tasks settle the row's top-k, the merge only passes it on
     d = lambda t: t.to(DEV)
     layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
