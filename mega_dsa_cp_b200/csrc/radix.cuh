@@ -371,6 +371,185 @@ __device__ inline Threshold<uint32_t> block_select_bits_smem(const uint32_t* key
   return th;
 }
 
+// The k-th largest of the valid (non-zero) u32 keys of a shared-memory array by histograms instead of
+// one block-wide pass per bit: the keys' common upper bits are skipped (kmax ^ kmin), then each level
+// histograms the next 11 bits of the keys that are still undecided (2048 bins: spread-out keys meet
+// little contention), finds the boundary bin and descends into it; as soon as the boundary bin holds at
+// most kBitsListCap keys they are copied to a list and one warp settles the remaining bits.  Three
+// levels cover 32 bits.  Same result and conventions as block_select_bits_smem.  hist: 2048 words of
+// shared memory.  keys: 16-byte aligned, n_pos a multiple of 4 or zero-padded to one.
+__device__ inline Threshold<uint32_t> block_select_hist_smem(const uint32_t* keys, int n_pos, int k, SelectScratch& sc,
+                                                            uint32_t* hist, int* n_eq_out = nullptr) {
+  constexpr int kBins = 2048, kBits = 11, PER = kBins / kBlockThreads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n4 = n_pos >> 2;
+  const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+  Threshold<uint32_t> th;
+  uint32_t kmax = 0u, kmin = 0xffffffffu;
+  int mine = 0;
+  for (int i = tid; i < n4; i += kBlockThreads) {
+    const uint4 q = k4[i];
+    const uint32_t v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mine += v[j] != 0u;
+      kmax = max(kmax, v[j]);
+      kmin = min(kmin, v[j] != 0u ? v[j] : 0xffffffffu);
+    }
+  }
+  for (int i = (n4 << 2) + tid; i < n_pos; i += kBlockThreads) {
+    const uint32_t v = keys[i];
+    mine += v != 0u;
+    kmax = max(kmax, v);
+    kmin = min(kmin, v != 0u ? v : 0xffffffffu);
+  }
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  kmax = __reduce_max_sync(0xffffffffu, kmax);
+  kmin = __reduce_min_sync(0xffffffffu, kmin);
+  sync_workers();
+  if (lane == 0) {
+    sc.wgt[warp] = mine;
+    sc.hist[warp] = kmax;
+    sc.hist[8 + warp] = kmin;
+  }
+  sync_workers();
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    total += sc.wgt[w];
+    kmax = max(kmax, sc.hist[w]);
+    kmin = min(kmin, sc.hist[8 + w]);
+  }
+  if (total <= k) {
+    th.tau = 0;
+    th.need_eq = 0x7fffffff;
+    th.n_sel = total;
+    sync_workers();
+    return th;
+  }
+  int lo_bits = 32 - __clz(static_cast<int>((kmax ^ kmin) | 1u));   // the low bits in which valid keys differ
+  uint32_t prefix = lo_bits >= 32 ? 0u : (kmax >> lo_bits) << lo_bits;
+  int remaining = k;   // rank of the wanted key among the keys that share `prefix` above lo_bits
+#pragma unroll 1
+  while (true) {
+    const int shift = max(0, lo_bits - kBits);
+    const uint32_t bmask = (1u << (lo_bits - shift)) - 1u;
+    for (int i = tid; i < kBins; i += kBlockThreads) hist[i] = 0u;
+    if (tid == 0) {
+      sc.bnd = 0;
+      sc.c_gt = 0;
+      sc.hist_bnd = 0;
+      sc.list_n = 0;
+    }
+    sync_workers();
+    for (int i = tid; i < n4; i += kBlockThreads) {
+      const uint4 q = k4[i];
+      const uint32_t v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool in = v[j] != 0u && (lo_bits >= 32 || ((v[j] ^ prefix) >> lo_bits) == 0u);
+        if (in) atomicAdd(&hist[(v[j] >> shift) & bmask], 1u);
+      }
+    }
+    for (int i = (n4 << 2) + tid; i < n_pos; i += kBlockThreads) {
+      const uint32_t v = keys[i];
+      if (v != 0u && (lo_bits >= 32 || ((v ^ prefix) >> lo_bits) == 0u)) atomicAdd(&hist[(v >> shift) & bmask], 1u);
+    }
+    sync_workers();
+    uint32_t c[PER];
+    int local = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      c[j] = hist[kBins - 1 - PER * tid - j];
+      local += static_cast<int>(c[j]);
+    }
+    int wtot;
+    int cum = warp_excl_scan(local, lane, &wtot);
+    if (lane == 0) sc.wgt[warp] = wtot;
+    sync_workers();
+    for (int w = 0; w < warp; ++w) cum += sc.wgt[w];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if (cum < remaining && cum + static_cast<int>(c[j]) >= remaining) {   // (one thread at most)
+        sc.bnd = kBins - 1 - PER * tid - j;
+        sc.c_gt = cum;
+        sc.hist_bnd = static_cast<int>(c[j]);
+      }
+      cum += static_cast<int>(c[j]);
+    }
+    sync_workers();
+    const int inside = sc.hist_bnd;
+    prefix |= static_cast<uint32_t>(sc.bnd) << shift;
+    remaining -= sc.c_gt;
+    lo_bits = shift;
+    sync_workers();
+    if (shift == 0) {   // the bin is one key value: `inside` keys equal it, `remaining` of them are wanted
+      th.tau = prefix;
+      th.need_eq = remaining;
+      th.n_sel = k;
+      if (n_eq_out) *n_eq_out = inside;
+      return th;
+    }
+    if (inside <= kBitsListCap) break;
+  }
+  // the keys of the boundary bin -> list; one warp settles their low lo_bits bits
+  {
+    const int n_iter = ceil_div(n_pos, kBlockThreads);
+#pragma unroll 1
+    for (int it = 0; it < n_iter; ++it) {
+      const int i = it * kBlockThreads + tid;
+      const uint32_t v = i < n_pos ? keys[i] : 0u;
+      const bool in = v != 0u && ((v ^ prefix) >> lo_bits) == 0u;
+      const uint32_t m = __ballot_sync(0xffffffffu, in);
+      if (m != 0u) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&sc.list_n, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        const int slot = base + __popc(m & ((1u << lane) - 1u));
+        if (in && slot < kBitsListCap) sc.list[slot] = v;
+      }
+    }
+  }
+  sync_workers();
+  if (warp == 0) {
+    constexpr int LPER = kBitsListCap / 32;
+    const int ln = min(sc.list_n, kBitsListCap);
+    uint32_t lk[LPER];
+#pragma unroll
+    for (int j = 0; j < LPER; ++j) lk[j] = (j * 32 + lane < ln) ? sc.list[j * 32 + lane] : 0u;
+    uint32_t t2 = prefix;
+#pragma unroll 1
+    for (int bit = lo_bits - 1; bit >= 0; --bit) {
+      const uint32_t cand = t2 | (1u << bit);
+      int cnt = 0;
+#pragma unroll
+      for (int j = 0; j < LPER; ++j) cnt += lk[j] >= cand;
+      cnt = __reduce_add_sync(0xffffffffu, cnt);
+      if (cnt >= remaining) t2 = cand;
+    }
+    int g = 0, e = 0;
+#pragma unroll
+    for (int j = 0; j < LPER; ++j) {
+      g += lk[j] > t2;
+      e += lk[j] == t2;
+    }
+    g = __reduce_add_sync(0xffffffffu, g);
+    e = __reduce_add_sync(0xffffffffu, e);
+    if (lane == 0) {
+      sc.fin_tau = t2;
+      sc.fin_gt = g;
+      sc.fin_eq = e;
+    }
+  }
+  sync_workers();
+  th.tau = sc.fin_tau;
+  th.need_eq = remaining - sc.fin_gt;
+  th.n_sel = k;
+  if (n_eq_out) *n_eq_out = sc.fin_eq;
+  sync_workers();
+  return th;
+}
+
 // Deterministic emit of the selected elements in position order.
 // emit(pos, slot) is called once per selected element; returns the count.
 template <typename KeyT, typename Src, typename Emit>

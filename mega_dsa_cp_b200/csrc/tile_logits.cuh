@@ -313,98 +313,6 @@ struct RowExactScratch {
   RowExactSmem xs;
 };
 
-// The need-th largest of n keys that share their upper 32 - kThrShift bits (all of one row bin), 0 < need < n:
-// one histogram pass over the next 11 bits narrows the search to one sub-bin, whose few keys one warp then
-// settles.  hist2: 2048 words of shared memory.  Same result as block_select_bits_smem, which also serves as
-// the fallback when the sub-bin is long (keys that agree in 23 bits).
-__device__ inline Threshold<uint32_t> select_inside_bin(const uint32_t* und, int n, int n4, int need, uint32_t* hist2,
-                                                       SelectScratch& sc) {
-  constexpr int kBins2 = 2048, kShift2 = kThrShift - 11, PER = kBins2 / kBlockThreads;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < kBins2; i += kBlockThreads) hist2[i] = 0u;
-  if (tid == 0) {
-    sc.bnd = -1;
-    sc.list_n = 0;
-  }
-  sync_workers();
-  for (int i = tid; i < n; i += kBlockThreads) atomicAdd(&hist2[(und[i] >> kShift2) & (kBins2 - 1)], 1u);
-  sync_workers();
-  uint32_t c[PER];
-  int local = 0;
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    c[j] = hist2[kBins2 - 1 - PER * tid - j];
-    local += static_cast<int>(c[j]);
-  }
-  int wtot;
-  int cum = warp_excl_scan(local, lane, &wtot);
-  if (lane == 0) sc.wgt[warp] = wtot;
-  sync_workers();
-  for (int w = 0; w < warp; ++w) cum += sc.wgt[w];
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    if (cum < need && cum + static_cast<int>(c[j]) >= need) {   // (one thread at most)
-      sc.bnd = kBins2 - 1 - PER * tid - j;
-      sc.c_gt = cum;                      // keys in higher sub-bins
-      sc.hist_bnd = static_cast<int>(c[j]);
-    }
-    cum += static_cast<int>(c[j]);
-  }
-  sync_workers();
-  const int sub = sc.bnd, above = sc.c_gt, inside = sc.hist_bnd;
-  if (sub < 0 || inside > kBitsListCap) {
-    sync_workers();
-    return block_select_bits_smem(und, n4, need, sc);
-  }
-  for (int i0 = 0; i0 < n; i0 += kBlockThreads) {
-    const int i = i0 + tid;
-    const uint32_t v = i < n ? und[i] : 0u;
-    const bool in = i < n && static_cast<int>((v >> kShift2) & (kBins2 - 1)) == sub;
-    const uint32_t m = __ballot_sync(0xffffffffu, in);
-    if (m != 0u) {
-      int base = 0;
-      if (lane == 0) base = atomicAdd(&sc.list_n, __popc(m));
-      base = __shfl_sync(0xffffffffu, base, 0);
-      const int slot = base + __popc(m & ((1u << lane) - 1u));
-      if (in && slot < kBitsListCap) sc.list[slot] = v;
-    }
-  }
-  sync_workers();
-  if (warp == 0) {
-    constexpr int LPER = kBitsListCap / 32;
-    const int ln = min(sc.list_n, kBitsListCap);
-    const int want = need - above;   // 1 <= want <= ln
-    uint32_t lk[LPER];
-#pragma unroll
-    for (int j = 0; j < LPER; ++j) lk[j] = (j * 32 + lane < ln) ? sc.list[j * 32 + lane] : 0u;
-    uint32_t t2 = ln > 0 ? (sc.list[0] & ~((1u << kShift2) - 1u)) : 0u;   // the sub-bin's common upper bits
-#pragma unroll 1
-    for (int bit = kShift2 - 1; bit >= 0; --bit) {
-      const uint32_t cand = t2 | (1u << bit);
-      int cnt = 0;
-#pragma unroll
-      for (int j = 0; j < LPER; ++j) cnt += lk[j] >= cand;
-      cnt = __reduce_add_sync(0xffffffffu, cnt);
-      if (cnt >= want) t2 = cand;
-    }
-    int g = 0;
-#pragma unroll
-    for (int j = 0; j < LPER; ++j) g += lk[j] > t2;
-    g = __reduce_add_sync(0xffffffffu, g);
-    if (lane == 0) {
-      sc.fin_tau = t2;
-      sc.fin_gt = above + g;
-    }
-  }
-  sync_workers();
-  Threshold<uint32_t> th;
-  th.tau = sc.fin_tau;
-  th.need_eq = need - sc.fin_gt;
-  th.n_sel = need;
-  sync_workers();
-  return th;
-}
-
 // Steps b and c of the exact mode, after the boundary bin `bin` of the global row is known (0: the row
 // holds fewer than top_k scores, everything valid is selected).  n_pass: this chunk's scores in bins >= bin.
 // Returns true when the row was published (this task emitted its share), false when the row falls back.
@@ -526,7 +434,7 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
   if (bin != 0u) {
     const int need = top_k - A;   // 1 <= need <= U by the choice of the bin
     if (need > 0 && need < U) {
-      const Threshold<uint32_t> th = select_inside_bin(und, U, U4, need, hist2, sel);
+      const Threshold<uint32_t> th = block_select_hist_smem(und, U4, need, sel, hist2);
       if (th.need_eq != 0x7fffffff) {
         tau = th.tau;
         need_eq = th.need_eq;

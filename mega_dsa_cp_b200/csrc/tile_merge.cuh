@@ -481,10 +481,12 @@ __device__ inline int merge_staged_hybrid(int n_pos, int top_k, float* out_v, in
 // logit threshold rank highest, tied entries rank by ~id, everything else is out.
 template <typename IdFn>
 __device__ inline int merge_staged_bits(int n_pos, int top_k, float* out_v, int32_t* out_i, int32_t* out_c, int32_t* dbg,
-                                        MergeSmem& sm, const uint32_t* vb, IdFn id_of) {
+                                        MergeSmem& sm, const uint32_t* vb, IdFn id_of, uint32_t* hist = nullptr) {
   const int tid = threadIdx.x;
   int n_eq = 0;
-  Threshold<uint32_t> th = block_select_bits_smem(vb, n_pos, top_k, sm.sel, &n_eq);
+  // hist (2048 words of shared memory) given: the histogram search; else one block-wide pass per bit
+  Threshold<uint32_t> th = hist ? block_select_hist_smem(vb, n_pos, top_k, sm.sel, hist, &n_eq)
+                                : block_select_bits_smem(vb, n_pos, top_k, sm.sel, &n_eq);
   const int expect = th.n_sel;
   int n;
   auto put = [&](int pos, int slot) {
@@ -622,8 +624,11 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
         return n;
       }
     }
-    // a long row (several full lists): drop what cannot reach the top k before the exact search
     const int used = (compact ? n_cap : n_pos) * 8;
+    if (stage_bytes - used >= 2048 * 4)   // room for a histogram behind the staged row: the histogram search
+      return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; },
+                               reinterpret_cast<uint32_t*>(stage + used));
+    // a long row (several full lists): drop what cannot reach the top k before the exact search
     const int cap = ((stage_bytes - used - 2048 * 4) / 8) & ~3;
     if (n_valid >= 2 * top_k && n_pos % 4 == 0 && cap >= top_k + 4) {
       uint32_t* hist = reinterpret_cast<uint32_t*>(stage + used);
