@@ -3,11 +3,12 @@
 
 namespace mdc {
 constexpr int kMergeStageMax = 200 * 1024;  // rows of up to 25600 positions are staged in shared memory
+constexpr int kMergeHistBytes = 2048 * 4;    // behind a staged row: the histogram of the threshold search
 __global__ void __launch_bounds__(kBlockThreads) merge_topk_kernel(const __grid_constant__ mdc_merge_topk_params p) {
   __shared__ MergeSmem sm;
   extern __shared__ __align__(16) unsigned char stage[];
   const int n_pos = p.L * p.maxK;
-  const int need = n_pos * 8 <= kMergeStageMax ? n_pos * 8 : (n_pos * 4 <= kMergeStageMax ? n_pos * 4 : 0);
+  const int need = n_pos * 8 <= kMergeStageMax ? n_pos * 8 + kMergeHistBytes : (n_pos * 4 <= kMergeStageMax ? n_pos * 4 : 0);
   merge_topk_tile(p, blockIdx.x, sm, need ? stage : nullptr, need);
 }
 }  // namespace mdc
@@ -19,8 +20,9 @@ extern "C" int mdc_merge_topk_launch(const mdc_merge_topk_params* p, void* strea
     return MDC_ERR_BAD_SHAPE;
   if (static_cast<int64_t>(p->L) * p->maxK > (1ll << 30)) return MDC_ERR_TOO_LARGE;
   const int64_t n_pos = static_cast<int64_t>(p->L) * p->maxK;
-  const int smem = n_pos * 8 <= kMergeStageMax ? static_cast<int>(n_pos * 8) : (n_pos * 4 <= kMergeStageMax ? static_cast<int>(n_pos * 4) : 0);
-  MDC_CUDA_OK(cudaFuncSetAttribute(merge_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeStageMax));
+  const int smem = n_pos * 8 <= kMergeStageMax ? static_cast<int>(n_pos * 8) + kMergeHistBytes
+                                               : (n_pos * 4 <= kMergeStageMax ? static_cast<int>(n_pos * 4) : 0);
+  MDC_CUDA_OK(cudaFuncSetAttribute(merge_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeStageMax + kMergeHistBytes));
   merge_topk_kernel<<<p->B * p->q_len, kBlockThreads, smem, static_cast<cudaStream_t>(stream)>>>(*p);
   MDC_CUDA_OK(cudaGetLastError());
   return MDC_OK;

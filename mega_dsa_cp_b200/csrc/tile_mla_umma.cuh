@@ -122,10 +122,12 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
   constexpr int S = SM::kStages;
   constexpr uint32_t kQCols = DQK / 2, kOCol = kQCols, kSCol = kOCol + kMuDv, kPCol = kSCol + kMuTile;
   static_assert(kPCol + kMuTile / 2 <= 512, "tensor memory over-subscribed");
-  static_assert(SM::kPanels * kMuHeads * 128 <= S * SM::kStageBytes, "the staged query must fit the KV ring");
+  static_assert(S >= 2 && SM::kPanels * kMuHeads * 128 <= (S - 1) * SM::kStageBytes,
+                "the staged query must fit the KV ring behind its first stage");
   constexpr long long kBudget = 1ll << 31;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* kst = smem + SM::kK;
+  unsigned char* qst = kst + SM::kStageBytes;   // the query rows are staged in stages 1.. while tile 0 lands in stage 0
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::kBars);
   uint64_t* free_ = full + S;
   uint64_t* s_ready = free_ + S;
@@ -176,7 +178,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
     const int h = hb * kMuHeads + warp * 32 + lane;
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(warp * 32) << 16);
     {  // Q row -> tensor memory (bf16 pairs, 16 columns per store), from the copy the gather warps staged
-      // in the (still empty) KV ring as DQK/64 panels of 128 rows x 128 bytes, 128-byte swizzle
+      // in the (still empty) stages 1.. of the KV ring as DQK/64 panels of 128 rows x 128 bytes, 128-byte swizzle
       bool okq = mbar_wait(qs_ready, 0, kBudget, abort_flag);
       if (!okq && lane == 0) give_up(7, 0);
       const int row = warp * 32 + lane;
@@ -186,7 +188,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int ch = 4 * j + u;
-          const uint4 x = *reinterpret_cast<const uint4*>(kst + (ch >> 3) * (kMuHeads * 128) + row * 128 +
+          const uint4 x = *reinterpret_cast<const uint4*>(qst + (ch >> 3) * (kMuHeads * 128) + row * 128 +
                                                           (((ch & 7) ^ (row & 7)) << 4));
           v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
         }
@@ -382,15 +384,29 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
         const int row = gw * (kMuHeads / kMuGatherWarps) + rr;
 #pragma unroll
         for (int ch = lane; ch < kChunks; ch += 32) {
-          cp_async16_zfill(kst + (ch >> 3) * (kMuHeads * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4),
+          cp_async16_zfill(qst + (ch >> 3) * (kMuHeads * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4),
                            q0 + static_cast<int64_t>(row) * DQK * 2 + ch * 16, true);
         }
       }
       cp_async_commit();
+    }
+    // row pointers are looked up one tile ahead, so the page-table read is not on the path
+    const unsigned char* mine = n_my > 0 ? mla_umma_row_ptr<DQK>(p, r, t_begin * kMuTile, k_valid, win_valid, gw, lane)
+                                         : nullptr;
+    int i0 = 0;
+    if (n_my > 0) {  // tile 0 goes into stage 0 behind the query copies: its latency hides under the query's
+      const uint32_t bits = mla_umma_gather_rows<DQK>(p, mine, kst, gw, lane);
+      if (n_my > 1) mine = mla_umma_row_ptr<DQK>(p, r, (t_begin + 1) * kMuTile, k_valid, win_valid, gw, lane);
+      if (lane == 0) validb[gw] = static_cast<unsigned char>(bits);
+      i0 = 1;
+      cp_async_wait<1>();   // the query rows (the older group) have landed
+    } else {
       cp_async_wait<0>();
+    }
+    {
       __syncwarp();
       mbar_arrive_if(qs_ready, lane == 0);
-      // the ring is free for KV tiles once the softmax warps have moved the rows into tensor memory
+      // stages 1.. are free for KV tiles once the softmax warps have moved the rows into tensor memory
       if (!mbar_wait(q_ready, 0, kBudget, abort_flag)) {
         if (lane == 0) give_up(8, 0);
         ok = false;
@@ -407,10 +423,7 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       for (int t = done; t < upto; ++t) mbar_arrive_if(&full[t % S], lane == 0);
       done = upto;
     };
-    // row pointers are looked up one tile ahead, so the page-table read is not on the path
-    const unsigned char* mine = n_my > 0 ? mla_umma_row_ptr<DQK>(p, r, t_begin * kMuTile, k_valid, win_valid, gw, lane)
-                                         : nullptr;
-    for (int i = 0; i < n_my && ok; ++i) {
+    for (int i = i0; i < n_my && ok; ++i) {
       const int st = i % S;
       if (i >= S) {
         const uint32_t par = ((i / S) - 1) & 1;
