@@ -359,7 +359,7 @@ int mdc_test_pingpong_launch(const mdc_pingpong_params* p, void* stream);
  * of the reference).  Rank r holds tokens t with t % cp == r at local index
  * t / cp.  All buffers are per rank; the arena regions are per phase.
  *   cand region : (B, cp, cand_slice) with cand_slice = top_k*8 + 16 bytes:
- *                 [top_k f32 logits][top_k i32 global ids][i32 count, pad]
+ *                 [i32 count, pad to 16 bytes][top_k f32 logits][top_k i32 global ids]
  *   inbox region: (B_owned, cp, H*512*2 + H*4) bytes, owner(b) = b % cp,
  *                 owned index b / cp: [H x 512 bf16 partial O][H f32 log2-LSE]  */
 #define MDC_THR_BINS 4096  /* bins of the row histogram: the upper 12 bits of the order-preserving u32 image of a score */
@@ -436,7 +436,9 @@ typedef struct {
    * through a histogram exchange and a short list of undecided keys, write the selection and the gather
    * lists themselves and mark their candidate counts -1; the merge task of the row (MERGE_L1 with one
    * rank, MERGE_L2 with several and cand_direct = 1, which it requires there) then only passes the result
-   * on.  Heavily tied rows fall back to the merge.  thr_off: byte offset inside one arena phase of
+   * on.  Heavily tied rows fall back to the merge.  thr_exact = 2 (several ranks, cand_direct = 0): the chunk
+   * tasks of a rank settle the RANK's exact top-k the same way, without any exchange between ranks, and store
+   * it as the rank's candidate list on every rank; MERGE_L1 then only passes on, MERGE_L2 merges cp lists.  thr_off: byte offset inside one arena phase of
    * (B, cp * 4 * MDC_THR_BINS + cp * n_chunks * 2064) bytes of exchange space (histograms per rank, then one slot per
    * rank and chunk); thr_ev_base: first of 2 * B extra event cells (beyond the queue's events) of the
    * event buffer: cell thr_ev_base + b counts histogram arrivals, thr_ev_base + B + b slot arrivals. */

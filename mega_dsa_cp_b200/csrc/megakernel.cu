@@ -42,7 +42,11 @@ struct MegaShared {
 __device__ inline int64_t phase_offset(const mdc_mega_params& p, unsigned long long phase) {
   return static_cast<int64_t>(phase % static_cast<unsigned long long>(max(p.layer.phases, 1))) * p.layer.phase_bytes;
 }
+// One candidate slice of the arena: [count cell, 16 bytes][top_k f32 logits][top_k i32 ids].  The cell comes first so
+// that a list of n entries leaves as ONE bulk copy of the slice's head (cell, all logits, the first n ids).
 __device__ inline int cand_slice_bytes(const mdc_layer_params& L) { return L.top_k * 8 + 16; }
+constexpr int kSliceV = 16;
+__device__ __host__ inline int64_t slice_i_off(int K) { return 16 + static_cast<int64_t>(K) * 4; }
 __device__ inline int inbox_slice_bytes(const mdc_layer_params& L) { return L.H * kMlaDv * 2 + L.H * 4; }
 // Lists each rank contributes to a row's candidate region.
 __device__ __host__ inline int cand_lists_per_rank(const mdc_layer_params& L) { return L.cand_direct && L.cp > 1 ? L.n_chunks : 1; }
@@ -244,15 +248,18 @@ __device__ __noinline__ void op_logits(const mdc_mega_params& p, int b, int chun
       x.ev = EventSet{static_cast<unsigned char*>(p.events.base), p.events.offsets, p.events.my_rank, p.events.world};
       x.ev_hist = L.thr_ev_base + b;
       x.ev_keys = L.thr_ev_base + L.B + b;
-      x.hist_target = static_cast<unsigned long long>(L.cp) * (phase + 1ull);
-      x.keys_target = static_cast<unsigned long long>(L.cp) * C * (phase + 1ull);
+      const bool local_only = L.thr_exact == 2 && L.cp > 1;   // each rank settles its own list
+      x.pcp = local_only ? 1 : L.cp;
+      x.prank = local_only ? 0 : L.rank;
+      x.hist_target = static_cast<unsigned long long>(x.pcp) * (phase + 1ull);
+      x.keys_target = static_cast<unsigned long long>(x.pcp) * C * (phase + 1ull);
       x.arena = static_cast<unsigned char*>(p.arena.base);
       x.arena_offsets = p.arena.offsets;
       const int64_t row_bytes = static_cast<int64_t>(L.cp) * (kRowHistBytes + static_cast<int64_t>(C) * kRowSlotBytes);
       x.hist_off = phase_offset(p, phase) + L.thr_off + b * row_bytes;
       x.slot_off = x.hist_off + static_cast<int64_t>(L.cp) * kRowHistBytes;
       x.slice_bytes = cand_slice_bytes(L);
-      x.out_off = phase_offset(p, phase) + L.cand_off + static_cast<int64_t>(b) * L.cp * C * x.slice_bytes;
+      x.out_off = phase_offset(p, phase) + L.cand_off + static_cast<int64_t>(b) * L.cp * cand_lists_per_rank(L) * x.slice_bytes;
       x.cp = L.cp;
       x.rank = L.rank;
       x.out_v = L.sel_v + static_cast<int64_t>(b) * K;
@@ -282,11 +289,12 @@ __device__ __noinline__ void op_logits(const mdc_mega_params& p, int b, int chun
     int n = lp.cand_c[row];
     if (n < 0) return;   // (uniform over the block) the row was published by the tasks themselves, cells included
     n = min(n, K);
-    const int n4 = (n + 3) & ~3;   // K is even and the slice 16-byte aligned: the rounded part stays inside it
+    const int n4 = (n + 3) & ~3;   // K is a multiple of 4 here: the rounded part stays inside the slice
+    // staged with the slice's own layout, so that one bulk copy per rank carries cell, logits and ids
     unsigned char* stage = smem + logits_smem_layout<FMT, PAGE>(1, lp.blocks_per_chunk * PAGE, true).ring;
-    uint32_t* sv = reinterpret_cast<uint32_t*>(stage);
-    uint32_t* si = sv + n4;
-    int32_t* sc = reinterpret_cast<int32_t*>(si + n4);
+    int32_t* sc = reinterpret_cast<int32_t*>(stage);
+    uint32_t* sv = reinterpret_cast<uint32_t*>(stage + kSliceV);
+    uint32_t* si = reinterpret_cast<uint32_t*>(stage + slice_i_off(K));
     const uint32_t* gv = reinterpret_cast<const uint32_t*>(lp.cand_v + row * K);
     const uint32_t* gi = reinterpret_cast<const uint32_t*>(lp.cand_i + row * K);
     for (int i = threadIdx.x; i < n4; i += kBlockThreads) {
@@ -300,11 +308,7 @@ __device__ __noinline__ void op_logits(const mdc_mega_params& p, int b, int chun
       const int64_t off = phase_offset(p, phase) + L.cand_off +
                           ((static_cast<int64_t>(b) * L.cp + L.rank) * C + chunk) * cand_slice_bytes(L);
       unsigned char* dst = arena.peer_ptr(off, threadIdx.x);
-      if (n4 > 0) {
-        bulk_s2g(dst, sv, n4 * 4);
-        bulk_s2g(dst + K * 4, si, n4 * 4);
-      }
-      bulk_s2g(dst + K * 8, sc, 16);
+      bulk_s2g(dst, stage, n4 > 0 ? static_cast<uint32_t>(slice_i_off(K) + n4 * 4) : 16u);
       bulk_commit();
       bulk_wait_all();
       fence_proxy_async_global();
@@ -347,7 +351,7 @@ __device__ __noinline__ void op_merge_l1(const mdc_mega_params& p, int b, unsign
   ls.c = (two_level ? L.mid_c : L.logits.cand_c) + static_cast<int64_t>(b) * C;
   ls.stride = K;
   ls.c_stride = 1;
-  if (L.thr_exact && L.cp == 1 && !two_level) {
+  if (L.thr_exact && !two_level && (L.cp == 1 || L.thr_exact == 2)) {
     // the LOGITS tasks of the row published the selection and the gather list themselves: nothing to do
     int pub = 0;
     if (threadIdx.x < 32) {
@@ -363,15 +367,15 @@ __device__ __noinline__ void op_merge_l1(const mdc_mega_params& p, int b, unsign
   }
   const int64_t off = phase_offset(p, phase) + L.cand_off + (static_cast<int64_t>(b) * L.cp + L.rank) * cand_slice_bytes(L);
   unsigned char* slice = arena.local_ptr(off);
-  merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice), reinterpret_cast<int32_t*>(slice + K * 4),
-                          reinterpret_cast<int32_t*>(slice + K * 8), nullptr, sm, smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
+  merge_lists_auto<false>(ls, C, K, K, reinterpret_cast<float*>(slice + kSliceV), reinterpret_cast<int32_t*>(slice + slice_i_off(K)),
+                          reinterpret_cast<int32_t*>(slice), nullptr, sm, smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
   if (L.cp == 1) {
     // one rank: this list IS the selection; publish it and the gather list here (no MERGE_L2 task)
     __threadfence();
     sync_workers();
-    const int n = *reinterpret_cast<const int32_t*>(slice + K * 8);
-    const float* sv = reinterpret_cast<const float*>(slice);
-    const int32_t* si = reinterpret_cast<const int32_t*>(slice + K * 4);
+    const int n = *reinterpret_cast<const int32_t*>(slice);
+    const float* sv = reinterpret_cast<const float*>(slice + kSliceV);
+    const int32_t* si = reinterpret_cast<const int32_t*>(slice + slice_i_off(K));
     for (int i = threadIdx.x; i < n; i += kBlockThreads) {
       L.sel_v[static_cast<int64_t>(b) * K + i] = sv[i];
       L.sel_i[static_cast<int64_t>(b) * K + i] = si[i];
@@ -413,20 +417,20 @@ __device__ __noinline__ void op_merge_l2(const mdc_mega_params& p, int b, unsign
                       static_cast<int64_t>(b) * L.cp * cand_lists_per_rank(L) * cand_slice_bytes(L);
   const unsigned char* first = static_cast<const unsigned char*>(p.arena.base) + off;
   MergeLists ls;
-  ls.v = reinterpret_cast<const float*>(first);
-  ls.i = reinterpret_cast<const int32_t*>(first + K * 4);
-  ls.c = reinterpret_cast<const int32_t*>(first + K * 8);
+  ls.v = reinterpret_cast<const float*>(first + kSliceV);
+  ls.i = reinterpret_cast<const int32_t*>(first + slice_i_off(K));
+  ls.c = reinterpret_cast<const int32_t*>(first);
   ls.stride = cand_slice_bytes(L) / 4;
   ls.c_stride = cand_slice_bytes(L) / 4;
   int32_t* sel_i = L.sel_i + static_cast<int64_t>(b) * K;
-  if (L.thr_exact && L.cand_direct) {
+  if (L.thr_exact == 1 && L.cand_direct) {
     // published by the LOGITS tasks of all ranks (every slice's cell holds {-1, length}): the selection lies
     // in slice 0 of the row; the gather list and its length are already in place
     const int J = L.cp * L.n_chunks;
     if (threadIdx.x < 32) {
       int all = 1;
       for (int j = threadIdx.x; j < J; j += 32)
-        all &= __float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + static_cast<int64_t>(j) * cand_slice_bytes(L) + K * 8))) < 0;
+        all &= __float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + static_cast<int64_t>(j) * cand_slice_bytes(L)))) < 0;
       const int pub = __all_sync(0xffffffffu, all);
       if (threadIdx.x == 0) sm.sel.bnd = pub;
     }
@@ -434,12 +438,12 @@ __device__ __noinline__ void op_merge_l2(const mdc_mega_params& p, int b, unsign
     const int pub = sm.sel.bnd;
     sync_workers();
     if (pub) {
-      const int n = min(max(__float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + K * 8 + 4))), 0), K);
+      const int n = min(max(__float_as_int(ld_sys_f32(reinterpret_cast<const float*>(first + 4))), 0), K);
       const int n4 = (n + 3) >> 2;
       float* ov = L.sel_v + static_cast<int64_t>(b) * K;
       for (int i = threadIdx.x; i < n4; i += kBlockThreads) {
-        const uint4 v = ld_sys_u4(reinterpret_cast<const uint4*>(first) + i);
-        const uint4 d = ld_sys_u4(reinterpret_cast<const uint4*>(first + K * 4) + i);
+        const uint4 v = ld_sys_u4(reinterpret_cast<const uint4*>(first + kSliceV) + i);
+        const uint4 d = ld_sys_u4(reinterpret_cast<const uint4*>(first + slice_i_off(K)) + i);
         reinterpret_cast<uint4*>(ov)[i] = v;
         reinterpret_cast<uint4*>(sel_i)[i] = d;
       }
@@ -770,9 +774,12 @@ static int layer_check(const mdc_mega_params& p) {
   if (L.l1_groups > 1 && (!L.mid_v || !L.mid_i || !L.mid_c)) return MDC_ERR_NULL;
   if (L.l1_groups < 0 || L.l1_groups > L.n_chunks) return MDC_ERR_BAD_SHAPE;
   if (L.cand_direct && L.cp > 1 && (L.l1_groups > 1 || L.cp * L.n_chunks > 256)) return MDC_ERR_BAD_SHAPE;  // the merge takes 256 lists
+  if (L.cand_direct && L.cp > 1 && L.top_k % 4 != 0) return MDC_ERR_BAD_ALIGN;   // the ids start on a 16-byte boundary of the slice
   if (L.thr_exact) {
     if (!L.thr_hist || !L.thr_done || L.thr_ev_base < p.n_events || (L.thr_off & 15)) return MDC_ERR_BAD_SHAPE;
-    if (L.cp * L.n_chunks > kRowMaxSlots || L.l1_groups > 1 || (L.cp > 1 && !L.cand_direct)) return MDC_ERR_BAD_SHAPE;
+    if (L.thr_exact != 1 && L.thr_exact != 2) return MDC_ERR_BAD_SHAPE;
+    if (L.cp * L.n_chunks > kRowMaxSlots || L.l1_groups > 1) return MDC_ERR_BAD_SHAPE;
+    if (L.cp > 1 && (L.thr_exact == 1) != (L.cand_direct != 0)) return MDC_ERR_BAD_SHAPE;   // 1: with the chunk lists' layout, 2: one list per rank
     if (L.top_k % 4 != 0) return MDC_ERR_BAD_ALIGN;   // the published selection is copied in 16-byte pieces
   }
   if (static_cast<long long>(L.cp) * (L.attn_splits > 1 ? L.attn_splits : 1) > kLseMaxSlices) return MDC_ERR_TOO_LARGE;

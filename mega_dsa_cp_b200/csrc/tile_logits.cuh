@@ -255,8 +255,11 @@ struct RowExact {
   int64_t hist_off;                            // this step, this row: [cp][bins] u32 (unused with one rank)
   int64_t slot_off;                            // this step, this row: [cp * n_chunks] slots
   int64_t out_off;                             // several ranks: the row's candidate slices (slice 0 receives the
-  int64_t slice_bytes;                         //   selection: [K f32][K i32]; every slice's cell: {-1, total})
-  int cp, rank;
+  int64_t slice_bytes;                         //   selection behind its 16-byte cell: [K f32][K i32]; every slice's cell: {-1, total})
+  int cp, rank;                                // the ranks of the context-parallel group, and this one
+  int pcp, prank;                              // the ranks that settle the row together: (cp, rank), or (1, 0): this rank's
+                                               //   tasks settle the rank's own top-k and store it as the rank's candidate
+                                               //   list (slice `rank` of the row, a plain count in its cell) on every rank
   float* out_v;                                // one rank: the row of the selection lists, written directly
   int32_t* out_i;
   int32_t* sel_c;
@@ -323,7 +326,8 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
   const RowExact& x = *rt.x;
   RowExactSmem& xs = rs.xs;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int J = x.cp * n_chunks, me = x.rank * n_chunks + chunk;
+  const int J = x.pcp * n_chunks, me = x.prank * n_chunks + chunk;
+  const bool local_only = x.pcp == 1;   // (slots, cells and counters on this rank only)
   const uint32_t floor_tau = bin ? (bin << kThrShift) - 1u : 0u;   // keys > floor_tau: the bins >= bin
   // ---- the chunk's survivors, compacted in position order: every later step works on this short list
   const bool fits = n_pass <= kSurvCap;
@@ -372,18 +376,18 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
   {
     const int n_keys = over ? 0 : n_und;
     const int64_t at = x.slot_off + static_cast<int64_t>(me) * kRowSlotBytes;
-    for (int d = 0; d < x.cp; ++d) {
-      unsigned char* dst = x.arena + x.arena_offsets[d] + at;
+    for (int d = 0; d < x.pcp; ++d) {
+      unsigned char* dst = x.arena + x.arena_offsets[local_only ? x.rank : d] + at;
       if (tid == 0) *reinterpret_cast<int4*>(dst) = make_int4(n_above, n_keys, over ? 1 : 0, 0);
       for (int i = tid; i < n_keys; i += kBlockThreads) reinterpret_cast<uint32_t*>(dst + 16)[i] = rs.mylist[i];
     }
-    if (x.cp > 1) __threadfence_system();
+    if (!local_only) __threadfence_system();
     else __threadfence();
     sync_workers();
     if (tid == 0) {
-      for (int d = 0; d < x.cp; ++d) x.ev.notify_1t(x.ev_keys, d);
+      for (int d = 0; d < x.pcp; ++d) x.ev.notify_1t(x.ev_keys, local_only ? x.rank : d);
       unsigned long long seen = 0;
-      const bool ok = x.ev.poll_1t(x.ev_keys, x.keys_target, x.cp > 1, rt.budget_ns, &seen, 64);
+      const bool ok = x.ev.poll_1t(x.ev_keys, x.keys_target, !local_only, rt.budget_ns, &seen, 64);
       if (!ok) report_failure(status, MDC_DEV_WAIT_TIMEOUT, -1000 - b, chunk, seen, x.keys_target);
       xs.ok = ok ? 1 : 0;
       xs.overflow = 0;
@@ -465,8 +469,10 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
   if (warp == 0) warp_prefix256(xs.take, xs.to, J, lane);
   sync_workers();
   const int my_eq = min(xs.e[me], max(0, need_eq - xs.eo[me]));
-  const int off_g = xs.to[me], off_l = xs.to[me] - xs.to[x.rank * n_chunks];
-  const int total = xs.to[J], local_total = xs.to[(x.rank + 1) * n_chunks] - xs.to[x.rank * n_chunks];
+  const int off_g = xs.to[me], off_l = xs.to[me] - xs.to[x.prank * n_chunks];
+  const int total = xs.to[J], local_total = xs.to[(x.prank + 1) * n_chunks] - xs.to[x.prank * n_chunks];
+  const bool as_list = local_only && x.cp > 1;   // the result is this rank's candidate list, not the selection
+  const int64_t out_at = x.out_off + (as_list ? static_cast<int64_t>(x.rank) * x.slice_bytes : 0);
   // ---- this chunk's share, from its survivor list (position order)
   Threshold<uint32_t> th;
   th.tau = tau;
@@ -478,7 +484,7 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
     const int pos = rs.spos[idx];
     const float v = __uint_as_float((kv & 0x80000000u) ? (kv ^ 0x80000000u) : ~kv);
     const int id = (base_pos + pos) * id_mul + id_add;
-    if (off_l + slot < x.pt_cols) x.pt[off_l + slot] = x.row_base + base_pos + pos;
+    if (!as_list && off_l + slot < x.pt_cols) x.pt[off_l + slot] = x.row_base + base_pos + pos;
     const int o = off_g + slot;
     if (o < K) {
       if (x.cp == 1) {
@@ -486,22 +492,26 @@ static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& 
         x.out_i[o] = id;
       } else {
         for (int d = 0; d < x.cp; ++d) {
-          unsigned char* dst = x.arena + x.arena_offsets[d] + x.out_off;
-          reinterpret_cast<float*>(dst)[o] = v;
-          reinterpret_cast<int32_t*>(dst + static_cast<int64_t>(K) * 4)[o] = id;
+          unsigned char* dst = x.arena + x.arena_offsets[d] + out_at;   // slice: [cell 16 B][K f32][K i32]
+          reinterpret_cast<float*>(dst + 16)[o] = v;
+          reinterpret_cast<int32_t*>(dst + 16 + static_cast<int64_t>(K) * 4)[o] = id;
         }
       }
     }
   });
   if (tid == 0) {
-    if (chunk == 0) {
+    if (chunk == 0 && !as_list) {
       *x.k_valid = x.win_slots + min(local_total, x.pt_cols);
       if (x.cp == 1) *x.sel_c = min(total, K);
     }
-    if (x.cp > 1) {  // this task's slice on every rank: "published", and the length of the selection
+    if (as_list) {   // the rank's list on every rank: its length, by the row's first task
+      if (chunk == 0)
+        for (int d = 0; d < x.cp; ++d)
+          *reinterpret_cast<int4*>(x.arena + x.arena_offsets[d] + out_at) = make_int4(min(total, K), 0, 0, 0);
+    } else if (x.cp > 1) {  // this task's slice on every rank: "published", and the length of the selection
       for (int d = 0; d < x.cp; ++d)
-        *reinterpret_cast<int4*>(x.arena + x.arena_offsets[d] + x.out_off + static_cast<int64_t>(me) * x.slice_bytes +
-                                 static_cast<int64_t>(K) * 8) = make_int4(-1, min(total, K), 0, 0);
+        *reinterpret_cast<int4*>(x.arena + x.arena_offsets[d] + x.out_off + static_cast<int64_t>(me) * x.slice_bytes) =
+            make_int4(-1, min(total, K), 0, 0);
     }
   }
   return true;
@@ -537,7 +547,7 @@ __device__ inline int chunk_emit_above_row_threshold(const RowThreshold& rt, int
   __threadfence();
   sync_workers();
   const RowExact* x = rt.x;
-  const bool many = x != nullptr && x->cp > 1;   // the row spans several ranks: the histograms are exchanged
+  const bool many = x != nullptr && x->pcp > 1;   // the ranks settle the row together: the histograms are exchanged
   if (tid == 0) {
     const uint32_t before = atomicAdd(&rt.done[b], 1u);
     sel.hist_bnd = (before + 1u == rt.target) ? 1 : 0;   // the last task of this rank's row to count in

@@ -190,7 +190,7 @@ class DsaDecodeLayer:
                  kv_seq_stride: int | None = None, n_ctas: int | None = None, group_name: str = "0",
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
-                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact: bool | None = None,
+                 row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact=None,
                  q_tasks: bool | None = None):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
@@ -232,13 +232,19 @@ class DsaDecodeLayer:
         self.l1_groups = 1 if row_threshold else l1_groups_for(self.n_chunks)
         # several ranks, one merge level: the chunk lists go straight to every rank (no exact local top-k
         # in between: the global top-k lies inside the union of what the chunks emit)
-        self.cand_direct = cand_direct and row_threshold and cp > 1 and self.l1_groups == 1 and cp * self.n_chunks <= 256
+        # row_exact = "local" (several ranks): each rank's chunk tasks settle the rank's own exact top-k and
+        # store it as the rank's candidate list on every rank (one list per rank, MERGE_L1 only passes on)
+        local_exact = row_exact == "local" and cp > 1 and row_threshold and self.l1_groups == 1 and top_k % 4 == 0 \
+            and self.n_chunks <= 256
+        self.cand_direct = (cand_direct and not local_exact and row_threshold and cp > 1 and self.l1_groups == 1
+                            and cp * self.n_chunks <= 256 and top_k % 4 == 0)
         # row_exact: the chunk tasks of a row (on all ranks) settle the exact top-k themselves; the merge
         # task behind them stays in the graph and only acts on rows that fell back (heavy ties)
         if row_exact is None:
             row_exact = cp == 1
-        self.row_exact = (row_exact and row_threshold and cp * self.n_chunks <= 256 and top_k % 4 == 0
-                          and (cp == 1 or self.cand_direct))
+        self.row_exact = 2 if local_exact else int(bool(row_exact and row_exact != "local" and row_threshold
+                                                        and cp * self.n_chunks <= 256 and top_k % 4 == 0
+                                                        and (cp == 1 or self.cand_direct)))
         self.compressor = compressor
         if compressor is not None:
             assert (compressor.B, compressor.cp, compressor.rank) == (B, cp, rank)
@@ -346,7 +352,7 @@ class DsaDecodeLayer:
         L.kv_group = self.kv_group
         L.cand_direct = int(self.cand_direct)
         if self.row_exact:
-            L.thr_exact, L.thr_ev_base, L.thr_off = 1, self.n_dag_events, self.arena.regions["thr"]
+            L.thr_exact, L.thr_ev_base, L.thr_off = self.row_exact, self.n_dag_events, self.arena.regions["thr"]
         L.attn_splits = self.attn_splits
         L.l1_groups = self.l1_groups
         L.mid_v, L.mid_i, L.mid_c = N.ptr(self.mid_v), N.ptr(self.mid_i), N.ptr(self.mid_c)

@@ -89,12 +89,26 @@ def main():
         torch.cuda.synchronize()
         xlayer.check_status()
         dist.barrier()
-    ok &= bool(torch.equal(xlayer.sel_c, layer.sel_c))
-    for b in range(B):
-        n = int(layer.sel_c[b])
-        ok &= bool(torch.equal(xlayer.sel_i[b, :n], layer.sel_i[b, :n]))
-        if b % world == rank:
-            ok &= float((xlayer.out[b // world] - layer.out[b // world]).abs().max()) < 1e-3
+    # ... and each rank settling its own exact list (no exchange between ranks before the cross-rank merge)
+    llayer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
+                            kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
+                            group_name=dist.group.WORLD.group_name, device=dev, row_exact="local")
+    assert llayer.row_exact == 2 and not llayer.cand_direct
+    llayer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx), d(w_idx), d(q_mla), d(kv_loc)))
+    dist.barrier()
+    for _ in range(3):
+        llayer.step(wait_budget_ns=5_000_000_000)
+        torch.cuda.synchronize()
+        llayer.check_status()
+        dist.barrier()
+    for other in (xlayer, llayer):
+        ok &= bool(torch.equal(other.sel_c, layer.sel_c))
+        for b in range(B):
+            n = int(layer.sel_c[b])
+            ok &= bool(torch.equal(torch.sort(other.sel_i[b, :n]).values, torch.sort(layer.sel_i[b, :n]).values))
+            if b % world == rank:
+                ok &= float((other.out[b // world] - layer.out[b // world]).abs().max()) < 1e-3
+    ok &= all(bool(torch.equal(xlayer.sel_i[b, :int(layer.sel_c[b])], layer.sel_i[b, :int(layer.sel_c[b])])) for b in range(B))
     # ---- the compressor as tasks of the same persistent kernel, across the real ranks: 13 steps of the
     # ratio-4 window machine (3 closing groups), each entry checked on its owner (n % world)
     from test_gpu_compress import _post_checks
