@@ -625,18 +625,21 @@ __device__ inline int merge_lists_auto(const MergeLists& ls, int L, int maxK, in
       }
     }
     const int used = (compact ? n_cap : n_pos) * 8;
-    if (stage_bytes - used >= 2048 * 4)   // room for a histogram behind the staged row: the histogram search
-      return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; },
-                               reinterpret_cast<uint32_t*>(stage + used));
-    // a long row (several full lists): drop what cannot reach the top k before the exact search
+    // room behind the staged row for a 2048-word histogram: the histogram search instead of one pass per bit
+    uint32_t* hist = stage_bytes - used >= 2048 * 4 ? reinterpret_cast<uint32_t*>(stage + used) : nullptr;
+    // a long row (several full lists): one histogram pass drops what cannot reach the top k, and every later
+    // pass (search, emit) runs over about k survivors instead of the whole row
     const int cap = ((stage_bytes - used - 2048 * 4) / 8) & ~3;
-    if (n_valid >= 2 * top_k && n_pos % 4 == 0 && cap >= top_k + 4) {
-      uint32_t* hist = reinterpret_cast<uint32_t*>(stage + used);
+    // (worth its fixed cost from about four lists' worth: measured 26.8 against 23.7 us at 2.6 x top_k candidates)
+    if (n_valid >= 4 * top_k && n_pos % 4 == 0 && cap >= top_k + 4) {
       uint32_t* vb2 = hist + 2048;
       int32_t* ib2 = reinterpret_cast<int32_t*>(vb2) + cap;
       const int n2 = merge_prefilter(vb, ib, n_pos, top_k, sm, hist, vb2, ib2, cap);
-      if (n2 >= 0) return merge_staged_bits(n2, top_k, out_v, out_i, out_c, dbg, sm, vb2, [&](int pos) { return ib2[pos]; });
+      if (n2 >= 0)
+        return merge_staged_bits(n2, top_k, out_v, out_i, out_c, dbg, sm, vb2, [&](int pos) { return ib2[pos]; }, hist);
     }
+    if (hist)
+      return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; }, hist);
     return merge_staged_bits(n_pos, top_k, out_v, out_i, out_c, dbg, sm, vb, [&](int pos) { return ib[pos]; });
   }
   if (stage && n_pos * 4 <= stage_bytes && maxK >= 1) {

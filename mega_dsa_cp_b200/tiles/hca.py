@@ -35,6 +35,22 @@ def split_workspace(rows: int, n_splits: int, heads: int, device):
             torch.empty(rows, n_splits, heads, dtype=torch.float32, device=device))
 
 
+def dense_layer_tables(n_entries: torch.Tensor, first_page: torch.Tensor, page_cmp: int, cols: int | None = None):
+    """Page table and k_valid of a layer that attends to EVERY compressed entry of a sequence instead of
+    a top-k selection (the ratio-128 layers of DeepSeek-V4: docs/overview.md:50-59 of the reference lists
+    them; its kernels take the same tables).  n_entries (rows,) int32 valid entries per query row,
+    first_page (rows,) int32 first pool page of the row's sequence (its pages are consecutive), page_cmp
+    entries per page.  Returns (pt_cmp (rows, cols) int32 enumerating the pages in order, k_valid (rows,)
+    = 128 window slots + entries).  A sliding-window-only layer needs no table at all: k_valid = 128
+    everywhere (nothing beyond the window), any pt_cmp of one column."""
+    rows = n_entries.numel()
+    pages = torch.div(n_entries + page_cmp - 1, page_cmp, rounding_mode="floor")
+    cols = int(cols or max(1, int(pages.max())))
+    idx = torch.arange(cols, dtype=torch.int32, device=n_entries.device).view(1, cols)
+    pt = torch.where(idx < pages.view(rows, 1), first_page.view(rows, 1).to(torch.int32) + idx, torch.zeros_like(idx))
+    return pt.contiguous(), (128 + n_entries).to(torch.int32)
+
+
 def run_sparse_mla(
     q: torch.Tensor,            # (B, T, H, d_qk) bf16 | float8_e4m3fn
     kv_win: torch.Tensor | None,   # (pages_win, 128, d_qk)

@@ -300,6 +300,34 @@ def test_sparse_mla_bf16_partial_output_and_paged_pool():
     assert (l - rl).abs().max() < 1e-3
 
 
+def test_sparse_mla_dense_layer_and_window_only_layer():
+    """The two layer variants that need no selection, through the same entry point: every compressed
+    entry of the sequence in order (pages enumerated by dense_layer_tables), and the sliding window alone."""
+    from mega_dsa_cp_b200.tiles.hca import dense_layer_tables
+
+    g = torch.Generator().manual_seed(31)
+    B, T, H, DQK, page = 3, 1, 128, 576, 16
+    n_entries = torch.tensor([1024, 517, 16], dtype=torch.int32)           # 128 K / 128 = 1024 entries at most
+    first = torch.tensor([0, 64, 130], dtype=torch.int32)
+    case = mla_case(B, T, H, DQK, 200, [16] * B, with_window=True, seed=32, page_cmp=page)
+    pt, k_valid = dense_layer_tables(n_entries, first, page)
+    assert pt.shape == (B, 64) and pt[1, :33].tolist() == list(range(64, 97)) and int(pt[1, 33]) == 0
+    case["pt_cmp"], case["k_valid"] = pt, k_valid
+    case["win_valid"] = torch.tensor([128, 77, 0], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(DQK)
+    sink = torch.randn(H, generator=g) * 0.5 - 1.0
+    o, l = _mla(case, sink, scale, n_splits=None)
+    ro, rl = mla_oracle(case, sink, scale)
+    assert (o - ro).abs().max() < 2e-2 and (l - rl).abs().max() < 1e-3
+    # window only: nothing beyond the 128 window slots
+    case["k_valid"] = torch.full((B,), 128, dtype=torch.int32)
+    case["pt_cmp"] = torch.zeros(B, 1, dtype=torch.int32)
+    o, l = _mla(case, sink, scale, n_splits=1)
+    ro, rl = mla_oracle(case, sink, scale)
+    assert (o - ro).abs().max() < 2e-2 and (l - rl).abs().max() < 1e-3
+    assert bool(torch.isfinite(l).all())      # the sink keeps the row with an empty window finite
+
+
 @pytest.mark.parametrize("fmt,P,T,K,bpc,S,seq,wex", [
     ("nvfp4", 64, 1, 2048, 128, 32768, 32768, 0),    # BASELINE config 2 row: 4 chunks of 8192
     ("nvfp4", 64, 1, 2048, 64, 32768, 30011, 0),     # 8 chunks, ragged length
