@@ -257,3 +257,24 @@ def test_layer_dag_variants_validate(n_chunks, cp, splits):
     reg = arena_regions(B, cp, 2048, heads, splits)
     assert reg["inbox"] == -(-B // cp) * cp * splits * (heads * 512 * 2 + heads * 4)
     assert arena_regions(B, cp, 2048, heads, splits, cand_lists=n_chunks)["cand"] == n_chunks * reg["cand"]
+
+
+def test_prefill_causal_lengths_and_dense_tables():
+    """Host arithmetic of the chunked prefill (token t lives on rank t % cp at local index t // cp) and of the
+    dense-layer page tables."""
+    import torch
+
+    from mega_dsa_cp_b200.prefill import causal_local_lens
+    from mega_dsa_cp_b200.tiles.hca import dense_layer_tables
+
+    pos = torch.tensor([0, 1, 5, 7, 8, 4095])
+    for cp in (1, 2, 4, 8):
+        total = torch.zeros_like(pos)
+        for r in range(cp):
+            n = causal_local_lens(pos, cp, r)
+            want = torch.tensor([len([t for t in range(int(p) + 1) if t % cp == r]) for p in pos])
+            assert n.tolist() == want.tolist(), (cp, r)
+            total += n
+        assert total.tolist() == (pos + 1).tolist()      # every visible token is on exactly one rank
+    pt, kv = dense_layer_tables(torch.tensor([33, 16, 0], dtype=torch.int32), torch.tensor([10, 0, 7], dtype=torch.int32), 16)
+    assert pt.tolist() == [[10, 11, 12], [0, 0, 0], [0, 0, 0]] and kv.tolist() == [161, 144, 128]
