@@ -499,14 +499,17 @@ def run_layer(args):
             "data": "synthetic",
             "config": {"workload": f"full DSA decode layer-step, CP={world}: B={B}, ctx 131072 sharded token-interleaved "
                                    f"({c['S'] // world} tokens/rank/seq), indexer + top-k 2048 + sparse MLA (128 heads, "
-                                   "512+64) + LSE merge, one persistent kernel per rank, P2P stores into symmetric memory (query blocks, candidates, partials)",
+                                   "512+64) + LSE merge, one persistent kernel per rank" +
+                                   (", P2P stores into symmetric memory (query blocks, candidates, partials)" if world > 1 else ""),
                        "l2": f"rotating {c['copies']} cache copies per rank (index cache + KV pool 1.3 GB each > 126 MB L2)",
                        "parallelism": f"cp{world}", "attn_splits": layers[0].attn_splits},
             "step_us": ms_step * 1e3,
             "e2e": {"value": B / (e2e_step_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": hblock.numel(),
                     "d2h_bytes_per_step": h_out.numel() * 2, "ms_per_step": e2e_step_ms,
                     "api": "DsaDecodeLayer.step(): each rank sends the query block of the sequences it owns from pinned host "
-                           "memory (the step's QPATH tasks spread it over NVLink) and reads its owned output rows back"},
+                           "memory (" + ("the step's QPATH tasks spread it over NVLink" if world > 1 else
+                                         "one rank: the kernels read the staging block in place") +
+                           ") and reads its owned output rows back"},
             "gpu_launches": args.steps, "kernels_per_step": 1,
             "parity": parity,
             "timeline_rank0": timeline, "lse_merge_latency": lse_lat,
