@@ -451,12 +451,16 @@ __device__ __noinline__ void op_merge_l2(const mdc_mega_params& p, int b, unsign
       return;
     }
   }
-  const int n = merge_lists_auto<SYS>(ls, L.cp * cand_lists_per_rank(L), K, K, L.sel_v + static_cast<int64_t>(b) * K, sel_i, L.sel_c + b, nullptr, sm,
-                                     smem + kMergeHdr, kMegaTileSmem - kMergeHdr);
-  __threadfence();
+  // The selected ids land in shared memory (the tail of the staging area): the gather list is compacted from
+  // there, without a fence and two round trips to the copy in global memory.
+  const int sid_bytes = (K * 4 + 15) & ~15;
+  int32_t* sid = reinterpret_cast<int32_t*>(smem + kMegaTileSmem - sid_bytes);
+  const int n = merge_lists_auto<SYS>(ls, L.cp * cand_lists_per_rank(L), K, K, L.sel_v + static_cast<int64_t>(b) * K, sid, L.sel_c + b, nullptr, sm,
+                                     smem + kMergeHdr, kMegaTileSmem - kMergeHdr - sid_bytes);
   sync_workers();
+  for (int i = threadIdx.x; i < n; i += kBlockThreads) sel_i[i] = sid[i];
   int32_t* pt = const_cast<int32_t*>(L.mla.pt_cmp) + static_cast<int64_t>(b) * L.mla.pt_cols;
-  const int mine = compact_local_ids(sel_i, n, L.cp, L.rank, static_cast<int>(kv_row_base(L, b)), pt, L.mla.pt_cols, sm.sel);
+  const int mine = compact_local_ids(sid, n, L.cp, L.rank, static_cast<int>(kv_row_base(L, b)), pt, L.mla.pt_cols, sm.sel);
   if (threadIdx.x == 0) const_cast<int32_t*>(L.mla.k_valid)[b] = kWinSlots + mine;
 }
 
