@@ -262,7 +262,7 @@ def build_rank(R, c, seed0=1000):
         layer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, heads=H, d_qk=DQK, max_pages=pages,
                                blocks_per_chunk=c["blocks_per_chunk"], kv_seq_stride=S_loc,
                                group_name=R.group_name, device=dev, distribute_q=True, row_exact=c.get("row_exact"),
-                               cand_direct=c.get("cand_direct", True))
+                               cand_direct=c.get("cand_direct", True), dynamic=c.get("dynamic", False))
         layer.bind(LayerInputs(cache, bt, seq_loc, q_idx[rank::world], w_idx[rank::world], q_mla[rank::world], kv))
         layers.append(layer)
         inputs.append((cache, bt, kv))
@@ -406,6 +406,7 @@ def run_layer(args):
     world, rank, dev = R.world, R.rank, R.dev
     c = cp_config(world)
     c["row_exact"] = {"default": None, "local": "local", "global": True, "off": False, "l1": False}[args.row_exact]
+    c["dynamic"] = args.dynamic
     c["cand_direct"] = args.row_exact != "l1"   # l1: every rank merges its chunk lists exactly before the exchange
     B, H, DQK = c["B"], c["H"], c["d_qk"]
     layers, inputs, q = build_rank(R, c)
@@ -785,6 +786,7 @@ def main():
     ap.add_argument("--skip-alone", action="store_true", help="N=1: omit the kernels-alone legs (indexer, MLA)")
     ap.add_argument("--row-exact", default="default", choices=["default", "local", "global", "off", "l1"],
                     help="where the chunk tasks settle the exact selection (default: the layer's choice for N)")
+    ap.add_argument("--dynamic", action="store_true", help="blocks pull tasks from one shared queue (dynamic scheduling)")
     ap.add_argument("--only", default=None, choices=["indexer", "mla", "merge"],
                     help="run only one kernel-alone leg and print its block (profiling runs)")
     args = ap.parse_args()

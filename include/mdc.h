@@ -479,6 +479,16 @@ typedef struct {
    * counts in after reading scalars[0]; the last one stores scalars[0] + 1 for the next launch and
    * clears the counter (scalars must then be writable). */
   unsigned long long* phase_ctl;
+  /* Dynamic scheduling (the reference plans a dynamic scheduler, docs/event-system.md:27,110; its code has
+   * the static queues only).  dyn_task_off != NULL: `queue` holds ONE row (row_words words) with all of this
+   * rank's tasks in dependency order; dyn_task_off[i] is the word offset of task i, dyn_n_tasks their number;
+   * the n_ctas blocks pull the next task with an atomic counter instead of walking a row of their own.  A task's
+   * producers come earlier in the row, so they are always running or done when it is pulled.  dyn_ctl: two
+   * u32 words, zero before the first launch (next task, finished blocks); the last block to finish clears
+   * them, so a launch can be replayed. */
+  const int32_t* dyn_task_off;
+  int32_t dyn_n_tasks;
+  uint32_t* dyn_ctl;
 } mdc_mega_params;
 int mdc_megakernel_launch(const mdc_mega_params* p, void* stream);
 /* The host-side validation of a launch alone (no GPU needed): the return code mdc_megakernel_launch

@@ -107,6 +107,7 @@ class MegaParams(C.Structure):
         ("wait_budget_ns", i64), ("status", p_void), ("log", p_void), ("log_cap", i32),
         ("test_off", i64), ("test_slot_bytes", i32), ("layer", LayerParams),
         ("trace", p_void), ("trace_cap", i32), ("phase_ctl", p_void),
+        ("dyn_task_off", p_void), ("dyn_n_tasks", i32), ("dyn_ctl", p_void),
     ]
 
 

@@ -36,6 +36,7 @@ static_assert(kMergeHdr + 16384 * 8 <= kMegaTileSmem, "a row of 16384 staged can
 struct MegaShared {
   int32_t row[kStagedWords];
   int32_t fail;
+  int32_t next;   // dynamic scheduling: index of the task this block pulled
   unsigned long long phase;
 };
 
@@ -583,8 +584,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
   const int tid = threadIdx.x, warp = tid >> 5;
   const bool worker = warp < kWarps;
 
-  const int32_t* row_g = p.queue + static_cast<int64_t>(blockIdx.x) * p.row_words;
-  const bool staged = p.row_words <= kStagedWords;
+  const bool dyn = p.dyn_task_off != nullptr;   // one shared row, tasks pulled with an atomic counter
+  const int32_t* row_g = p.queue + (dyn ? 0 : static_cast<int64_t>(blockIdx.x) * p.row_words);
+  const bool staged = !dyn && p.row_words <= kStagedWords;
   if (staged) {
     for (int i = tid; i < p.row_words; i += kMegaThreads) sh.row[i] = row_g[i];
   }
@@ -615,7 +617,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
   const EventSet ev{static_cast<unsigned char*>(p.events.base), p.events.offsets, p.events.my_rank, p.events.world};
   const mdc_layer_params& L = p.layer;
 
-  for (TaskInfo t = cur.read(0); t.valid(); t = cur.advance(t)) {
+  TaskInfo t_end;
+  t_end.op = kOpEnd;
+  auto pull = [&]() -> TaskInfo {   // dynamic: the next task of the shared row, or the end marker
+    if (tid == 0) sh.next = static_cast<int32_t>(atomicAdd(p.dyn_ctl, 1u));
+    __syncthreads();
+    const int idx = sh.next;
+    __syncthreads();
+    return idx >= 0 && idx < p.dyn_n_tasks ? cur.read(p.dyn_task_off[idx]) : t_end;
+  };
+  for (TaskInfo t = dyn ? pull() : cur.read(0); t.valid(); t = dyn ? pull() : cur.advance(t)) {
     unsigned long long tr0 = 0, tr1 = 0;
     if (p.trace && tid == 0) tr0 = global_timer_ns();
     // ---- waits: thread 0 polls, the barrier publishes
@@ -736,6 +747,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_kernel(const __grid_cons
     }
     __syncthreads();
   }
+  if (dyn && tid == 0) {   // the last block to finish rewinds the counters for the next launch
+    __threadfence();
+    if (atomicAdd(p.dyn_ctl + 1, 1u) + 1u == gridDim.x) {
+      p.dyn_ctl[0] = 0u;
+      p.dyn_ctl[1] = 0u;
+      __threadfence();
+    }
+  }
 }
 
 }  // namespace mdc
@@ -822,6 +841,7 @@ extern "C" int mdc_megakernel_check(const mdc_mega_params* p) {
   if (!p || !p->queue || !p->scalars || !p->arity || !p->scopes || !p->events.base || !p->events.offsets)
     return MDC_ERR_NULL;
   if (p->n_ctas < 1 || p->row_words < 1 || p->n_events < 0) return MDC_ERR_BAD_SHAPE;
+  if (p->dyn_task_off && (!p->dyn_ctl || p->dyn_n_tasks < 0)) return MDC_ERR_NULL;
   if (p->wait_budget_ns <= 0) return MDC_ERR_BAD_SHAPE;
   return layer_check(*p);
 }

@@ -191,7 +191,7 @@ class DsaDecodeLayer:
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
                  row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact=None,
-                 q_tasks: bool | None = None):
+                 q_tasks: bool | None = None, dynamic: bool = False):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
         distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
@@ -253,7 +253,9 @@ class DsaDecodeLayer:
                                              cand_direct=self.cand_direct)
         self.kvwrite = kvwrite
         self.distribute_q = distribute_q
-        self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=n_ctas, world_size=cp, op_of=ops)
+        # dynamic: one shared queue in dependency order, the blocks pull tasks with an atomic counter
+        self.dynamic = dynamic
+        self.schedule = codegen_schedule(tasks, events, rank=rank, n_ctas=1 if dynamic else n_ctas, world_size=cp, op_of=ops)
         if row_threshold:
             # The LOGITS tasks of a row wait for each other inside the task.  That is free of deadlock as
             # long as, in this rank's dealing order, they come row by row and nothing that depends on a
@@ -268,7 +270,7 @@ class DsaDecodeLayer:
                     assert not seen_consumer and coords[0] not in closed, "LOGITS tasks must be queued first, row by row"
                 elif op in (N.OP_MERGE_L1, N.OP_MERGE_L1A, N.OP_MERGE_L2, N.OP_ATTN, N.OP_LSE_MERGE):
                     seen_consumer = True
-        self.dsched = upload_schedule(self.schedule, self.device)
+        self.dsched = upload_schedule(self.schedule, self.device, dynamic_ctas=n_ctas if dynamic else None)
         self.n_dag_events = len(events)
         self.events = alloc_event_buffer(len(events) + (2 * B if self.row_exact else 0), rank, cp, group_name, self.device)
         from .tiles.compress import stats_bytes

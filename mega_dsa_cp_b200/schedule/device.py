@@ -31,14 +31,34 @@ class DeviceSchedule:
     n_ctas: int
     row_words: int
     n_events: int
+    task_off: torch.Tensor | None = None   # dynamic scheduling: int32 word offset of every task in the one shared row
+    dyn_ctl: torch.Tensor | None = None    # ... and its two counters (next task, finished blocks)
+    n_tasks: int = 0
 
 
-def upload_schedule(schedule: Schedule, device="cuda", n_scalars: int = 8) -> DeviceSchedule:
+def task_offsets(row) -> list[int]:
+    """Word offsets of the task entries of one packed queue row (format of schedule/codegen.py)."""
+    offs, pos = [], 0
+    while (row[pos] & 0xFF) != 0xFF:
+        offs.append(pos)
+        pos += 4 + ((row[pos] >> 8) & 0x3F) + ((row[pos] >> 14) & 0x3F)
+    return offs
+
+
+def upload_schedule(schedule: Schedule, device="cuda", n_scalars: int = 8, dynamic_ctas: int | None = None) -> DeviceSchedule:
+    """dynamic_ctas: the schedule was generated for ONE queue (n_ctas = 1: all tasks of the rank in dependency
+    order); the kernel runs dynamic_ctas blocks that pull tasks from it with an atomic counter."""
     flat, row = pack_queues(schedule)
     n_ctas = len(schedule.queues)
     i32 = lambda x: torch.tensor(x if len(x) else [0], dtype=torch.int32, device=device)
-    return DeviceSchedule(
-        queue=torch.tensor(flat, dtype=torch.int32, device=device).view(n_ctas, row),
+    dyn = {}
+    if dynamic_ctas is not None:
+        assert n_ctas == 1, "dynamic scheduling pulls from one shared queue: generate the schedule with n_ctas = 1"
+        offs = task_offsets(flat[:row])
+        dyn = dict(task_off=i32(offs), dyn_ctl=torch.zeros(2, dtype=torch.int32, device=device), n_tasks=len(offs))
+        n_ctas = dynamic_ctas
+    return DeviceSchedule(**dyn, 
+        queue=torch.tensor(flat, dtype=torch.int32, device=device).view(len(schedule.queues), row),
         arity=i32(schedule.arity), scopes=i32(schedule.scopes),
         scalars=torch.zeros(n_scalars, dtype=torch.int64, device=device),
         phase_ctl=torch.zeros(1, dtype=torch.int64, device=device),
@@ -74,4 +94,6 @@ def launch_megakernel(ds: DeviceSchedule, events: EventBuffer, arena: SymmetricA
     p.trace = N.ptr(trace)
     p.trace_cap = 0 if trace is None else (trace.numel() - 4) // 4
     p.phase_ctl = N.ptr(ds.phase_ctl) if device_phase else None
+    if ds.task_off is not None:
+        p.dyn_task_off, p.dyn_n_tasks, p.dyn_ctl = N.ptr(ds.task_off), ds.n_tasks, N.ptr(ds.dyn_ctl)
     N.call("mdc_megakernel_launch", p, stream)

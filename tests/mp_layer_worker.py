@@ -101,7 +101,19 @@ def main():
         torch.cuda.synchronize()
         llayer.check_status()
         dist.barrier()
-    for other in (xlayer, llayer):
+    # ... and the default exchange with the blocks pulling tasks from one shared queue (dynamic scheduling)
+    dlayer = DsaDecodeLayer(B, cp=world, rank=rank, top_k=K, max_pages=pages, blocks_per_chunk=max(1, pages // 2),
+                            kv_seq_stride=S_loc, out_dtype=torch.float32, n_ctas=64,
+                            group_name=dist.group.WORLD.group_name, device=dev, distribute_q=True, dynamic=True)
+    dlayer.bind(LayerInputs(d(fused), d(bt), d(seq_loc), d(q_idx[rank::world]), d(w_idx[rank::world]),
+                            d(q_mla[rank::world]), d(kv_loc)))
+    dist.barrier()
+    for _ in range(3):
+        dlayer.step(wait_budget_ns=5_000_000_000)
+        torch.cuda.synchronize()
+        dlayer.check_status()
+        dist.barrier()
+    for other in (xlayer, llayer, dlayer):
         ok &= bool(torch.equal(other.sel_c, layer.sel_c))
         for b in range(B):
             n = int(layer.sel_c[b])

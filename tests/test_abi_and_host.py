@@ -278,3 +278,18 @@ def test_prefill_causal_lengths_and_dense_tables():
         assert total.tolist() == (pos + 1).tolist()      # every visible token is on exactly one rank
     pt, kv = dense_layer_tables(torch.tensor([33, 16, 0], dtype=torch.int32), torch.tensor([10, 0, 7], dtype=torch.int32), 16)
     assert pt.tolist() == [[10, 11, 12], [0, 0, 0], [0, 0, 0]] and kv.tolist() == [161, 144, 128]
+
+
+def test_task_offsets_of_a_packed_row():
+    """The dynamic scheduler's task index: offsets of the entries of a one-queue schedule, in dependency order."""
+    from mega_dsa_cp_b200.layer import build_layer_dag
+    from mega_dsa_cp_b200.schedule.codegen import codegen_schedule, pack_queues
+    from mega_dsa_cp_b200.schedule.device import task_offsets
+
+    tasks, events, ops = build_layer_dag(3, 4, 2, 128, 2, 1, qpath=True, cand_direct=True)
+    s = codegen_schedule(tasks, events, rank=1, n_ctas=1, world_size=2, op_of=ops)
+    flat, row = pack_queues(s)
+    offs = task_offsets(flat[:row])
+    assert len(offs) == len(s.topo) == sum(1 for t in tasks if t.rank == 1)
+    assert offs[0] == 0 and all(b - a >= 4 for a, b in zip(offs, offs[1:]))
+    assert [flat[o] & 0xFF for o in offs] == [s.op_of[i] for i in s.topo]

@@ -67,6 +67,32 @@ def test_random_dag_runs_in_dependency_order_over_two_phases():
     assert torch.equal(cells[:len(events)], 2 * arity)   # counters only ever grow
 
 
+def test_random_dag_with_dynamic_task_pulling():
+    """The same random DAG as one shared queue in dependency order: 32 blocks pull the next task with an
+    atomic counter; three launches (the counters rewind themselves), the order stays a valid linearisation."""
+    from mega_dsa_cp_b200 import _native as N
+    from mega_dsa_cp_b200.events.symm import alloc_event_buffer
+    from mega_dsa_cp_b200.schedule.device import launch_megakernel, upload_schedule
+
+    tasks, events, preds = _random_dag(5, 512, 0.01)
+    sched = codegen_schedule(tasks, events, rank=0, n_ctas=1, op_of={t.name: N.OP_LOG for t in tasks})
+    ds = upload_schedule(sched, DEV, dynamic_ctas=32)
+    assert ds.n_tasks == 512 and ds.n_ctas == 32
+    ev = alloc_event_buffer(max(len(events), 1), device=DEV)
+    status = torch.zeros(8, dtype=torch.int32, device=DEV)
+    for phase in range(3):
+        log = torch.zeros(1024, dtype=torch.int32, device=DEV)
+        ds.scalars[0] = phase
+        launch_megakernel(ds, ev, None, status, log=log)
+        torch.cuda.synchronize()
+        assert status[0].item() == 0, status.tolist()
+        order = log[1:1 + log[0].item()].tolist()
+        assert sorted(order) == list(range(512))
+        at = {t: i for i, t in enumerate(order)}
+        assert all(at[p] < at[t] for t, ps in preds.items() for p in ps)
+        assert ds.dyn_ctl.tolist() == [0, 0]
+
+
 def test_wait_gives_up_within_its_budget_and_reports():
     """A wait whose event nobody notifies must end after the budget with a
     status record (code, event, seen, wanted) and leave the context usable."""
@@ -116,9 +142,10 @@ def test_bulk_push_and_verify_world1():
     assert arena.tensor.view(torch.int32).abs().sum().item() != 0
 
 
-@pytest.mark.parametrize("B,S,K,bpc,qpath,exact", [(2, 4096, 512, 16, False, True), (3, 8192, 2048, 32, False, True),
-                                                   (3, 8192, 2048, 32, True, True), (3, 8192, 2048, 32, False, False)])
-def test_decode_layer_cp1_matches_oracle(B, S, K, bpc, qpath, exact):
+@pytest.mark.parametrize("B,S,K,bpc,qpath,exact,dynamic", [
+    (2, 4096, 512, 16, False, True, False), (3, 8192, 2048, 32, False, True, False), (3, 8192, 2048, 32, True, True, False),
+    (3, 8192, 2048, 32, False, False, False), (3, 8192, 2048, 32, True, True, True)])
+def test_decode_layer_cp1_matches_oracle(B, S, K, bpc, qpath, exact, dynamic):
     from dsa_inputs import indexer_case
     from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
     from oracle import dsa_oracle as orc
@@ -131,6 +158,7 @@ def test_decode_layer_cp1_matches_oracle(B, S, K, bpc, qpath, exact):
     seq = torch.tensor([S - 100 * b for b in range(B)], dtype=torch.int32)
     layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
                            out_dtype=torch.float32, n_ctas=64, distribute_q=qpath, q_tasks=qpath,   # qpath: q through the QPATH task
+                           dynamic=dynamic,   # dynamic: the blocks pull tasks from one shared queue
                            row_exact=exact)   # exact: the chunk tasks settle the row's top-k, the merge only passes it on
     d = lambda t: t.to(DEV)
     layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), d(case["q"]), d(case["w"]), d(q_mla), d(kv)))
