@@ -49,42 +49,51 @@ class DsaPrefillChunk:
                                     device=device, out_dtype=out_dtype, **layer_kw)
         dev = self.layer.device
         self.block_table = torch.zeros(tile, max_pages, dtype=torch.int32, device=dev)
-        self.seq_lens = torch.zeros(tile, dtype=torch.int32, device=dev)
-        # the layer's launch parameters hold addresses: the tile's query tensors are fixed buffers
-        self.q_idx = torch.zeros(tile, 64, 128, dtype=torch.bfloat16, device=dev)
-        self.w_idx = torch.zeros(tile, 64, device=dev)
-        self.q_mla = torch.zeros(tile, 1, heads, d_qk, dtype=torch.bfloat16, device=dev)
-        self._bound = None
+        self._caches = None
+        self._plan = None
 
     def bind(self, kv_pages: torch.Tensor, block_table_row: torch.Tensor, kv_mla: torch.Tensor) -> None:
         """The sequence's caches on this rank: index-K pages, its page-table row (max_pages,), its local
         KV rows (max_pages * page_tokens, 1, d_qk) with local token l at row l."""
         self.block_table.copy_(block_table_row.to(torch.int32).view(1, -1).expand_as(self.block_table))
-        self._bound = LayerInputs(kv_pages=kv_pages, block_table=self.block_table, seq_lens=self.seq_lens,
-                                  q_idx=self.q_idx, w_idx=self.w_idx, q_mla=self.q_mla, kv_mla=kv_mla)
-        self.layer.bind(self._bound)
+        self._caches = (kv_pages, kv_mla)
+        self._plan = None
 
     def run(self, q_idx: torch.Tensor, w_idx: torch.Tensor, q_mla: torch.Tensor, positions: torch.Tensor,
             out: torch.Tensor, out_lse: torch.Tensor | None = None, sel_i: torch.Tensor | None = None,
             sel_c: torch.Tensor | None = None, stream=None) -> None:
-        """q_idx (Tq, 64, 128) bf16, w_idx (Tq, 64) fp32, q_mla (Tq, 1, H, d_qk) bf16 and positions (Tq,)
-        global token positions of the chunk's query tokens, replicated on every rank; Tq a multiple of
-        `tile`.  `out` (Tq / cp, H, 512) receives this rank's owned rows: query j of the chunk is owned by
-        rank j % cp (tile is a multiple of cp) and lands at row j // cp.  Optional `sel_i` (Tq, top_k) /
-        `sel_c` (Tq,) receive every query's selection (identical on all ranks).  Asynchronous on `stream`;
-        one kernel launch plus small device copies per tile."""
-        assert self._bound is not None, "bind() the sequence's caches first"
+        """q_idx (Tq, 64, 128) bf16, w_idx (Tq, 64) fp32, q_mla (Tq, 1, H, d_qk) bf16 (contiguous, on the
+        device) and positions (Tq,) global token positions of the chunk's query tokens, replicated on every
+        rank; Tq a multiple of `tile`.  `out` (Tq / cp, H, 512) receives this rank's owned rows: query j of
+        the chunk is owned by rank j % cp (tile is a multiple of cp) and lands at row j // cp.  Optional
+        `sel_i` (Tq, top_k) / `sel_c` (Tq,) receive every query's selection (identical on all ranks).
+        Asynchronous on `stream`.  Per tile: the launch parameters point at the tile's slices of the query
+        tensors (no copies of the inputs), one kernel launch, and the copies of the results."""
+        assert self._caches is not None, "bind() the sequence's caches first"
+        kv_pages, kv_mla = self._caches
         Tq, T, cp = q_idx.shape[0], self.tile, self.cp
         assert Tq % T == 0 and positions.numel() == Tq
-        lens = causal_local_lens(positions.to(self.layer.device), cp, self.rank)
+        assert q_idx.is_contiguous() and w_idx.is_contiguous() and q_mla.is_contiguous()
+        # The launch parameters of every tile (addresses of the tile's slices) are built once per set of
+        # tensors and reused while the caller keeps passing the same buffers: building them is host work of
+        # about a tile's run time.  The causal lengths go through a buffer of this object for the same reason.
+        key = (q_idx.data_ptr(), w_idx.data_ptr(), q_mla.data_ptr(), kv_pages.data_ptr(), kv_mla.data_ptr(), Tq)
+        if self._plan is None or self._plan[0] != key:
+            lens_buf = torch.zeros(Tq, dtype=torch.int32, device=self.layer.device)
+            params = []
+            for t0 in range(0, Tq, T):
+                self.layer.bind(LayerInputs(kv_pages=kv_pages, block_table=self.block_table, seq_lens=lens_buf[t0:t0 + T],
+                                            q_idx=q_idx[t0:t0 + T], w_idx=w_idx[t0:t0 + T], q_mla=q_mla[t0:t0 + T],
+                                            kv_mla=kv_mla))
+                params.append(self.layer._params)
+            self._plan = (key, lens_buf, params, (q_idx, w_idx, q_mla))   # (the tensors are kept alive with the plan)
+        _, lens_buf, params, _ = self._plan
         own = T // cp
         ctx = torch.cuda.stream(stream) if stream is not None and hasattr(stream, "cuda_stream") else _null()
         with ctx:
-            for t0 in range(0, Tq, T):
-                self.q_idx.copy_(q_idx[t0:t0 + T], non_blocking=True)
-                self.w_idx.copy_(w_idx[t0:t0 + T], non_blocking=True)
-                self.q_mla.copy_(q_mla[t0:t0 + T], non_blocking=True)
-                self.seq_lens.copy_(lens[t0:t0 + T], non_blocking=True)
+            lens_buf.copy_(causal_local_lens(positions.to(self.layer.device), cp, self.rank), non_blocking=True)
+            for i, t0 in enumerate(range(0, Tq, T)):
+                self.layer._params = params[i]
                 self.layer.step(stream=stream)
                 r0 = t0 // cp
                 out[r0:r0 + own].copy_(self.layer.out[:own], non_blocking=True)
