@@ -423,6 +423,10 @@ __device__ void mla_umma_tile(const mdc_sparse_mla_params& p, int r, int hb, int
       for (int t = done; t < upto; ++t) mbar_arrive_if(&full[t % S], lane == 0);
       done = upto;
     };
+    if (i0 == 1 && ok) {  // tile 0 was issued before the query hand-over: it has had time to land, publish it now
+      cp_async_wait<0>();
+      publish(1);
+    }
     for (int i = i0; i < n_my && ok; ++i) {
       const int st = i % S;
       if (i >= S) {
