@@ -318,7 +318,8 @@ struct RowExactScratch {
 
 // Steps b and c of the exact mode, after the boundary bin `bin` of the global row is known (0: the row
 // holds fewer than top_k scores, everything valid is selected).  n_pass: this chunk's scores in bins >= bin.
-// Returns true when the row was published (this task emitted its share), false when the row falls back.
+// hist2: 2048 words of shared memory for the threshold search (the chunk histogram's space, which is no longer
+// needed).  Returns true when the row was published (this task emitted its share), false when the row falls back.
 static __device__ __noinline__ bool chunk_publish_row_exact(const RowThreshold& rt, int32_t* status, int b, int chunk, int n_chunks,
                                                const uint32_t* keys, int n_local, int base_pos, int top_k, int id_mul,
                                                int id_add, uint32_t bin, int n_pass, SelectScratch& sel,
