@@ -444,6 +444,12 @@ typedef struct {
    * event buffer: cell thr_ev_base + b counts histogram arrivals, thr_ev_base + B + b slot arrivals. */
   int32_t thr_exact, thr_ev_base;
   int64_t thr_off;
+  /* Optional: the attention query of the step (mla.q without q_stage, the q_mla part of q_stage with it)
+   * arrives by a host copy that may still be in flight when the launch starts.  The tasks that read it first
+   * (ATTN, or QPATH parts >= 1) then wait, bounded by wait_budget_ns, until *q_host_flag >= phase + 1; the
+   * host writes that value with a copy queued behind the query's copy on the same stream.  The wait is on
+   * a DMA, not on another kernel.  NULL: the query is in place when the launch starts. */
+  const unsigned long long* q_host_flag;
 } mdc_layer_params;
 
 /* Persistent kernel: block i walks queue row i (format of

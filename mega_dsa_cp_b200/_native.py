@@ -96,7 +96,7 @@ class LayerParams(C.Structure):
         ("out_dtype", i32), ("l1_groups", i32), ("mid_v", p_void), ("mid_i", p_void), ("mid_c", p_void),
         ("cmp", CompressParams), ("q_stage", p_void), ("q_off", i64),
         ("kvw_k_idx", p_void), ("kvw_kv", p_void), ("kvw_glen", p_void), ("kvw_advance", i32),
-        ("thr_hist", p_void), ("thr_done", p_void), ("kv_group", i32), ("cand_direct", i32), ("thr_exact", i32), ("thr_ev_base", i32), ("thr_off", i64),
+        ("thr_hist", p_void), ("thr_done", p_void), ("kv_group", i32), ("cand_direct", i32), ("thr_exact", i32), ("thr_ev_base", i32), ("thr_off", i64), ("q_host_flag", p_void),
     ]
 
 

@@ -120,10 +120,31 @@ __device__ __host__ inline int64_t q_mla_bytes(const mdc_layer_params& L) { retu
 // One SM moves about 45 GB/s this way, so the big array is cut into slices that run as separate tasks.
 // part 0: the indexer's share (q_idx, weights: 16.6 KB, what the LOGITS tasks wait for); part 1 + s:
 // slice s of n_slices of the attention query (147 KB in all, needed only once the selection is done).
+// The step's attention query may still be on its way from the host: thread 0 polls the flag the host's copy
+// stream writes behind it (bounded), the caller's barrier publishes the result.
+__device__ inline void wait_host_query(const mdc_mega_params& p, unsigned long long phase) {
+  const unsigned long long* flag = p.layer.q_host_flag;
+  if (flag == nullptr || threadIdx.x != 0) return;
+  const unsigned long long want = phase + 1ull, t0 = global_timer_ns();
+  unsigned long long seen = ld_acquire_sys_u64(flag);
+  while (seen < want) {
+    nanosleep(128);
+    seen = ld_acquire_sys_u64(flag);
+    if (seen < want && static_cast<long long>(global_timer_ns() - t0) > p.wait_budget_ns) {
+      report_failure(p.status, MDC_DEV_WAIT_TIMEOUT, -2000, 0, seen, want);
+      break;
+    }
+  }
+}
+
 __device__ __noinline__ void op_qpath(const mdc_mega_params& p, int b, int part, int n_slices, unsigned long long phase,
                                 unsigned char* smem) {
   const mdc_layer_params& L = p.layer;
   if (!L.q_stage || b % L.cp != L.rank) return;
+  if (part >= 1 && L.q_host_flag) {
+    wait_host_query(p, phase);
+    sync_workers();
+  }
   const PeerBuffer arena{static_cast<unsigned char*>(p.arena.base), p.arena.offsets, p.arena.my_rank, p.arena.world,
                          p.arena.mc_base};
   const int n_owned = ceil_div(L.B - L.rank, L.cp), j = b / L.cp;
@@ -487,6 +508,10 @@ __device__ __noinline__ void op_attn(const mdc_mega_params& p, int b, int hbv, i
   mdc_sparse_mla_params mp = L.mla;
   if (L.rank != owner) mp.attn_sink = nullptr;
   redirect_q(p, phase, nullptr, &mp);
+  if (L.q_host_flag && !L.q_stage) {   // (with QPATH tasks they have waited for it)
+    wait_host_query(p, phase);
+    __syncthreads();
+  }
   if (mp.kv_dtype == MDC_DT_BF16 && L.H % kMuHeads == 0) {
     if (mp.d_qk == 576) mla_umma_tile<576>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);
     else mla_umma_tile<512>(mp, b, hbv >> 2, hbv & 3, split, ns, smem, slot, lse_row, true);

@@ -191,13 +191,17 @@ class DsaDecodeLayer:
                  device="cuda", out_dtype=torch.bfloat16, phases: int = 2, softmax_scale: float | None = None,
                  attn_splits: int | None = None, compressor=None, distribute_q: bool = False, kvwrite: bool = False,
                  row_threshold: bool = True, kv_group: int = 1, cand_direct: bool = True, row_exact=None,
-                 q_tasks: bool | None = None, dynamic: bool = False):
+                 q_tasks: bool | None = None, dynamic: bool = False, host_query: bool = False):
         """kv_group: consecutive batch entries that share one sequence's KV rows (chunked prefill: the
         query tokens of a tile as batch entries, see prefill.py); 1 = every entry its own sequence.
         distribute_q: the step's query block of sequence b is supplied by its owner rank only (bind()
         then takes the owned sequences' tensors) and a QPATH task stores it into every rank's arena.
         With one rank the kernels read the staging block in place and no QPATH task runs, unless
         q_tasks=True asks for them.
+        host_query (with distribute_q): step_from_host() copies the attention query on a second stream while
+        the step's indexer phase already runs; the tasks that read it wait for a flag the copy stream writes.
+        (Measured at one rank: slower than the plain sequence, 214 against 182 us per step: the query's copy
+        takes 23 us, the extra stream operations more.  Off by default.)
         row_exact: the chunk tasks settle the row's exact top-k themselves (default: with one rank;
         across ranks the two exchange rounds cost more than the merge they save: measured).
         compressor: an optional tiles.compress.CompressorState of this rank; the layer-step then also
@@ -284,6 +288,12 @@ class DsaDecodeLayer:
         # distribute_q: the owned sequences' query blocks, one contiguous block [q_idx | w | q_mla] that a
         # caller fills from the host in one copy (views below); sequence b = j * cp + rank is entry j
         self.q_stage = None
+        self.host_query = host_query and distribute_q
+        if self.host_query:
+            self.q_flag = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self._h_flags = torch.zeros(8, dtype=torch.int64).pin_memory()
+            self._side = torch.cuda.Stream(device=self.device)
+            self._prev_done = None
         if distribute_q:
             n = self.n_owned
             nq, nw, nm = n * 64 * 128 * 2, n * 64 * 4, n * heads * d_qk * 2
@@ -368,6 +378,9 @@ class DsaDecodeLayer:
             L.q_stage, L.q_off = N.ptr(self.q_stage), self.arena.regions["q"]
         L.thr_hist, L.thr_done = N.ptr(self.thr_hist), N.ptr(self.thr_done)
         self._params, self._inputs = L, x
+        if self.host_query:   # step_from_host() launches with a copy of the parameters that carries the flag
+            self._params_hq = N.LayerParams.from_buffer_copy(L)
+            self._params_hq.q_host_flag = N.ptr(self.q_flag)
 
     def bind_compressor(self, seq_len, new_attn, new_idx, ape_attn, ape_idx, norm_w_attn, norm_w_idx, norm_eps: float,
                         freqs, fp8_scale: float = 1.0) -> None:
@@ -375,7 +388,7 @@ class DsaDecodeLayer:
         step): seq_len (B,) int32 GLOBAL lengths before the step, the new records of this rank, the slot
         biases, norm weights and rope table.  Call after bind()."""
         from .tiles.compress import fill_finalize_params
-        assert self._params is not None and self.compressor is not None
+        assert self._params is not None and self.compressor is not None and not self.host_query
         st = self.compressor
         c = N.CompressParams()
         c.B, c.cp, c.rank, c.q_len, c.ratio = st.B, st.cp, st.rank, st.q_len, st.ratio
@@ -393,20 +406,48 @@ class DsaDecodeLayer:
         by the caller before each step; global_len (B,) int32 = sequence lengths before the step.  With
         `advance` the kernel adds 1 to global_len itself.  The bound block table must already hold a page
         for the new slot; seq_lens and the caches are written by the step."""
-        assert self._params is not None and self.kvwrite
+        assert self._params is not None and self.kvwrite and not self.host_query
         assert k_idx_new.dtype == torch.float32 and global_len.dtype == torch.int32
         L = self._params
         L.kvw_k_idx, L.kvw_kv, L.kvw_glen, L.kvw_advance = N.ptr(k_idx_new), N.ptr(kv_new), N.ptr(global_len), int(advance)
         self._kvw_keep = (k_idx_new, kv_new, global_len)
 
-    def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None) -> None:
+    def step(self, wait_budget_ns: int = 2_000_000_000, stream=None, trace=None, _params=None) -> None:
         """Launches one layer-step (asynchronous): exactly one kernel launch, nothing else.  The
         phase lives on the device and the kernel advances it, so a step can be captured in a CUDA
         graph and replayed.  Every rank must run the same number of steps."""
         assert self._params is not None, "bind() inputs first"
-        launch_megakernel(self.dsched, self.events, self.arena, self.status, layer=self._params,
+        launch_megakernel(self.dsched, self.events, self.arena, self.status, layer=_params or self._params,
                           wait_budget_ns=wait_budget_ns, stream=stream, trace=trace, device_phase=True)
         self.phase += 1   # host mirror, for reporting only
+
+    def step_from_host(self, hblock: torch.Tensor, h_out: torch.Tensor | None = None, wait_budget_ns: int = 2_000_000_000) -> None:
+        """One step whose query block comes from pinned host memory (`hblock`: uint8, the layout of
+        q_stage: [q_idx | w | q_mla] of the owned sequences) and whose owned output rows go back to pinned
+        host memory (`h_out`, optional), all asynchronous on the current stream (synchronize it to read
+        h_out).  Built with host_query=True, the indexer part is copied on the current stream ahead of the
+        launch and the attention query, nine tenths of the block, on a second stream while the indexer
+        phase runs; a flag copied behind it releases the tasks that read it."""
+        assert self.q_stage is not None and hblock.numel() == self.q_stage.numel()
+        main = torch.cuda.current_stream(self.device)
+        if not self.host_query:
+            self.q_stage.copy_(hblock, non_blocking=True)
+            self.step(wait_budget_ns=wait_budget_ns)
+        else:
+            n_idx = self.n_owned * (64 * 128 * 2 + 64 * 4)
+            self.q_stage[:n_idx].copy_(hblock[:n_idx], non_blocking=True)
+            slot = self.phase % self._h_flags.numel()
+            self._h_flags[slot] = self.phase + 1        # (read by the copy below; eight steps may be in flight)
+            if self._prev_done is not None:
+                self._side.wait_event(self._prev_done)  # the previous step has finished reading its query
+            with torch.cuda.stream(self._side):
+                self.q_stage[n_idx:].copy_(hblock[n_idx:], non_blocking=True)
+                self.q_flag.copy_(self._h_flags[slot:slot + 1], non_blocking=True)
+            self.step(wait_budget_ns=wait_budget_ns, _params=self._params_hq)
+            self._prev_done = torch.cuda.Event()
+            self._prev_done.record(main)
+        if h_out is not None:
+            h_out.copy_(self.out, non_blocking=True)
 
     def owned_rows(self):
         """Sequences whose merged output this rank holds; sequence b is row b // cp of `out`."""

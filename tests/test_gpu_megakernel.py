@@ -420,3 +420,44 @@ def test_decode_layer_tied_rows_fall_back_to_the_merge():
                                        1 / math.sqrt(DQK))
         assert (layer.out[b].cpu() - o).abs().max() < 2e-2
         assert (layer.out_lse[b].cpu() - l).abs().max() < 1e-3
+
+
+def test_step_from_host_copies_the_attention_query_behind_the_launch():
+    """The step's query block comes from pinned host memory: the indexer part ahead of the launch, the attention
+    query on a second stream while the step already runs.  Four steps with a different query each; every
+    step's output must belong to ITS query (a task that read the query before it landed would show the
+    previous step's), against the oracle for the last one."""
+    from dsa_inputs import indexer_case
+    from mega_dsa_cp_b200.layer import DsaDecodeLayer, LayerInputs
+    from oracle import dsa_oracle as orc
+
+    B, S, K, bpc, P, H, DQK = 3, 8192, 1024, 32, 64, 128, 576
+    case = indexer_case(B, S, P, "nvfp4", seed=41)
+    g = torch.Generator().manual_seed(42)
+    kv = (torch.randn(B * S, 1, DQK, generator=g) * 0.5).bfloat16()
+    seq = torch.tensor([S, S - 9, S - 200], dtype=torch.int32)
+    layer = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=64, distribute_q=True, host_query=True)
+    d = lambda t: t.to(DEV)
+    layer.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), None, None, None, d(kv)))
+    hblock = torch.zeros(layer.q_stage.numel(), dtype=torch.uint8).pin_memory()
+    nq, nw = B * 64 * 128 * 2, B * 64 * 4
+    hblock[:nq].view(torch.bfloat16).copy_(case["q"].reshape(-1))
+    hblock[nq:nq + nw].view(torch.float32).copy_(case["w"].reshape(-1))
+    h_out = torch.zeros(B, H, 512, dtype=torch.float32).pin_memory()
+    outs, qs = [], []
+    for step in range(4):
+        q_mla = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+        hblock[nq + nw:].view(torch.bfloat16).copy_(q_mla.reshape(-1))
+        layer.step_from_host(hblock, h_out)
+        torch.cuda.current_stream().synchronize()
+        layer.check_status()
+        outs.append(h_out.clone())
+        qs.append(q_mla)
+    assert all(not torch.equal(outs[i], outs[i + 1]) for i in range(3))
+    for b in range(B):
+        n = int(layer.sel_c[b])
+        for step in (2, 3):   # the selection is the same every step (same indexer query); the attention follows q_mla
+            o, _ = orc.attend_selected_ref(qs[step][b, 0].float(), kv[b * S:(b + 1) * S, 0].float(), layer.sel_i[b, :n].cpu(),
+                                           1 / math.sqrt(DQK))
+            assert (outs[step][b] - o).abs().max() < 2e-2, (b, step)
