@@ -449,6 +449,23 @@ class DsaDecodeLayer:
         if h_out is not None:
             h_out.copy_(self.out, non_blocking=True)
 
+    def capture_host_step(self, hblock: torch.Tensor, h_out: torch.Tensor | None = None):
+        """The plain step_from_host() sequence (query block in, one launch, owned rows out) captured once as a
+        CUDA graph over the given pinned buffers: graph.replay() then costs one host call per step instead of
+        three.  The caller refreshes `hblock` before a replay and synchronizes before reading `h_out`."""
+        assert self.q_stage is not None and self._params is not None
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                self.q_stage.copy_(hblock, non_blocking=True)
+                self.step(stream=stream)
+                if h_out is not None:
+                    h_out.copy_(self.out, non_blocking=True)
+        self.phase -= 1   # (the capture itself ran nothing)
+        return graph
+
     def owned_rows(self):
         """Sequences whose merged output this rank holds; sequence b is row b // cp of `out`."""
         return [b for b in range(self.B) if b % self.cp == self.rank]

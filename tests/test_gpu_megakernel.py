@@ -461,3 +461,21 @@ def test_step_from_host_copies_the_attention_query_behind_the_launch():
             o, _ = orc.attend_selected_ref(qs[step][b, 0].float(), kv[b * S:(b + 1) * S, 0].float(), layer.sel_i[b, :n].cpu(),
                                            1 / math.sqrt(DQK))
             assert (outs[step][b] - o).abs().max() < 2e-2, (b, step)
+    # the plain sequence (block in, launch, rows out) captured once and replayed with a new query
+    plain = DsaDecodeLayer(B, cp=1, top_k=K, max_pages=S // P, blocks_per_chunk=bpc, kv_seq_stride=S,
+                           out_dtype=torch.float32, n_ctas=64, distribute_q=True)
+    plain.bind(LayerInputs(d(case["fused"]), d(case["bt"]), d(seq), None, None, None, d(kv)))
+    plain.step_from_host(hblock, h_out)
+    torch.cuda.synchronize()
+    assert (h_out - outs[3]).abs().max() < 1e-5      # same inputs as the last step above
+    graph = plain.capture_host_step(hblock, h_out)
+    q_new = (torch.randn(B, 1, H, DQK, generator=g) * 0.5).bfloat16()
+    hblock[nq + nw:].view(torch.bfloat16).copy_(q_new.reshape(-1))
+    graph.replay()
+    torch.cuda.synchronize()
+    plain.check_status()
+    for b in range(B):
+        n = int(plain.sel_c[b])
+        o, _ = orc.attend_selected_ref(q_new[b, 0].float(), kv[b * S:(b + 1) * S, 0].float(), plain.sel_i[b, :n].cpu(),
+                                       1 / math.sqrt(DQK))
+        assert (h_out[b] - o).abs().max() < 2e-2, b
