@@ -114,6 +114,32 @@ def test_megakernel_check_rejects_bad_layer_configurations():
     p = _valid_mega_params(N)
     p.arena = N.PeerBufferC(None, None, 0, 1, 0)                      # a layer needs the arena
     assert chk(p) == -4
+    # the exact row selection and the candidate exchange variants
+    A = 1 << 20
+    def exact(cp, mode, direct):
+        p = _valid_mega_params(N, cp=cp)
+        p.layer.thr_hist = p.layer.thr_done = A
+        p.layer.thr_exact, p.layer.thr_ev_base, p.layer.thr_off, p.layer.cand_direct = mode, p.n_events, 4096, direct
+        return p
+    assert chk(exact(1, 1, 0)) == 0 and chk(exact(2, 1, 1)) == 0 and chk(exact(2, 2, 0)) == 0
+    assert chk(exact(2, 1, 0)) == -1          # across ranks the selection is published through the chunk lists' layout
+    assert chk(exact(2, 2, 1)) == -1          # ... and a rank's own exact list is one list per rank
+    assert chk(exact(1, 3, 0)) == -1
+    p = exact(1, 1, 0)
+    p.layer.thr_hist = None                   # no row histogram
+    assert chk(p) == -1
+    p = exact(1, 1, 0)
+    p.layer.thr_ev_base = 0                   # the extra event cells must lie behind the queue's events
+    assert chk(p) == -1
+    p = _valid_mega_params(N, cp=2, top_k=2046)
+    p.layer.cand_direct = 1                   # the ids of a slice start on a 16-byte boundary
+    assert chk(p) in (-1, -2)
+    p = _valid_mega_params(N)
+    p.layer.kv_group = -1
+    assert chk(p) == -1
+    p = _valid_mega_params(N)
+    p.dyn_task_off, p.dyn_n_tasks = A, 4      # dynamic scheduling without its counters
+    assert chk(p) == -4
     # and the Python layer object refuses the same things before it builds anything
     from mega_dsa_cp_b200.layer import DsaDecodeLayer
     with pytest.raises(AssertionError):
@@ -293,3 +319,39 @@ def test_task_offsets_of_a_packed_row():
     assert len(offs) == len(s.topo) == sum(1 for t in tasks if t.rank == 1)
     assert offs[0] == 0 and all(b - a >= 4 for a, b in zip(offs, offs[1:]))
     assert [flat[o] & 0xFF for o in offs] == [s.op_of[i] for i in s.topo]
+
+
+def test_ctypes_mirrors_match_the_header_layout(tmp_path):
+    """include/mdc.h compiled as plain C by gcc: size of every parameter struct and the offset of every field
+    against the ctypes mirrors of _native.py (a mismatch would hand the kernels shifted pointers)."""
+    import ctypes as C
+    import shutil
+    import subprocess
+
+    from mega_dsa_cp_b200 import _native as N
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    pairs = {"mdc_logits_params": N.LogitsParams, "mdc_merge_topk_params": N.MergeTopkParams,
+             "mdc_lse_merge_params": N.LseMergeParams, "mdc_sparse_mla_params": N.SparseMlaParams,
+             "mdc_event_set": N.EventSetC, "mdc_peer_buffer": N.PeerBufferC, "mdc_compress_params": N.CompressParams,
+             "mdc_pingpong_params": N.PingpongParams, "mdc_layer_params": N.LayerParams, "mdc_mega_params": N.MegaParams}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "mdc.h"', "int main(void) {"]
+    for cname, mirror in pairs.items():
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for fname, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([gcc, "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = dict(line.split() for line in subprocess.run([str(exe)], capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs.items():
+        assert int(got[cname]) == C.sizeof(mirror), (cname, got[cname], C.sizeof(mirror))
+        for fname, _ in mirror._fields_:
+            assert int(got[f"{cname}.{fname}"]) == getattr(mirror, fname).offset, (cname, fname)
